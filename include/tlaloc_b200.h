@@ -1,0 +1,218 @@
+/*
+ * C ABI of libtlaloc_kernels.so: the B200 (sm_100a) kernels of Tlaloc's LLM
+ * decode hot path.  Plain pointers and sizes only; every pointer named
+ * "device" is a CUDA device pointer, `stream` is a cudaStream_t / CUstream
+ * passed as void*, and every function only enqueues work on that stream (no
+ * allocation, no synchronisation, no context switch), so it can be called
+ * while the stream is being captured into a CUDA graph.
+ *
+ * Each function returns TLALOC_B200_OK or a negative status; the calling
+ * thread's message is then available from tlaloc_b200_last_error().
+ *
+ * Reference interfaces these entry points stand in for (paths inside the
+ * reference project) are cited at each declaration.  Bindings: the typed-FFI
+ * handlers registered by TlalocRegisterKernels call these same functions; a
+ * JVM binds them with java.lang.foreign downcalls exactly as
+ * runtime-cuda/src/jvmMain/kotlin/io/tlaloc/runtime/cuda/CudaDriverFfm.kt:68-72
+ * binds libcuda.
+ */
+#ifndef TLALOC_B200_H_
+#define TLALOC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TLALOC_B200_ABI_VERSION 1
+
+/* Status codes. */
+#define TLALOC_B200_OK 0
+#define TLALOC_B200_INVALID_ARGUMENT (-1) /* a shape/dtype the op's contract refuses; message names it */
+#define TLALOC_B200_UNSUPPORTED (-2)      /* legal for the op, outside what these kernels cover */
+#define TLALOC_B200_INTERNAL (-3)         /* a CUDA error; message carries cudaGetErrorString */
+
+/* Element types, numbered as XLA_FFI_DataType (xla/ffi/api/c_api.h:239-260) so
+ * the typed-FFI handlers pass a buffer's dtype through unchanged. */
+#define TLALOC_B200_S8 2
+#define TLALOC_B200_S32 4
+#define TLALOC_B200_F32 11
+#define TLALOC_B200_BF16 16
+
+int tlaloc_b200_abi_version(void);
+
+/* The calling thread's last error message ("" if none). Static storage per thread. */
+const char* tlaloc_b200_last_error(void);
+
+/*
+ * One-time kernel set-up for the current device (opt-in dynamic shared
+ * memory).  Call once per process before the first launch that may run inside
+ * a CUDA graph capture; later launches call it lazily otherwise.
+ * Replaces: tlaloc_kernels::AllowMaxSharedMemory at XLA's INITIALIZE stage
+ * (triton/kernels/kernel_setup.cuh:24-47, paged_attention.cu:1347-1350).
+ */
+int tlaloc_b200_init(void);
+
+/* ------------------------------------------------------------------ paged attention */
+
+/*
+ * Number of context splits the kernels would like for a decode call of this
+ * shape, and the bytes of the f32 scratch [splits, R, H, D + 2] that goes with
+ * a split count.  The record per (split, row, head) is {max, sum, acc[D]} as
+ * in triton/kernels/paged_attention.cu:13-15.
+ */
+int tlaloc_b200_paged_attention_splits(int32_t num_rows, int32_t num_kv_heads, int32_t num_tables,
+                                       int32_t max_blocks_per_seq, int32_t block_size);
+size_t tlaloc_b200_paged_attention_scratch_bytes(int32_t num_rows, int32_t num_heads, int32_t head_dim,
+                                                 int32_t splits);
+
+/*
+ * PAGED_ATTENTION (ir/.../PagedAttentionAttrs.kt:79-286, interpreter
+ * ir/.../passes/DxirInterpreter.kt:2049-2140); replaces the launch pair
+ * SliceKernel + CombineKernel behind the tlaloc_paged_attention custom call
+ * (triton/kernels/paged_attention.cu:135-274,1174-1216,1300-1319) and the
+ * three-stage PTX chain kptx_paged_scores/softmax/out (kptx/.../KptxKernels.kt:970-1356).
+ *
+ *   query        device [R, H, D]            q_dtype  F32 | BF16
+ *   key_cache    device [P, bs, Hkv, D]      kv_dtype F32 | BF16
+ *   value_cache  device, same shape/dtype
+ *   block_tables device i32 [Tb, M]          row r reads table r / (R / Tb)
+ *   seq_lens     device i32 [R]              row r attends positions [first, seq_lens[r])
+ *   keep         device i32 [R, keep_chunks] or NULL: position t of row r takes part
+ *                iff keep[r, t / (M*bs/keep_chunks)] != 0
+ *   out          device [R, H, D]            out_dtype F32 | BF16
+ *   lse          device f32 [R, H] or NULL   log-sum-exp of the scaled scores (return_lse)
+ *   scratch      device f32 [splits, R, H, D + 2], caller-owned, contents undefined
+ *                on entry and exit; at most `splits` context slices are used
+ *   scale        softmax temperature (required attr); sliding_window 0 = none, else
+ *                first = max(0, len - window)
+ *
+ * GQA: query head h reads kv head h / (H / Hkv).  A row with seq_len 0 gives
+ * zeros (and lse -inf), as the interpreter does.  Positions >= seq_len are
+ * never read; block ids are clamped into [0, P) and lengths into [0, M*bs]
+ * rather than trusted.
+ */
+int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, const void* key_cache, const void* value_cache,
+                                int32_t kv_dtype, const int32_t* block_tables, const int32_t* seq_lens,
+                                const int32_t* keep, int32_t keep_chunks, void* out, int32_t out_dtype, float* lse,
+                                float* scratch, int32_t splits, int32_t num_rows, int32_t num_heads, int32_t head_dim,
+                                int32_t num_blocks, int32_t block_size, int32_t num_kv_heads,
+                                int32_t max_blocks_per_seq, int32_t num_tables, float scale, int32_t sliding_window,
+                                void* stream);
+
+/*
+ * KV_CACHE_WRITE (ir/.../KvCacheWriteAttrs.kt:62-159, interpreter
+ * DxirInterpreter.kt:2233-2272; XLA scatter form stablehlo/.../StablehloEmitter.kt:4634):
+ * row i of new_kv [T, Hkv*D] goes to pool slot slot_mapping[i]; a negative slot
+ * is padding and is skipped; slots >= P*bs are skipped too (the interpreter
+ * refuses them; the scatter drops them).  In place on the pool.
+ */
+int tlaloc_b200_kv_cache_write(void* pool, int32_t pool_dtype, const void* new_kv, int32_t new_dtype,
+                               const int32_t* slot_mapping, int32_t num_tokens, int32_t row_elems,
+                               int32_t num_slots, void* stream);
+
+/* ------------------------------------------------------------------ int8 weight-only projection */
+
+/*
+ * Bytes of f32 scratch the projection wants for this shape (split-K partials);
+ * 0 when it needs none.
+ */
+size_t tlaloc_b200_int8_gemm_scratch_bytes(int32_t m, int32_t k, int32_t n);
+
+/*
+ * y = (cast(x) @ cast(codes)) * scale: HfDecoderGraph.proj over a
+ * WeightQuant.INT8 weight (ir/.../inference/HfDecoderGraph.kt:625-655,
+ * WeightQuant.kt:8-22); replaces the XLA fusion of convert + dot_general +
+ * multiply the reference emits for it (stablehlo Int8WeightEmitTest.kt:44-61,
+ * docs/SERVING_ARCHITECTURE.md:562-564,786-789).
+ *
+ *   x       device [M, K]  x_dtype F32 | BF16 (F32 is rounded to bf16 RNE first, as
+ *           the graph's CAST does when the weight dtype is bf16)
+ *   codes   device int8 [K, N]  (in, out): the staged layout of HfStagedWeights.quantize
+ *   scales  device f32 [N], or NULL for none
+ *   residual device f32 [M, N] or NULL: added after the scale (the layer's residual add)
+ *   y       device [M, N]  y_dtype F32 | BF16
+ *   scratch device f32, scratch_bytes >= tlaloc_b200_int8_gemm_scratch_bytes(m, k, n)
+ *
+ * flags: TLALOC_B200_GEMM_EXACT runs the order-faithful kernel (f32 accumulate
+ * in increasing k with separate multiply and add, bit-identical to the
+ * interpreter's MATMUL, DxirInterpreter.kt:739-765); it is slow and exists for
+ * parity runs and odd shapes.
+ */
+#define TLALOC_B200_GEMM_EXACT 1
+#define TLALOC_B200_GEMM_X_F32_EXACT 2 /* with GEMM_EXACT: do not round an F32 x to bf16 (weight dtype F32) */
+int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_t* codes, const float* scales,
+                          const float* residual, void* y, int32_t y_dtype, float* scratch, size_t scratch_bytes,
+                          int32_t m, int32_t k, int32_t n, int32_t flags, void* stream);
+
+/*
+ * The same projection over an unquantized weight w [K, N] (F32 | BF16), order-faithful
+ * (the embedding-free head of ReferenceDecodeGraph.kt:113-147 and a bf16 lm_head).
+ */
+int tlaloc_b200_dense_gemm_exact(const void* x, int32_t x_dtype, const void* w, int32_t w_dtype, float* y, int32_t m,
+                                 int32_t k, int32_t n, int32_t flags, void* stream);
+
+/* ------------------------------------------------------------------ the decode step's small ops */
+
+/* EMBEDDING (DxirInterpreter.kt:1007-1040): out[p, :] = table[ids[p], :] widened to f32; ids clamped into the vocabulary. */
+int tlaloc_b200_embedding(const void* table, int32_t table_dtype, const int32_t* ids, float* out, int32_t positions,
+                          int32_t vocab, int32_t dim, void* stream);
+
+/*
+ * RMSNorm over the last axis (HfDecoderGraph.kt:663-699): x * rsqrt(mean(x^2) + eps) * gain.
+ * x f32 [rows, n]; gain f32 [n] or NULL; out F32 | BF16.
+ */
+int tlaloc_b200_rmsnorm(const float* x, const float* gain, void* out, int32_t out_dtype, int32_t rows, int32_t n,
+                        float eps, void* stream);
+
+/*
+ * RoPE (HfDecoderGraph.kt:792-818, HF rotate_half with the duplicated cos/sin tables of
+ * ropeTables :436-462) applied to q [T, H, hd] and k [T, Hkv, hd] (f32), followed by the two
+ * KV_CACHE_WRITEs of attention() (:1230-1231): rotated k and v [T, Hkv, hd] go to the pools at
+ * slot_mapping.  q_out [T, H, hd] is F32 | BF16.  cos/sin are f32 [max_pos, hd].  ld_q/ld_k/ld_v are the row
+ * strides of q, k and v in elements, so the three may be column blocks of one fused q|k|v projection result.
+ */
+int tlaloc_b200_rope_kv_write(const float* q, const float* k, const float* v, const int32_t* positions,
+                              const float* cos_table, const float* sin_table, const int32_t* slot_mapping,
+                              void* q_out, int32_t q_out_dtype, void* key_cache, void* value_cache, int32_t kv_dtype,
+                              int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                              int32_t num_slots, int32_t max_pos, int32_t ld_q, int32_t ld_k, int32_t ld_v,
+                              void* stream);
+
+/* SwiGLU (HfDecoderGraph.kt:979-988): silu(gate) * up; gate/up f32 with row stride `ld`, out F32 | BF16 [rows, n]. */
+int tlaloc_b200_swiglu(const float* gate, const float* up, int32_t ld, void* out, int32_t out_dtype, int32_t rows,
+                       int32_t n, void* stream);
+
+/* Greedy NEXT_TOKEN (DxirInterpreter.kt:2414-2426; triton/kernels/sample.cu greedy arm): first index of the maximum. */
+int tlaloc_b200_argmax(const float* logits, int32_t* out, int32_t rows, int32_t n, void* stream);
+
+/* ------------------------------------------------------------------ XLA typed-FFI registration */
+
+struct PJRT_Api;
+/*
+ * Registers this library's typed-FFI handlers (tlaloc_paged_attention,
+ * tlaloc_int8_gemm, tlaloc_kv_cache_write) with a PJRT GPU plugin's custom-call
+ * extension.  Returns NULL on success, else a message in static storage.
+ * Same name, signature and protocol as triton/kernels/tlaloc_kernels.cu:479-526,
+ * so triton/backend/pjrt_runtime.cc:139-164 (RegisterKernels) and
+ * runtime-pjrt/.../ffm/PjrtFfiRegistry.kt:192-204 (registerNativeLibrary) load
+ * this library unchanged.
+ */
+const char* TlalocRegisterKernels(const struct PJRT_Api* api);
+
+/*
+ * One handler by target name ("tlaloc_paged_attention", "tlaloc_int8_gemm",
+ * "tlaloc_kv_cache_write"), as an XLA_FFI_Handler* (XLA_FFI_Error* (*)(XLA_FFI_CallFrame*)),
+ * or NULL for an unknown name: for callers that register handlers one at a time
+ * (runtime-pjrt/.../ffm/PjrtFfiRegistry.kt:168-182) and for tests that drive a
+ * handler with a hand-built call frame (runtime-pjrt/.../ffm/XlaFfiCallFrameTest.kt:55-100).
+ */
+void* tlaloc_b200_ffi_handler(const char* target);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TLALOC_B200_H_ */

@@ -1,0 +1,132 @@
+"""Parity of the CUDA int8 weight-only projection with the CPU oracle, through the C ABI (needs a B200).
+
+The reference has no int8 x int8 -> int32 contraction on this path (activations are never int8); its projection
+is (cast(x) @ cast(codes)) * scale with bf16-exact products and an f32 accumulate
+(ir/.../inference/HfDecoderGraph.kt:625-655).  Two bars:
+  - wherever the f32 accumulation is exact (integer-valued activations, partial sums below 2^24) the result must
+    be the exact integer dot product, bit for bit, whatever the summation order;
+  - otherwise rel 1e-2 / abs 2e-3 against the oracle (in practice ~1e-6 relative: only the f32 summation order differs).
+The order-faithful kernel must equal the oracle bit for bit on any input.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from tlaloc_b200 import ops as o
+
+    return o
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    return t if dtype is None else t.to(dtype)
+
+
+def make(rng, m, k, n, x_int=False):
+    codes = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    scales = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
+    if x_int:
+        x = rng.integers(-8, 9, size=(m, k)).astype(np.float32)
+    else:
+        x = oracle.snap_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    return x, codes, scales
+
+
+def close(got, want):
+    err = np.abs(got - want)
+    assert np.all(err <= 2e-3 + 1e-2 * np.abs(want)), err.max()
+    return err.max()
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 16, 17, 32])
+@pytest.mark.parametrize("k,n", [(4096, 4096), (1024, 14336), (14336, 1024), (256, 688), (688, 256), (256, 1024), (2048, 4112)])
+def test_integer_activations_give_the_exact_integer_dot_product(m, k, n):
+    rng = np.random.default_rng(m * 7 + k + n)
+    x, codes, _ = make(rng, m, k, n, x_int=True)
+    want = (x.astype(np.int64) @ codes.astype(np.int64)).astype(np.float32)  # |sum| <= 14336*8*127 < 2^24
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), None)
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), want)
+    # power-of-two scales keep it exact too, and an f32 x is cast to bf16 on the way in
+    scales = np.exp2(rng.integers(-8, -2, size=n)).astype(np.float32)
+    got = ops().int8_gemm(dev(x), dev(codes), dev(scales))
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), want * scales[None, :])
+
+
+@pytest.mark.parametrize("m", [1, 8, 32])
+@pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 14336), (14336, 4096)])
+def test_sweep_shapes_against_the_oracle(m, k, n):
+    rng = np.random.default_rng(3)
+    x, codes, scales = make(rng, m, k, n)
+    want = oracle.proj_int8(x, codes, scales, round_x_bf16=True, threads=8)
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales))
+    torch.cuda.synchronize()
+    worst = close(got.cpu().numpy(), want)
+    assert worst <= 1e-4 * max(1.0, np.abs(want).max())
+
+
+def test_vocabulary_head_shape_against_the_oracle():
+    rng = np.random.default_rng(4)
+    m, k, n = 8, 4096, 128256
+    x, codes, scales = make(rng, m, k, n)
+    want = oracle.proj_int8(x, codes, scales, round_x_bf16=True, threads=8)
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales))
+    torch.cuda.synchronize()
+    close(got.cpu().numpy(), want)
+
+
+def test_more_than_32_rows_residual_and_bf16_output():
+    rng = np.random.default_rng(5)
+    m, k, n = 70, 1024, 2048
+    x, codes, scales = make(rng, m, k, n)
+    res = rng.standard_normal((m, n)).astype(np.float32)
+    want = oracle.proj_int8(x, codes, scales, round_x_bf16=True, threads=8) + res
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), residual=dev(res))
+    torch.cuda.synchronize()
+    close(got.cpu().numpy(), want)
+    got_b = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), residual=dev(res), out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    assert np.array_equal(got_b.float().cpu().numpy(), oracle.snap_bf16(got.cpu().numpy()))
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 8, 11), (2, 8, 8), (5, 37, 11), (4, 256, 688), (3, 300, 130)])
+def test_order_faithful_kernel_is_bit_identical_to_the_oracle(m, k, n):
+    rng = np.random.default_rng(k * n)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[0, min(3, k - 1)] = 0.0
+    codes = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    scales = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
+    for round_x in (True, False):
+        want = oracle.proj_int8(x, codes, scales, round_x_bf16=round_x)
+        got = ops().int8_gemm(dev(x), dev(codes), dev(scales), exact=True, x_f32_exact=not round_x)
+        torch.cuda.synchronize()
+        assert np.array_equal(got.cpu().numpy(), want)
+    w = rng.standard_normal((k, n)).astype(np.float32)
+    got = ops().dense_gemm_exact(dev(x), dev(w))
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), oracle.matmul_f32(x, w))
+    wb = oracle.snap_bf16(w)
+    got = ops().dense_gemm_exact(dev(x), dev(wb, torch.bfloat16))
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), oracle.matmul_f32(oracle.snap_bf16(x), wb))
+
+
+def test_quantized_weights_round_trip_like_the_reference_identity():
+    """int8 graph == graph of dequantized weights to 4.7e-6 relative (docs/CAPABILITIES.md:113), on the GPU path."""
+    rng = np.random.default_rng(6)
+    w = (rng.standard_normal((1024, 512)) * 0.02).astype(np.float32)  # [out, in]
+    codes, scales = oracle.quantize_int8(w)
+    x = oracle.snap_bf16(rng.standard_normal((4, 512)).astype(np.float32))
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales)).cpu().numpy()
+    deq = codes.astype(np.float32) * scales[None, :]
+    want = (x.astype(np.float64) @ deq.astype(np.float64)).astype(np.float32)
+    assert np.abs(got - want).max() <= 4.7e-6 * max(1.0, np.abs(want).max()) * 4
+    assert np.abs(deq.T - w).max() <= np.abs(w).max() / 127.0 * 0.5 + 1e-9

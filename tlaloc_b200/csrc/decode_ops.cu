@@ -1,0 +1,254 @@
+// The small ops of a Llama decode step around the two hot kernels (ir/.../inference/HfDecoderGraph.kt:
+// embedding :904-909, rmsNorm :663-699, rope :792-818 + the two KV_CACHE_WRITEs of attention() :1230-1231,
+// SwiGLU :979-988, greedy next token).  All are single-pass, HBM-bound element-wise or row-reduction kernels;
+// RoPE, the KV write and the query's narrowing are one launch.
+#include "common.cuh"
+
+namespace tlaloc_b200 {
+namespace {
+
+template <typename TT>
+__global__ void EmbeddingKernel(const TT* table, const int* ids, float* out, int vocab, int dim)
+{
+  const int p = blockIdx.x;
+  int v = __ldg(ids + p);
+  v = v < 0 ? 0 : (v >= vocab ? vocab - 1 : v);
+  const TT* src = table + static_cast<size_t>(v) * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) out[static_cast<size_t>(p) * dim + d] = ToF32(src[d]);
+}
+
+__device__ __forceinline__ float BlockSum(float v, float* red)
+{
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = 0.f;
+  for (int w = 0; w < nw; ++w) r += red[w];
+  return r;
+}
+
+// One CTA per row: x * rsqrt(mean(x^2) + eps) * gain.  mean = sum / n, rsqrt in double then narrowed, and the two
+// multiplies kept separate, as the interpreter evaluates the graph's nodes (DxirInterpreter.kt:567-572,1791-1807).
+template <typename OT>
+__global__ void __launch_bounds__(256) RmsNormKernel(const float* x, const float* gain, OT* out, int n, float eps)
+{
+  __shared__ float red[8];
+  const float* xr = x + static_cast<size_t>(blockIdx.x) * n;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const float v = xr[j];
+    ss = fmaf(v, v, ss);
+  }
+  ss = BlockSum(ss, red);
+  const float mean = ss / static_cast<float>(n);
+  const float rsq = static_cast<float>(1.0 / sqrt(static_cast<double>(mean + eps)));
+  OT* o = out + static_cast<size_t>(blockIdx.x) * n;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    float v = __fmul_rn(xr[j], rsq);
+    if (gain != nullptr) v = __fmul_rn(v, gain[j]);
+    o[j] = FromF32<OT>(v);
+  }
+}
+
+// Grid (tokens, H + 2*Hkv): head slot h < H rotates a query head into q_out; the next Hkv rotate a key head into
+// the key pool at the token's slot; the last Hkv copy a value head into the value pool.  x*cos + rotate_half(x)*sin
+// with each product and the sum rounded to f32 (HfDecoderGraph.kt:792-818).
+template <typename QT, typename KVT>
+__global__ void RopeKvWriteKernel(const float* q, const float* k, const float* v, const int* positions,
+                                  const float* cos_t, const float* sin_t, const int* slots, QT* q_out, KVT* kc,
+                                  KVT* vc, int H, int Hkv, int hd, int num_slots, int max_pos, int ldq, int ldk,
+                                  int ldv)
+{
+  const int t = blockIdx.x, hs = blockIdx.y;
+  const int half = hd >> 1;
+  int pos = __ldg(positions + t);
+  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+  const float* c = cos_t + static_cast<size_t>(pos) * hd;
+  const float* s = sin_t + static_cast<size_t>(pos) * hd;
+  if (hs < H) {
+    const float* x = q + static_cast<size_t>(t) * ldq + hs * hd;
+    QT* o = q_out + (static_cast<size_t>(t) * H + hs) * hd;
+    for (int j = threadIdx.x; j < hd; j += blockDim.x) {
+      const float rot = j < half ? -x[j + half] : x[j - half];
+      o[j] = FromF32<QT>(__fadd_rn(__fmul_rn(x[j], c[j]), __fmul_rn(rot, s[j])));
+    }
+    return;
+  }
+  const int slot = __ldg(slots + t);
+  if (slot < 0 || slot >= num_slots) return;  // padding lane (negative) or a slot past the pool: no write
+  if (hs < H + Hkv) {
+    const int h = hs - H;
+    const float* x = k + static_cast<size_t>(t) * ldk + h * hd;
+    KVT* o = kc + (static_cast<size_t>(slot) * Hkv + h) * hd;
+    for (int j = threadIdx.x; j < hd; j += blockDim.x) {
+      const float rot = j < half ? -x[j + half] : x[j - half];
+      o[j] = FromF32<KVT>(__fadd_rn(__fmul_rn(x[j], c[j]), __fmul_rn(rot, s[j])));
+    }
+  } else {
+    const int h = hs - H - Hkv;
+    const float* x = v + static_cast<size_t>(t) * ldv + h * hd;
+    KVT* o = vc + (static_cast<size_t>(slot) * Hkv + h) * hd;
+    for (int j = threadIdx.x; j < hd; j += blockDim.x) o[j] = FromF32<KVT>(x[j]);
+  }
+}
+
+template <typename OT>
+__global__ void SwigluKernel(const float* gate, const float* up, int ld, OT* out, int rows, int n)
+{
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<size_t>(rows) * n) return;
+  const int r = static_cast<int>(i / n), c = static_cast<int>(i - static_cast<size_t>(r) * n);
+  const float g = gate[static_cast<size_t>(r) * ld + c];
+  const float silu = g / (1.f + expf(-g));
+  out[i] = FromF32<OT>(__fmul_rn(silu, up[static_cast<size_t>(r) * ld + c]));
+}
+
+// One CTA per row; the first index of the maximum wins (DxirInterpreter.kt:2414-2426).
+__global__ void __launch_bounds__(256) ArgmaxKernel(const float* x, int* out, int n)
+{
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  const float* xr = x + static_cast<size_t>(blockIdx.x) * n;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const float v = xr[j];
+    if (v > best || (v == best && j < idx)) {
+      best = v;
+      idx = j;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) {
+      best = ov;
+      idx = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    bv[warp] = best;
+    bi[warp] = idx;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) {
+      if (bv[w] > best || (bv[w] == best && bi[w] < idx)) {
+        best = bv[w];
+        idx = bi[w];
+      }
+    }
+    // A row of NaNs (or an empty comparison) leaves idx unset: the interpreter's answer is index 0.
+    out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+  }
+}
+
+}  // namespace
+}  // namespace tlaloc_b200
+
+using namespace tlaloc_b200;
+
+extern "C" int tlaloc_b200_embedding(const void* table, int32_t table_dtype, const int32_t* ids, float* out,
+                                     int32_t positions, int32_t vocab, int32_t dim, void* stream)
+{
+  if (!table || !ids || !out) return Fail(kInvalid, "EMBEDDING: a required device pointer is null");
+  if (!IsFloatType(table_dtype)) return Fail(kInvalid, "EMBEDDING: the table must be f32 or bf16");
+  if (positions < 0 || vocab < 1 || dim < 1) return Fail(kInvalid, "EMBEDDING: bad sizes");
+  if (positions == 0) return kOk;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (table_dtype == TLALOC_B200_F32) {
+    EmbeddingKernel<<<positions, 256, 0, st>>>(static_cast<const float*>(table), ids, out, vocab, dim);
+  } else {
+    EmbeddingKernel<<<positions, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(table), ids, out, vocab, dim);
+  }
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? kOk : CudaFail("EMBEDDING launch", e);
+}
+
+extern "C" int tlaloc_b200_rmsnorm(const float* x, const float* gain, void* out, int32_t out_dtype, int32_t rows,
+                                   int32_t n, float eps, void* stream)
+{
+  if (!x || !out) return Fail(kInvalid, "RMSNORM: a required device pointer is null");
+  if (!IsFloatType(out_dtype)) return Fail(kInvalid, "RMSNORM: out must be f32 or bf16");
+  if (rows < 0 || n < 1) return Fail(kInvalid, "RMSNORM: bad sizes");
+  if (rows == 0) return kOk;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == TLALOC_B200_F32) {
+    RmsNormKernel<<<rows, 256, 0, st>>>(x, gain, static_cast<float*>(out), n, eps);
+  } else {
+    RmsNormKernel<<<rows, 256, 0, st>>>(x, gain, static_cast<__nv_bfloat16*>(out), n, eps);
+  }
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? kOk : CudaFail("RMSNORM launch", e);
+}
+
+extern "C" int tlaloc_b200_rope_kv_write(const float* q, const float* k, const float* v, const int32_t* positions,
+                                         const float* cos_table, const float* sin_table,
+                                         const int32_t* slot_mapping, void* q_out, int32_t q_out_dtype,
+                                         void* key_cache, void* value_cache, int32_t kv_dtype, int32_t num_tokens,
+                                         int32_t num_heads, int32_t num_kv_heads, int32_t head_dim, int32_t num_slots,
+                                         int32_t max_pos, int32_t ld_q, int32_t ld_k, int32_t ld_v, void* stream)
+{
+  const char* op = "ROPE_KV_WRITE";
+  if (!q || !k || !v || !positions || !cos_table || !sin_table || !slot_mapping || !q_out || !key_cache || !value_cache) {
+    return Fail(kInvalid, "%s: a required device pointer is null", op);
+  }
+  if (!IsFloatType(q_out_dtype) || !IsFloatType(kv_dtype)) return Fail(kInvalid, "%s: q_out and the pools must be f32 or bf16", op);
+  if (head_dim < 2 || head_dim % 2 != 0) {
+    return Fail(kInvalid, "%s: head_dim %d is odd; RoPE rotates pairs of channels (rotate_half)", op, head_dim);
+  }
+  if (num_tokens < 0 || num_heads < 1 || num_kv_heads < 1 || num_slots < 1 || max_pos < 1) return Fail(kInvalid, "%s: bad sizes", op);
+  if (ld_q < num_heads * head_dim || ld_k < num_kv_heads * head_dim || ld_v < num_kv_heads * head_dim) {
+    return Fail(kInvalid, "%s: a row stride is shorter than its row", op);
+  }
+  if (num_tokens == 0) return kOk;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 grid(num_tokens, num_heads + 2 * num_kv_heads);
+  const int threads = head_dim >= 128 ? 128 : 64;
+#define TLALOC_LAUNCH(QT, KVT)                                                                                      \
+  RopeKvWriteKernel<<<grid, threads, 0, st>>>(q, k, v, positions, cos_table, sin_table, slot_mapping,               \
+                                              static_cast<QT*>(q_out), static_cast<KVT*>(key_cache),                \
+                                              static_cast<KVT*>(value_cache), num_heads, num_kv_heads, head_dim,    \
+                                              num_slots, max_pos, ld_q, ld_k, ld_v)
+  if (q_out_dtype == TLALOC_B200_F32 && kv_dtype == TLALOC_B200_F32) TLALOC_LAUNCH(float, float);
+  else if (q_out_dtype == TLALOC_B200_F32) TLALOC_LAUNCH(float, __nv_bfloat16);
+  else if (kv_dtype == TLALOC_B200_F32) TLALOC_LAUNCH(__nv_bfloat16, float);
+  else TLALOC_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef TLALOC_LAUNCH
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? kOk : CudaFail("ROPE_KV_WRITE launch", e);
+}
+
+extern "C" int tlaloc_b200_swiglu(const float* gate, const float* up, int32_t ld, void* out, int32_t out_dtype,
+                                  int32_t rows, int32_t n, void* stream)
+{
+  if (!gate || !up || !out) return Fail(kInvalid, "SWIGLU: a required device pointer is null");
+  if (!IsFloatType(out_dtype)) return Fail(kInvalid, "SWIGLU: out must be f32 or bf16");
+  if (rows < 0 || n < 1 || ld < n) return Fail(kInvalid, "SWIGLU: bad sizes");
+  if (rows == 0) return kOk;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t total = static_cast<size_t>(rows) * n;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  if (out_dtype == TLALOC_B200_F32) {
+    SwigluKernel<<<blocks, 256, 0, st>>>(gate, up, ld, static_cast<float*>(out), rows, n);
+  } else {
+    SwigluKernel<<<blocks, 256, 0, st>>>(gate, up, ld, static_cast<__nv_bfloat16*>(out), rows, n);
+  }
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? kOk : CudaFail("SWIGLU launch", e);
+}
+
+extern "C" int tlaloc_b200_argmax(const float* logits, int32_t* out, int32_t rows, int32_t n, void* stream)
+{
+  if (!logits || !out) return Fail(kInvalid, "ARGMAX: a required device pointer is null");
+  if (rows < 0 || n < 1) return Fail(kInvalid, "ARGMAX: bad sizes");
+  if (rows == 0) return kOk;
+  ArgmaxKernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(logits, out, n);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? kOk : CudaFail("ARGMAX launch", e);
+}

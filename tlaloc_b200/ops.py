@@ -1,0 +1,168 @@
+"""The hot-path operators on torch CUDA tensors, through the C ABI.
+
+PyTorch is plumbing here (device memory, the current stream); every operator is one call into
+libtlaloc_kernels.so with raw device pointers, enqueued on torch's current stream.  There is no CPU path:
+a tensor that is not on a CUDA device is refused.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native as N
+from .attrs import PagedAttentionShape, parse_paged_attention
+
+_DT = {torch.float32: N.F32, torch.bfloat16: N.BF16, torch.int8: N.S8, torch.int32: N.S32}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}") from None
+
+
+def _dev(*ts) -> None:
+    for t in ts:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise ValueError("operands must be contiguous CUDA tensors (there is no CPU path)")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def init() -> None:
+    N.check(N.lib().tlaloc_b200_init())
+
+
+def paged_attention_scratch(shape: PagedAttentionShape, device, splits: int | None = None) -> torch.Tensor:
+    """The f32 scratch [S, R, H, D + 2] a call of this shape wants (S as the reference's emitter sizes it)."""
+    lib = N.lib()
+    if splits is None:
+        splits = lib.tlaloc_b200_paged_attention_splits(shape.num_seqs, shape.num_kv_heads, shape.num_tables,
+                                                        shape.max_blocks_per_seq, shape.block_size)
+    return torch.empty((splits, shape.num_seqs, shape.num_heads, shape.head_dim + 2), dtype=torch.float32, device=device)
+
+
+def paged_attention(query, key_cache, value_cache, block_tables, seq_lens, *, scale, sliding_window=None, keep=None,
+                    return_lse=False, out=None, scratch=None):
+    """PAGED_ATTENTION: operands and attrs as ir/.../PagedAttentionAttrs.kt; see include/tlaloc_b200.h."""
+    p = parse_paged_attention(query, key_cache, value_cache, block_tables, seq_lens, scale=scale,
+                              sliding_window=sliding_window, keep=keep, layer="tlaloc_b200.ops")
+    _dev(query, key_cache, value_cache, block_tables, seq_lens, keep)
+    if block_tables.dtype != torch.int32 or seq_lens.dtype != torch.int32 or (keep is not None and keep.dtype != torch.int32):
+        raise TypeError("PAGED_ATTENTION: the kernels read blockTables, seqLens and keep as int32")
+    if out is None:
+        out = torch.empty_like(query)
+    if scratch is None:
+        scratch = paged_attention_scratch(p, query.device)
+    lse = torch.empty((p.num_seqs, p.num_heads), dtype=torch.float32, device=query.device) if return_lse else None
+    N.check(N.lib().tlaloc_b200_paged_attention(
+        _ptr(query), _dt(query), _ptr(key_cache), _ptr(value_cache), _dt(key_cache), _ptr(block_tables),
+        _ptr(seq_lens), _ptr(keep), 0 if keep is None else keep.shape[1], _ptr(out), _dt(out), _ptr(lse),
+        _ptr(scratch), scratch.shape[0], p.num_seqs, p.num_heads, p.head_dim, p.num_blocks, p.block_size,
+        p.num_kv_heads, p.max_blocks_per_seq, p.num_tables, float(scale), int(sliding_window or 0), _stream()))
+    return (out, lse) if return_lse else out
+
+
+def kv_cache_write(pool, new_kv, slot_mapping):
+    """KV_CACHE_WRITE in place: pool [P, bs, Hkv, D], new_kv [T, Hkv, D], slot_mapping i32 [T]."""
+    _dev(pool, new_kv, slot_mapping)
+    P, bs, Hkv, D = pool.shape
+    T = slot_mapping.shape[0]
+    if new_kv.numel() != T * Hkv * D:
+        raise ValueError(f"KV_CACHE_WRITE: newKv must be [T, {Hkv}, {D}] for the pool, got {tuple(new_kv.shape)}")
+    N.check(N.lib().tlaloc_b200_kv_cache_write(_ptr(pool), _dt(pool), _ptr(new_kv), _dt(new_kv), _ptr(slot_mapping), T,
+                                               Hkv * D, P * bs, _stream()))
+    return pool
+
+
+def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.float32, exact=False, x_f32_exact=False,
+              scratch=None):
+    """y = (cast(x) @ cast(codes)) * scales (+ residual): x [M, K], codes int8 [K, N] (in, out), scales f32 [N]."""
+    _dev(x, codes, scales, residual)
+    M, K = x.shape
+    K2, Nn = codes.shape
+    if K2 != K or codes.dtype != torch.int8 or (scales is not None and tuple(scales.shape) != (Nn,)):
+        raise ValueError(f"INT8_PROJ: x [M, K] x codes int8 [K, N] with scales [N]; got {tuple(x.shape)}, {tuple(codes.shape)}")
+    if out is None:
+        out = torch.empty((M, Nn), dtype=out_dtype, device=x.device)
+    if scratch is None and x.dtype == torch.float32 and not exact:
+        scratch = torch.empty((N.lib().tlaloc_b200_int8_gemm_scratch_bytes(M, K, Nn) + 3) // 4, dtype=torch.float32,
+                              device=x.device)
+    flags = (N.GEMM_EXACT if exact else 0) | (N.GEMM_X_F32_EXACT if x_f32_exact else 0)
+    N.check(N.lib().tlaloc_b200_int8_gemm(_ptr(x), _dt(x), _ptr(codes), _ptr(scales), _ptr(residual), _ptr(out), _dt(out),
+                                          _ptr(scratch), 0 if scratch is None else scratch.numel() * 4, M, K, Nn, flags,
+                                          _stream()))
+    return out
+
+
+def dense_gemm_exact(x, w, *, x_f32_exact=False):
+    """The interpreter's MATMUL order over an unquantized weight w [K, N]; returns f32 [M, N]."""
+    _dev(x, w)
+    M, K = x.shape
+    out = torch.empty((M, w.shape[1]), dtype=torch.float32, device=x.device)
+    N.check(N.lib().tlaloc_b200_dense_gemm_exact(_ptr(x), _dt(x), _ptr(w), _dt(w), _ptr(out), M, K, w.shape[1],
+                                                 N.GEMM_X_F32_EXACT if x_f32_exact else 0, _stream()))
+    return out
+
+
+def embedding(table, ids):
+    _dev(table, ids)
+    ids = ids.reshape(-1)
+    out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+    N.check(N.lib().tlaloc_b200_embedding(_ptr(table), _dt(table), _ptr(ids), _ptr(out), ids.shape[0], table.shape[0],
+                                          table.shape[1], _stream()))
+    return out
+
+
+def rmsnorm(x, gain, eps, *, out=None, out_dtype=torch.float32):
+    _dev(x, gain)
+    rows, n = x.shape
+    if out is None:
+        out = torch.empty((rows, n), dtype=out_dtype, device=x.device)
+    N.check(N.lib().tlaloc_b200_rmsnorm(_ptr(x), _ptr(gain), _ptr(out), _dt(out), rows, n, float(eps), _stream()))
+    return out
+
+
+def rope_kv_write(q, k, v, positions, cos_table, sin_table, slot_mapping, key_cache, value_cache, *, q_out=None,
+                  q_dtype=torch.float32):
+    """RoPE on q [T,H,hd] and k [T,Hkv,hd], then K/V rows into the pools at slot_mapping; returns rotated q."""
+    _dev(positions, cos_table, sin_table, slot_mapping, key_cache, value_cache)
+    for t in (q, k, v):
+        if not t.is_cuda or t.dtype != torch.float32 or t.stride(2) != 1 or t.stride(1) != t.shape[2]:
+            raise ValueError("ROPE_KV_WRITE: q, k and v must be f32 CUDA tensors [T, heads, hd] with dense heads")
+    T, H, hd = q.shape
+    Hkv = k.shape[1]
+    P, bs = key_cache.shape[0], key_cache.shape[1]
+    if q_out is None:
+        q_out = torch.empty((T, H, hd), dtype=q_dtype, device=q.device)
+    N.check(N.lib().tlaloc_b200_rope_kv_write(_ptr(q), _ptr(k), _ptr(v), _ptr(positions), _ptr(cos_table), _ptr(sin_table),
+                                              _ptr(slot_mapping), _ptr(q_out), _dt(q_out), _ptr(key_cache),
+                                              _ptr(value_cache), _dt(key_cache), T, H, Hkv, hd, P * bs,
+                                              cos_table.shape[0], q.stride(0), k.stride(0), v.stride(0), _stream()))
+    return q_out
+
+
+def swiglu(gate, up, *, out=None, out_dtype=torch.float32):
+    """silu(gate) * up; gate and up may be column slices of one [rows, ld] matrix (a fused gate|up projection)."""
+    if not gate.is_cuda or gate.stride(1) != 1 or up.stride(1) != 1 or gate.stride(0) != up.stride(0):
+        raise ValueError("SWIGLU: gate and up must be CUDA row-major views with the same row stride")
+    rows, n = gate.shape
+    if out is None:
+        out = torch.empty((rows, n), dtype=out_dtype, device=gate.device)
+    N.check(N.lib().tlaloc_b200_swiglu(_ptr(gate), _ptr(up), gate.stride(0), _ptr(out), _dt(out), rows, n, _stream()))
+    return out
+
+
+def argmax(logits, out=None):
+    _dev(logits)
+    rows, n = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    N.check(N.lib().tlaloc_b200_argmax(_ptr(logits), _ptr(out), rows, n, _stream()))
+    return out

@@ -55,6 +55,9 @@ const char* tlaloc_b200_last_error(void);
  */
 int tlaloc_b200_init(void);
 
+/* Kernels this library has launched (or captured into a graph) since it was loaded, over all threads. */
+long long tlaloc_b200_launch_count(void);
+
 /* ------------------------------------------------------------------ paged attention */
 
 /*

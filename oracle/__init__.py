@@ -179,6 +179,16 @@ def kv_cache_write(pool, new_kv, slots) -> np.ndarray:
     return out
 
 
+def kv_cache_write_inplace(pool: np.ndarray, new_kv, slots) -> None:
+    """KV_CACHE_WRITE on a caller-owned f32 pool (no copy); same refusals."""
+    assert pool.dtype == np.float32 and pool.flags.c_contiguous
+    new_kv, slots = _f32(new_kv), _i32(slots)
+    P, bs, Hkv, D = pool.shape
+    rc = lib().orc_kv_cache_write(_p(pool), _p(new_kv), _p(slots), slots.shape[0], Hkv * D, P * bs)
+    if rc:
+        raise OracleRefusal("KV_CACHE_WRITE refused the slots")
+
+
 def rmsnorm(x, gain, eps) -> np.ndarray:
     x = _f32(x)
     g = None if gain is None else _f32(gain)
@@ -307,8 +317,8 @@ def decode_step(shape: DecoderShape, w: DecoderWeights, key_pools, value_pools, 
         q, k = rope(q, positions, cos, sin), rope(k, positions, cos, sin)
         if shape.kv_dtype == "bf16":
             k, v = snap_bf16(k), snap_bf16(v)
-        key_pools[l][...] = kv_cache_write(key_pools[l], k.reshape(B, -1), slot_mapping)
-        value_pools[l][...] = kv_cache_write(value_pools[l], v.reshape(B, -1), slot_mapping)
+        kv_cache_write_inplace(key_pools[l], k.reshape(B, -1), slot_mapping)
+        kv_cache_write_inplace(value_pools[l], v.reshape(B, -1), slot_mapping)
         att = paged_attention(q, key_pools[l], value_pools[l], block_tables, seq_lens, scale, threads=threads)
         h = h + proj_int8(att.reshape(B, H * hd), *lw["o"], round_x_bf16=bf, threads=threads)
         hn2 = rmsnorm(h, lw["ln2"], shape.rms_eps)

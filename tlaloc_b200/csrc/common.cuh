@@ -51,6 +51,9 @@ __device__ __forceinline__ float FromF32<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 FromF32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
+// Kernels launched by this library since it was loaded (tlaloc_b200_launch_count); a plain statistic.
+void CountLaunches(int n);
+
 // Once-per-process kernel attribute setup (dynamic shared memory opt-in) of each
 // translation unit; called from tlaloc_b200_init and from the typed-FFI
 // handlers' INITIALIZE stage, so that no launch inside a CUDA graph capture

@@ -167,7 +167,9 @@ extern "C" int tlaloc_b200_embedding(const void* table, int32_t table_dtype, con
     EmbeddingKernel<<<positions, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(table), ids, out, vocab, dim);
   }
   const cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? kOk : CudaFail("EMBEDDING launch", e);
+  if (e != cudaSuccess) return CudaFail("EMBEDDING launch", e);
+  CountLaunches(1);
+  return kOk;
 }
 
 extern "C" int tlaloc_b200_rmsnorm(const float* x, const float* gain, void* out, int32_t out_dtype, int32_t rows,
@@ -184,7 +186,9 @@ extern "C" int tlaloc_b200_rmsnorm(const float* x, const float* gain, void* out,
     RmsNormKernel<<<rows, 256, 0, st>>>(x, gain, static_cast<__nv_bfloat16*>(out), n, eps);
   }
   const cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? kOk : CudaFail("RMSNORM launch", e);
+  if (e != cudaSuccess) return CudaFail("RMSNORM launch", e);
+  CountLaunches(1);
+  return kOk;
 }
 
 extern "C" int tlaloc_b200_rope_kv_write(const float* q, const float* k, const float* v, const int32_t* positions,
@@ -221,7 +225,9 @@ extern "C" int tlaloc_b200_rope_kv_write(const float* q, const float* k, const f
   else TLALOC_LAUNCH(__nv_bfloat16, __nv_bfloat16);
 #undef TLALOC_LAUNCH
   const cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? kOk : CudaFail("ROPE_KV_WRITE launch", e);
+  if (e != cudaSuccess) return CudaFail("ROPE_KV_WRITE launch", e);
+  CountLaunches(1);
+  return kOk;
 }
 
 extern "C" int tlaloc_b200_swiglu(const float* gate, const float* up, int32_t ld, void* out, int32_t out_dtype,
@@ -240,7 +246,9 @@ extern "C" int tlaloc_b200_swiglu(const float* gate, const float* up, int32_t ld
     SwigluKernel<<<blocks, 256, 0, st>>>(gate, up, ld, static_cast<__nv_bfloat16*>(out), rows, n);
   }
   const cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? kOk : CudaFail("SWIGLU launch", e);
+  if (e != cudaSuccess) return CudaFail("SWIGLU launch", e);
+  CountLaunches(1);
+  return kOk;
 }
 
 extern "C" int tlaloc_b200_argmax(const float* logits, int32_t* out, int32_t rows, int32_t n, void* stream)
@@ -250,5 +258,7 @@ extern "C" int tlaloc_b200_argmax(const float* logits, int32_t* out, int32_t row
   if (rows == 0) return kOk;
   ArgmaxKernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(logits, out, n);
   const cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? kOk : CudaFail("ARGMAX launch", e);
+  if (e != cudaSuccess) return CudaFail("ARGMAX launch", e);
+  CountLaunches(1);
+  return kOk;
 }

@@ -8,6 +8,7 @@
 //   3. any stage but EXECUTE: nothing to do;
 //   4. EXECUTE: validate operands/results/attrs, take XLA's stream, enqueue on it; never allocate or synchronise.
 // Handlers are thread-safe: they keep no state beyond the once-only kernel set-up, which is mutex-guarded.
+#include <atomic>
 #include <cstring>
 #include <string>
 
@@ -21,6 +22,12 @@ char* ErrorBuffer()
   static thread_local char buf[kErrorBufferBytes] = {0};
   return buf;
 }
+
+namespace {
+std::atomic<long long> g_launches{0};
+}  // namespace
+
+void CountLaunches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 namespace {
 
@@ -269,6 +276,8 @@ using namespace tlaloc_b200;
 extern "C" int tlaloc_b200_abi_version(void) { return TLALOC_B200_ABI_VERSION; }
 
 extern "C" const char* tlaloc_b200_last_error(void) { return ErrorBuffer(); }
+
+extern "C" long long tlaloc_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int tlaloc_b200_init(void)
 {

@@ -402,6 +402,7 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
             ? LaunchExact<float, int8_t>(x, codes, scales, residual, y, y_dtype, m, k, n, round_x, st)
             : LaunchExact<__nv_bfloat16, int8_t>(x, codes, scales, residual, y, y_dtype, m, k, n, 0, st);
     if (e != cudaSuccess) return CudaFail("INT8_PROJ exact launch", e);
+    CountLaunches(1);
     return kOk;
   }
   e = PrepareInt8GemmKernels();
@@ -417,6 +418,7 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
                                                                             reinterpret_cast<__nv_bfloat16*>(scratch), count);
     e = cudaGetLastError();
     if (e != cudaSuccess) return CudaFail("INT8_PROJ activation cast", e);
+    CountLaunches(1);
     xb = reinterpret_cast<const __nv_bfloat16*>(scratch);
   }
   GemmParams p;
@@ -440,6 +442,7 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
       e = y_dtype == TLALOC_B200_F32 ? LaunchGemv<2, 2, float>(p, st) : LaunchGemv<2, 2, __nv_bfloat16>(p, st);
     }
     if (e != cudaSuccess) return CudaFail("INT8_PROJ launch", e);
+    CountLaunches(1);
   }
   return kOk;
 }
@@ -465,5 +468,6 @@ extern "C" int tlaloc_b200_dense_gemm_exact(const void* x, int32_t x_dtype, cons
     e = LaunchExact<__nv_bfloat16, __nv_bfloat16>(x, w, nullptr, nullptr, y, TLALOC_B200_F32, m, k, n, 0, st);
   }
   if (e != cudaSuccess) return CudaFail("MATMUL exact launch", e);
+  CountLaunches(1);
   return kOk;
 }

@@ -788,6 +788,7 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return CudaFail("PAGED_ATTENTION combine launch", e);
+  CountLaunches(2);
   return kOk;
 }
 
@@ -820,5 +821,6 @@ extern "C" int tlaloc_b200_kv_cache_write(void* pool, int32_t pool_dtype, const 
   }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return CudaFail("KV_CACHE_WRITE launch", e);
+  CountLaunches(1);
   return kOk;
 }

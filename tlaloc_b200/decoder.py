@@ -1,0 +1,246 @@
+"""The Llama-style decode step on one B200, or tensor-parallel over the B200s of one box.
+
+What the step computes is the reference's decode graph (ir/.../inference/HfDecoderGraph.kt: embed :904-909;
+per layer rmsNorm :663-699 -> q/k/v proj :1183-1213 -> rope :792-818 -> KV_CACHE_WRITE x2 :1230-1231 ->
+PAGED_ATTENTION :1233-1253 -> o proj + residual :1266-1273 -> rmsNorm -> SiLU(gate)*up :979-988 -> down proj +
+residual :1002-1009; then the final norm and head :2121-2128; greedy next token = first maximum).  Every
+operator is one call through the C ABI of libtlaloc_kernels.so; PyTorch only owns device memory, the stream, the
+CUDA graph and (for tensor parallelism) the NCCL communicator.  There is no CPU path.
+
+Per layer the step launches: rmsnorm, fused q|k|v projection, rope + KV write, attention slice + combine,
+o projection (+ residual), rmsnorm, fused gate|up projection, swiglu, down projection (+ residual); with
+tensor parallelism an all-reduce follows the o and down projections.  The whole step is captured once into a
+CUDA graph and replayed.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import ops, sharding
+
+
+@dataclass
+class DecoderConfig:
+    num_layers: int
+    d_model: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    ffn: int
+    vocab: int
+    rms_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    block_size: int = 16
+    kv_dtype: torch.dtype = torch.bfloat16
+    head_quant: bool = True
+    max_positions: int = 8192
+
+    @property
+    def scale(self) -> float:
+        # HfDecoderGraph.kt:546: 1f / sqrt(hd.toFloat()), widened
+        return float(np.float32(1.0) / np.sqrt(np.float32(self.head_dim)))
+
+
+LLAMA3_8B = dict(num_layers=32, d_model=4096, num_heads=32, num_kv_heads=8, head_dim=128, ffn=14336, vocab=128256)
+LLAMA3_70B = dict(num_layers=80, d_model=8192, num_heads=64, num_kv_heads=8, head_dim=128, ffn=28672, vocab=128256)
+TINY = dict(num_layers=2, d_model=256, num_heads=4, num_kv_heads=2, head_dim=64, ffn=688, vocab=1024)
+
+
+def rope_tables(theta: float, head_dim: int, positions: int):
+    """HfDecoderGraph.ropeTables (:436-462): computed in double, narrowed to f32, both halves equal."""
+    half = head_dim // 2
+    inv = np.power(float(theta), -2.0 * np.arange(half, dtype=np.float64) / head_dim)
+    ang = np.arange(positions, dtype=np.float64)[:, None] * inv[None, :]
+    cos = np.concatenate([np.cos(ang), np.cos(ang)], axis=1).astype(np.float32)
+    sin = np.concatenate([np.sin(ang), np.sin(ang)], axis=1).astype(np.float32)
+    return cos, sin
+
+
+class Decoder:
+    """Weights, KV pools and step buffers of one rank; `step()` runs one decode step for `batch` sequences."""
+
+    def __init__(self, cfg: DecoderConfig, batch: int, num_blocks: int, max_blocks_per_seq: int, *, device="cuda:0",
+                 rank: int = 0, world: int = 1, group=None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("tlaloc_b200.Decoder needs a CUDA device: there is no CPU path")
+        sharding.check_world(cfg.num_heads, cfg.num_kv_heads, cfg.ffn, cfg.vocab, world)
+        self.cfg, self.batch, self.device, self.rank, self.world, self.group = cfg, batch, torch.device(device), rank, world, group
+        self.hq, self.hk, self.f = cfg.num_heads // world, cfg.num_kv_heads // world, cfg.ffn // world
+        self.num_blocks, self.max_blocks = num_blocks, max_blocks_per_seq
+        dev, B, d, hd = self.device, batch, cfg.d_model, cfg.head_dim
+        ops.init()
+        self.layers: list[dict] = []
+        self.embed = self.final_norm = self.head = None
+        self.key_pools = [torch.zeros((num_blocks, cfg.block_size, self.hk, hd), dtype=cfg.kv_dtype, device=dev)
+                          for _ in range(cfg.num_layers)]
+        self.value_pools = [torch.zeros_like(p) for p in self.key_pools]
+        cos, sin = rope_tables(cfg.rope_theta, hd, cfg.max_positions)
+        self.cos, self.sin = torch.from_numpy(cos).to(dev), torch.from_numpy(sin).to(dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        # step inputs (static addresses: the CUDA graph reads them)
+        self.token_ids = torch.zeros((B,), **i32)
+        self.positions = torch.zeros((B,), **i32)
+        self.block_tables = torch.zeros((B, max_blocks_per_seq), **i32)
+        self.seq_lens = torch.ones((B,), **i32)
+        self.slot_mapping = torch.full((B,), -1, **i32)
+        # step buffers
+        nqkv = (self.hq + 2 * self.hk) * hd
+        self.h = torch.empty((B, d), **f32)
+        self.h2 = torch.empty((B, d), **f32)
+        self.hn = torch.empty((B, d), **bf)
+        self.qkv = torch.empty((B, nqkv), **f32)
+        self.q_rot = torch.empty((B, self.hq, hd), **f32)
+        self.att = torch.empty((B, self.hq, hd), **bf)
+        self.gu = torch.empty((B, 2 * self.f), **f32)
+        self.act = torch.empty((B, self.f), **bf)
+        self.logits = torch.empty((B, cfg.vocab // world), **f32)
+        self.next_ids = torch.zeros((B,), **i32)
+        self.best = torch.empty((B,), **f32)
+        shape = ops.parse_paged_attention(self.q_rot, self.key_pools[0], self.value_pools[0], self.block_tables,
+                                          self.seq_lens, scale=cfg.scale)
+        self.att_scratch = ops.paged_attention_scratch(shape, dev)
+        self._graph = None
+
+    # ------------------------------------------------------------------ weights
+
+    def load_host_weights(self, w) -> None:
+        """Weights in the reference's staged layout (`oracle.DecoderWeights`-shaped: int8 codes [in, out] + f32
+        scales [out] per projection, embedding/head values, norm gains), sharded for this rank."""
+        cfg, dev = self.cfg, self.device
+        t = lambda a, dt=None: (torch.from_numpy(np.ascontiguousarray(a)).to(dev) if dt is None
+                                else torch.from_numpy(np.ascontiguousarray(a)).to(dev).to(dt))
+        self.embed = t(w.embed, torch.bfloat16)
+        self.final_norm = t(w.final_norm)
+        self.layers = []
+        for lw in w.layers:
+            s = sharding.shard_layer(lw, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.ffn, self.rank, self.world)
+            self.layers.append({k: (tuple(t(x) for x in v) if isinstance(v, tuple) else t(v)) for k, v in s.items()})
+        head = sharding.shard_head(w.head, cfg.vocab, self.rank, self.world)
+        self.head = tuple(t(x) for x in head) if isinstance(head, tuple) else t(head, torch.bfloat16)
+
+    def init_random_weights(self, seed: int = 0) -> None:
+        """Random int8 codes (uniform in [-127, 127]) and scales on the device, for throughput runs at sizes whose
+        weights would not fit through host memory.  Scales are sized so activations stay O(1) through the layers."""
+        cfg, dev = self.cfg, self.device
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed * 1000 + self.rank)
+        d, hd = cfg.d_model, cfg.head_dim
+
+        def lin(k, n):
+            codes = torch.randint(-127, 128, (k, n), dtype=torch.int8, device=dev, generator=g)
+            scales = torch.empty((n,), dtype=torch.float32, device=dev).uniform_(0.5, 1.5, generator=g) / (73.0 * np.sqrt(k))
+            return codes, scales
+
+        self.embed = (torch.randn((cfg.vocab, d), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        self.final_norm = torch.ones((d,), dtype=torch.float32, device=dev)
+        self.layers = []
+        for _ in range(cfg.num_layers):
+            self.layers.append({
+                "qkv": lin(d, (self.hq + 2 * self.hk) * hd), "o": lin(self.hq * hd, d),
+                "gate_up": lin(d, 2 * self.f), "down": lin(self.f, d),
+                "ln1": torch.ones((d,), dtype=torch.float32, device=dev),
+                "ln2": torch.ones((d,), dtype=torch.float32, device=dev),
+            })
+        self.head = lin(d, cfg.vocab // self.world)
+
+    def weight_bytes(self) -> int:
+        n = 0
+        for lw in self.layers:
+            for key in ("qkv", "o", "gate_up", "down"):
+                n += lw[key][0].numel() + 4 * lw[key][1].numel()
+        n += (self.head[0].numel() + 4 * self.head[1].numel()) if isinstance(self.head, tuple) else 2 * self.head.numel()
+        return n
+
+    # ------------------------------------------------------------------ the step
+
+    def set_inputs(self, token_ids, positions, block_tables, seq_lens, slot_mapping) -> None:
+        """Host (NumPy or pinned torch) step inputs -> the device buffers the graph reads."""
+        for dst, src in ((self.token_ids, token_ids), (self.positions, positions), (self.block_tables, block_tables),
+                         (self.seq_lens, seq_lens), (self.slot_mapping, slot_mapping)):
+            if src is None:
+                continue
+            if isinstance(src, np.ndarray):
+                src = torch.from_numpy(np.ascontiguousarray(src, dtype=np.int32))
+            dst.copy_(src.reshape(dst.shape), non_blocking=True)
+
+    def _all_reduce(self, x: torch.Tensor) -> None:
+        if self.world > 1:
+            torch.distributed.all_reduce(x, group=self.group)
+
+    def _run_step(self) -> None:
+        cfg, B = self.cfg, self.batch
+        hd, hq, hk = cfg.head_dim, self.hq, self.hk
+        ops.embedding(self.embed, self.token_ids, out=self.h)
+        h, h2 = self.h, self.h2
+        res_rank = self.rank == 0  # under tensor parallelism the residual enters the all-reduced sum once
+        q3 = self.qkv[:, :hq * hd].unflatten(1, (hq, hd))
+        k3 = self.qkv[:, hq * hd:(hq + hk) * hd].unflatten(1, (hk, hd))
+        v3 = self.qkv[:, (hq + hk) * hd:].unflatten(1, (hk, hd))
+        for l, lw in enumerate(self.layers):
+            ops.rmsnorm(h, lw["ln1"], cfg.rms_eps, out=self.hn)
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv)
+            ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
+                              self.value_pools[l], q_out=self.q_rot)
+            ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
+                                scale=cfg.scale, out=self.att, scratch=self.att_scratch)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2)
+            self._all_reduce(h2)
+            ops.rmsnorm(h2, lw["ln2"], cfg.rms_eps, out=self.hn)
+            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu)
+            ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
+            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h)
+            self._all_reduce(h)
+        ops.rmsnorm(h, self.final_norm, cfg.rms_eps, out=self.hn)
+        if isinstance(self.head, tuple):
+            ops.int8_gemm(self.hn, *self.head, out=self.logits)
+        else:
+            self.logits.copy_(ops.dense_gemm_exact(self.hn, self.head))
+        ops.argmax(self.logits, out=self.next_ids)
+        if self.world > 1:
+            self._merge_greedy()
+
+    def _merge_greedy(self) -> None:
+        """Each rank's best (logit, local id) -> the global greedy token on every rank (sharding.merge_greedy)."""
+        B, g, vp = self.batch, self.world, self.cfg.vocab // self.world
+        best = self.logits.gather(1, self.next_ids.long()[:, None])[:, 0].contiguous()
+        vals = torch.empty((g, B), dtype=torch.float32, device=self.device)
+        ids = torch.empty((g, B), dtype=torch.int32, device=self.device)
+        torch.distributed.all_gather_into_tensor(vals, best, group=self.group)
+        torch.distributed.all_gather_into_tensor(ids, self.next_ids, group=self.group)
+        # the largest value; among equals the lowest rank, whose ids are the lowest: argmax returns the first maximum
+        win = vals.argmax(dim=0)
+        glob = ids.long() + (torch.arange(g, device=self.device) * vp)[:, None]
+        self.next_ids.copy_(glob.gather(0, win[None, :])[0].to(torch.int32))
+
+    def capture(self) -> None:
+        """Capture the step into a CUDA graph (after one eager warm-up step on a side stream)."""
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self._run_step()
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._run_step()
+
+    def step(self) -> torch.Tensor:
+        """One decode step over the current inputs; returns the device tensor of next token ids [batch]."""
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self._run_step()
+        return self.next_ids
+
+    # ------------------------------------------------------------------ traffic model
+
+    def step_bytes(self, seq_lens: np.ndarray) -> dict:
+        """Algorithmic HBM bytes of one step on this rank: every weight byte once, every live K/V element once."""
+        cfg = self.cfg
+        kv = 2 * int(np.sum(seq_lens)) * self.hk * cfg.head_dim * self.key_pools[0].element_size() * cfg.num_layers
+        return {"weights": self.weight_bytes(), "kv": kv}

@@ -111,10 +111,11 @@ def dense_gemm_exact(x, w, *, x_f32_exact=False):
     return out
 
 
-def embedding(table, ids):
+def embedding(table, ids, *, out=None):
     _dev(table, ids)
     ids = ids.reshape(-1)
-    out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+    if out is None:
+        out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
     N.check(N.lib().tlaloc_b200_embedding(_ptr(table), _dt(table), _ptr(ids), _ptr(out), ids.shape[0], table.shape[0],
                                           table.shape[1], _stream()))
     return out

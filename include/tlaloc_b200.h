@@ -106,6 +106,35 @@ int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, const void* 
                                 void* stream);
 
 /*
+ * The same operator for callers that cannot allocate device memory: a handler running inside a CUDA graph
+ * capture, an XLA program whose emitter declared no scratch result for the call, or a host runtime (a JVM
+ * binding, a plugin) that is handed device pointers but owns no allocator.  It takes no scratch: the split
+ * records go to a 16 MiB array built into the library (tlaloc_b200_paged_attention_static_scratch_bytes()),
+ * which every GPU that loads the library holds until the process exits.  This entry point has no counterpart
+ * in the reference, whose kernel always receives an XLA-owned scratch result.
+ *
+ *  - It calls no cudaMalloc, cudaFree or other allocating routine.
+ *  - Limit: the records of ceil(M*bs / 8192) slices, num_rows * num_heads * (head_dim + 2) floats each, must fit
+ *    the array; a larger call is refused with TLALOC_B200_INVALID_ARGUMENT and a message giving both sizes.
+ *    Within the limit it uses as many slices as fit (at most ceil(M*bs / 256)).
+ *  - The first call on each device looks up the array's device address (with that device current); make that
+ *    first call before any stream capture begins.
+ *  - All calls on a device share the one array.  Nothing in it needs clearing between calls (every record that
+ *    is read was written by the same call), but two calls whose kernels overlap on the GPU (different streams,
+ *    or threads launching concurrently) race on it: serialise them, or give them their own scratch through
+ *    tlaloc_b200_paged_attention.
+ * All other arguments are those of tlaloc_b200_paged_attention.
+ */
+size_t tlaloc_b200_paged_attention_static_scratch_bytes(void);
+int tlaloc_b200_paged_attention_static(const void* query, int32_t q_dtype, const void* key_cache,
+                                       const void* value_cache, int32_t kv_dtype, const int32_t* block_tables,
+                                       const int32_t* seq_lens, const int32_t* keep, int32_t keep_chunks, void* out,
+                                       int32_t out_dtype, float* lse, int32_t num_rows, int32_t num_heads,
+                                       int32_t head_dim, int32_t num_blocks, int32_t block_size, int32_t num_kv_heads,
+                                       int32_t max_blocks_per_seq, int32_t num_tables, float scale,
+                                       int32_t sliding_window, void* stream);
+
+/*
  * KV_CACHE_WRITE (ir/.../KvCacheWriteAttrs.kt:62-159, interpreter
  * DxirInterpreter.kt:2233-2272; XLA scatter form stablehlo/.../StablehloEmitter.kt:4634):
  * row i of new_kv [T, Hkv*D] goes to pool slot slot_mapping[i]; a negative slot

@@ -28,6 +28,10 @@ _SIGNATURES = {
     "tlaloc_b200_paged_attention": (ctypes.c_int, [_vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
                                                    _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _i32,
                                                    _vp]),
+    "tlaloc_b200_paged_attention_static_scratch_bytes": (_sz, []),
+    "tlaloc_b200_paged_attention_static": (ctypes.c_int, [_vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp,
+                                                          _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _i32,
+                                                          _vp]),
     "tlaloc_b200_kv_cache_write": (ctypes.c_int, [_vp, _i32, _vp, _i32, _vp, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_int8_gemm_scratch_bytes": (_sz, [_i32] * 3),
     "tlaloc_b200_int8_gemm": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _sz, _i32, _i32, _i32, _i32, _vp]),

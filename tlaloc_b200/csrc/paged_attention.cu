@@ -824,3 +824,77 @@ extern "C" int tlaloc_b200_kv_cache_write(void* pool, int32_t pool_dtype, const 
   CountLaunches(1);
   return kOk;
 }
+
+// ------------------------------------------------------------------------------------------
+// Paged attention for callers that cannot allocate device memory.
+//
+// The split records live in one fixed array inside this library instead of a caller's buffer.  The array is a
+// device symbol: in host code its name only stands for it, so the address the kernels receive is looked up with
+// cudaGetSymbolAddress, once per device, with that device current.
+
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;  // 16 MiB on every GPU that loads the library, until exit
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+float* g_static_ptr[kMaxDevices] = {nullptr};
+
+// The device address of g_static_scratch on the current device (resolved on the first call per device).
+cudaError_t StaticScratch(float** out)
+{
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return e;
+  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[device] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    if (e != cudaSuccess) return e;
+    g_static_ptr[device] = ptr;
+  }
+  *out = g_static_ptr[device];
+  return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" size_t tlaloc_b200_paged_attention_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int tlaloc_b200_paged_attention_static(const void* query, int32_t q_dtype, const void* key_cache,
+                                                  const void* value_cache, int32_t kv_dtype,
+                                                  const int32_t* block_tables, const int32_t* seq_lens,
+                                                  const int32_t* keep, int32_t keep_chunks, void* out,
+                                                  int32_t out_dtype, float* lse, int32_t num_rows, int32_t num_heads,
+                                                  int32_t head_dim, int32_t num_blocks, int32_t block_size,
+                                                  int32_t num_kv_heads, int32_t max_blocks_per_seq,
+                                                  int32_t num_tables, float scale, int32_t sliding_window,
+                                                  void* stream)
+{
+  const char* op = "PAGED_ATTENTION (static scratch)";
+  if (num_rows < 1 || num_heads < 1 || head_dim < 1 || block_size < 1 || max_blocks_per_seq < 1) {
+    return Fail(kInvalid, "%s: needs positive query and table dims", op);
+  }
+  const int64_t ctx = static_cast<int64_t>(max_blocks_per_seq) * block_size;
+  const size_t record_set = sizeof(float) * static_cast<size_t>(num_rows) * num_heads * (head_dim + 2);  // one slice
+  const int64_t fit = static_cast<int64_t>(kStaticScratchBytes / record_set);
+  const int64_t least = (ctx + 8191) / 8192;  // the longest slice a launch takes is 8192 positions
+  if (fit < 1 || fit < least) {
+    return Fail(kInvalid,
+                "%s: %d rows x %d heads x head_dim %d over %lld positions needs %zu bytes of split records, more than "
+                "the %zu-byte array built into the library; use tlaloc_b200_paged_attention with your own scratch",
+                op, num_rows, num_heads, head_dim, (long long)ctx, record_set * static_cast<size_t>(least),
+                kStaticScratchBytes);
+  }
+  const int64_t want = (ctx + 255) / 256;
+  const int32_t splits = static_cast<int32_t>(std::min(fit, want));
+  float* scratch = nullptr;
+  const cudaError_t e = StaticScratch(&scratch);
+  if (e != cudaSuccess) return CudaFail("PAGED_ATTENTION (static scratch) set-up", e);
+  return tlaloc_b200_paged_attention(query, q_dtype, key_cache, value_cache, kv_dtype, block_tables, seq_lens, keep,
+                                     keep_chunks, out, out_dtype, lse, scratch, splits, num_rows, num_heads, head_dim,
+                                     num_blocks, block_size, num_kv_heads, max_blocks_per_seq, num_tables, scale,
+                                     sliding_window, stream);
+}

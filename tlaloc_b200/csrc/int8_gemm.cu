@@ -2,16 +2,18 @@
 // (HfDecoderGraph.proj over WeightQuant.INT8, ir/.../inference/HfDecoderGraph.kt:625-655).
 //
 //   Int8GemvKernel   decode rows (M <= 32 per launch; more rows run as several launches).  HBM-bound: every
-//                    weight byte is read once, straight from global memory into registers with 16-byte
-//                    coalesced loads of the reference's own [K, N] layout (no repacking).  A CTA owns 128
-//                    output columns and one slice of K; its eight warps split the slice's 16-row steps.  The
-//                    int8 codes become exact bf16 pairs in registers (one byte-permute, two logic ops and one
-//                    packed bf16 add per pair), the activations wait in shared memory as bf16 (double-buffered
-//                    cp.async chunks), and the products run on mma.sync m16n8k16 bf16 with fp32 accumulators.
-//                    The K slices of one column tile form a thread-block cluster and are summed through
-//                    distributed shared memory in rank order, so there is no global scratch, no second
-//                    kernel, and the result does not depend on timing.  The per-column scale (and an optional
-//                    residual) is applied to the finished sum, as the graph multiplies after the dot.
+//                    weight byte is read once, from the reference's own [K, N] layout (no repacking).  A CTA owns
+//                    128 output columns and one slice of K; each of its four warps is an independent cp.async
+//                    pipeline over its own 32-row stages (a 32 x 128 int8 weight tile plus the matching 32-wide
+//                    strip of the bf16 activations, XOR-swizzled in shared memory), so there is no CTA-wide barrier
+//                    in the loop and four CTAs fit an SM.  The MMA runs transposed: the 16 output columns a lane
+//                    pair-set owns are the M dimension and the (<= 8 per n-tile) activation rows the N dimension, so
+//                    one 16-row step costs 8 mma.sync m16n8k16 per n-tile.  The int8 codes become exact bf16 pairs in
+//                    registers (one byte-permute, two logic ops and one packed bf16 add per pair); products are
+//                    exact, accumulation fp32.  The K slices of one column tile form a thread-block cluster and are
+//                    summed through distributed shared memory in rank order: no global scratch, no second kernel,
+//                    and a result that does not depend on timing.  The per-column scale (and an optional residual)
+//                    is applied to the finished sum, as the graph multiplies after the dot.
 //   GemmExactKernel  the interpreter's MATMUL order (DxirInterpreter.kt:739-765): f32, k ascending, separate
 //                    multiply and add, zero activations skipped.  Bit-identical to the CPU oracle; slow.
 #include <cooperative_groups.h>
@@ -32,15 +34,16 @@ struct GemmParams {
   const float* residual;   // [M, N] or null
   void* y;                 // [M, N]
   int M, K, N;
-  int Kc;  // K per CTA (multiple of 16 * kGvWarps)
+  int Kc;  // K per CTA (a multiple of kGvStageK * kGvWarps)
   int ks;  // K slices (cluster size along y)
 };
 
-constexpr int kGvThreads = 256;
-constexpr int kGvWarps = 8;
+constexpr int kGvThreads = 128;
+constexpr int kGvWarps = 4;
 constexpr int kGvCols = 128;
-constexpr int kGvChunk = 1024;            // k per activation chunk in shared memory
-constexpr int kGvXStride = kGvChunk + 8;  // bf16 elements per staged row (16 bytes of padding: conflict-free ldmatrix)
+constexpr int kGvStageK = 32;  // k rows per pipeline stage
+constexpr int kGvStages = 3;
+constexpr int kGvWBytes = kGvStageK * kGvCols;  // the stage's weight tile
 constexpr int kGvRedStride = kGvCols + 4;
 
 __device__ __forceinline__ uint32_t SmemAddr(const void* ptr)
@@ -57,11 +60,15 @@ __device__ __forceinline__ void CpAsyncWait()
 {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
-__device__ __forceinline__ void LdMatrixX4(uint32_t (&r)[4], uint32_t addr)
+__device__ __forceinline__ void LdMatrixX2(uint32_t (&r)[2], uint32_t addr)
 {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ uint4 LdShared16(uint32_t addr)
+{
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
 }
 __device__ __forceinline__ void MmaBf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
 {
@@ -70,16 +77,7 @@ __device__ __forceinline__ void MmaBf16(float (&c)[4], const uint32_t (&a)[4], u
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// Streaming 16-byte load of weights: read once, kept out of L1.
-__device__ __forceinline__ uint4 LoadW(const int8_t* ptr)
-{
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(ptr));
-  return v;
-}
-// Bytes `b` of two words (codes of two consecutive k for one column) as an exact bf16 pair, lower k in the low
+// Bytes `B` of two words (codes of two consecutive k for one column) as an exact bf16 pair, lower k in the low
 // half.  For a code v with bits s:lo7, 0x4300|lo7 is the bf16 128 + lo7 and 0xC300|s<<7 is -128 or -256; their
 // sum is v, exactly.
 template <int B>
@@ -93,148 +91,133 @@ __device__ __forceinline__ uint32_t CodesToBf16x2(uint32_t w_lo_k, uint32_t w_hi
   return r;
 }
 
-template <int MT>
+template <int NT>
 struct GvLayout {
-  static constexpr int kRows = MT * 16;
-  static constexpr int kXBytes = kRows * kGvXStride * 2;  // one activation chunk
-  static constexpr int kRedBytes = kGvWarps * kRows * kGvRedStride * 4;
+  static constexpr int kRows = NT * 8;                     // activation rows a launch covers
+  static constexpr int kXBytes = kRows * kGvStageK * 2;    // the stage's activation strip, [rows][32] bf16
+  static constexpr int kStageBytes = kGvWBytes + kXBytes;
+  static constexpr int kWarpBytes = kGvStages * kStageBytes;
+  static constexpr int kPipeBytes = kGvWarps * kWarpBytes;
+  // After the loop the same space holds the four warps' partial tiles and the CTA's summed tile.
   static constexpr int kTileBytes = kRows * kGvRedStride * 4;
-  // The two activation buffers and the warps' partial tiles share one space (the partials come last).
-  static constexpr int kMainBytes = 2 * kXBytes > kRedBytes ? 2 * kXBytes : kRedBytes;
-  static constexpr int kBytes = kMainBytes + kTileBytes;
+  static constexpr int kRedBytes = (kGvWarps + 1) * kTileBytes;
+  static constexpr int kBytes = kPipeBytes > kRedBytes ? kPipeBytes : kRedBytes;
 };
 
-template <int MT, int U, typename YT>
-__global__ void __launch_bounds__(kGvThreads, 1) Int8GemvKernel(GemmParams p)
+template <int NT, typename YT>
+__global__ void __launch_bounds__(kGvThreads) Int8GemvKernel(GemmParams p)
 {
-  using L = GvLayout<MT>;
+  using L = GvLayout<NT>;
   extern __shared__ __align__(128) unsigned char smem[];
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);  // [2][kRows][kGvXStride]
-  float* red = reinterpret_cast<float*>(smem);                 // [kGvWarps][kRows][kGvRedStride] (after the loop)
-  float* tile = reinterpret_cast<float*>(smem + L::kMainBytes);  // [kRows][kGvRedStride]
-
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gid = lane >> 2, tig = lane & 3;
   const int col0 = blockIdx.x * kGvCols;
   const int kb = blockIdx.y * p.Kc;
   const int ke = min(p.K, kb + p.Kc);
-  const int nsteps = ke > kb ? (ke - kb + 15) >> 4 : 0;          // this CTA's 16-row steps
-  const int nchunks = (nsteps * 16 + kGvChunk - 1) / kGvChunk;    // activation chunks
-  constexpr int kStepsPerWarpChunk = kGvChunk / 16 / kGvWarps;    // 8
-  constexpr int kGroupsPerChunk = kStepsPerWarpChunk / U;
-  const int my_col = col0 + gid * 16;
-  const bool col_ok = my_col < p.N;
+  const int nstages = ke > kb ? (ke - kb + kGvStageK - 1) / kGvStageK : 0;
+  const int my_n = warp < nstages ? (nstages - warp + kGvWarps - 1) / kGvWarps : 0;
+  unsigned char* my_pipe = smem + warp * L::kWarpBytes;
+  const uint32_t my_pipe_addr = SmemAddr(my_pipe);
 
-  // Activation chunk c -> buffer c & 1: rows m < M copy 16-byte pieces of x[m, kb + c*chunk ...), the rest zero.
-  auto stage_x = [&](int c) {
-    __nv_bfloat16* dst = xs + (c & 1) * (L::kRows * kGvXStride);
-    const int k_lo = kb + c * kGvChunk;
-    for (int idx = tid; idx < L::kRows * (kGvChunk / 8); idx += kGvThreads) {
-      const int m = idx / (kGvChunk / 8), piece = idx - m * (kGvChunk / 8);
-      const int k = k_lo + piece * 8;
-      // K is a multiple of 8 on this path, so a piece is wholly inside or outside [0, K).
-      const bool valid = m < p.M && k < ke;
-      const __nv_bfloat16* src = p.x + (valid ? static_cast<size_t>(m) * p.K + k : 0);
-      CpAsync16(SmemAddr(dst + m * kGvXStride + piece * 8), src, valid ? 16 : 0);
+  // Stage `it` of this warp: k rows [k0, k0 + 32).  Weight row r's 16-byte chunk c lands at chunk c ^ (r & 6), the
+  // activation row m's chunk c at c ^ ((m >> 1) & 3), so the reads below are conflict-free.  K is a multiple of 8
+  // and N of 16 on this path, so a chunk is wholly inside or outside the matrix; outside is zero-filled.
+  auto issue = [&](int it) {
+    const int k0 = kb + (warp + kGvWarps * it) * kGvStageK;
+    const uint32_t dst = my_pipe_addr + (it % kGvStages) * L::kStageBytes;
+#pragma unroll
+    for (int i = 0; i < kGvWBytes / 16 / 32; ++i) {
+      const int c = lane + 32 * i;
+      const int r = c >> 3, ch = c & 7;
+      const bool valid = k0 + r < ke && col0 + ch * 16 < p.N;
+      const int8_t* src = p.w + (valid ? static_cast<size_t>(k0 + r) * p.N + col0 + ch * 16 : 0);
+      CpAsync16(dst + r * kGvCols + ((ch ^ (r & 6)) << 4), src, valid ? 16 : 0);
+    }
+#pragma unroll
+    for (int i = 0; i < L::kXBytes / 16 / 32; ++i) {
+      const int c = lane + 32 * i;
+      const int m = c >> 2, piece = c & 3;
+      const bool valid = m < p.M && k0 + piece * 8 < ke;
+      const __nv_bfloat16* src = p.x + (valid ? static_cast<size_t>(m) * p.K + k0 + piece * 8 : 0);
+      CpAsync16(dst + kGvWBytes + m * (kGvStageK * 2) + ((piece ^ ((m >> 1) & 3)) << 4), src, valid ? 16 : 0);
     }
   };
-  // The weights of step j (16 rows of K) for this lane: rows 2*tig + {0, 1, 8, 9}, 16 columns from my_col.
-  auto load_w = [&](int j, uint4 (&r)[4]) {
-    const int k0 = kb + 16 * j + 2 * tig;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int row = k0 + (q & 1) + (q >> 1) * 8;
-      if (j < nsteps && row < ke && col_ok) r[q] = LoadW(p.w + static_cast<size_t>(row) * p.N + my_col);
-      else r[q] = make_uint4(0u, 0u, 0u, 0u);
-    }
-  };
 
-  float acc[MT][16][4];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-    for (int nt = 0; nt < 16; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.f;
+  for (int it = 0; it < kGvStages - 1; ++it) {
+    if (it < my_n) issue(it);
+    CpAsyncCommit();
+  }
 
-  auto compute = [&](int j, const uint4 (&r)[4], const __nv_bfloat16* xbuf) {
-    if (j >= nsteps) return;
-    const int kl = (16 * j) % kGvChunk;  // step's first k inside its chunk
-    uint32_t a[MT][4];
+  // acc[j][nt]: output columns col0 + gid*16 + 2j (c0, c1) and + 2j + 1 (c2, c3), activation rows nt*8 + 2tig, + 1.
+  float acc[8][NT][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      const int row = mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-      LdMatrixX4(a[mt], SmemAddr(xbuf + row * kGvXStride + kl + (lane >> 4) * 8));
-    }
-    const uint32_t wa[4] = {r[0].x, r[0].y, r[0].z, r[0].w}, wb[4] = {r[1].x, r[1].y, r[1].z, r[1].w};
-    const uint32_t wc[4] = {r[2].x, r[2].y, r[2].z, r[2].w}, wd[4] = {r[3].x, r[3].y, r[3].z, r[3].w};
+  for (int j = 0; j < 8; ++j)
 #pragma unroll
-    for (int wi = 0; wi < 4; ++wi) {
-      uint32_t b0[4], b1[4];
-      b0[0] = CodesToBf16x2<0>(wa[wi], wb[wi]);
-      b0[1] = CodesToBf16x2<1>(wa[wi], wb[wi]);
-      b0[2] = CodesToBf16x2<2>(wa[wi], wb[wi]);
-      b0[3] = CodesToBf16x2<3>(wa[wi], wb[wi]);
-      b1[0] = CodesToBf16x2<0>(wc[wi], wd[wi]);
-      b1[1] = CodesToBf16x2<1>(wc[wi], wd[wi]);
-      b1[2] = CodesToBf16x2<2>(wc[wi], wd[wi]);
-      b1[3] = CodesToBf16x2<3>(wc[wi], wd[wi]);
+    for (int nt = 0; nt < NT; ++nt) acc[j][nt][0] = acc[j][nt][1] = acc[j][nt][2] = acc[j][nt][3] = 0.f;
+
+  for (int it = 0; it < my_n; ++it) {
+    if (it + kGvStages - 1 < my_n) issue(it + kGvStages - 1);
+    CpAsyncCommit();
+    CpAsyncWait<kGvStages - 1>();
+    __syncwarp();
+    const uint32_t w_addr = my_pipe_addr + (it % kGvStages) * L::kStageBytes;
+    const uint32_t x_addr = w_addr + kGvWBytes;
 #pragma unroll
-      for (int bi = 0; bi < 4; ++bi) {
+    for (int h = 0; h < kGvStageK / 16; ++h) {
+      // x^T as B fragments: b0b1 = x[row gid][16h + 2tig, +1], b2b3 = x[row gid][16h + 8 + 2tig, +1].
+      uint32_t b[NT][2];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) MmaBf16(acc[mt][wi * 4 + bi], a[mt], b0[bi], b1[bi]);
+      for (int nt = 0; nt < NT; ++nt) {
+        const int m = nt * 8 + (lane & 7), piece = 2 * h + ((lane >> 3) & 1);
+        LdMatrixX2(b[nt], x_addr + m * (kGvStageK * 2) + ((piece ^ ((m >> 1) & 3)) << 4));
+      }
+      // This lane's 16 columns of rows 16h + 2tig + {0, 1, 8, 9}.
+      uint4 r[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int row = 16 * h + 2 * tig + (q & 1) + (q >> 1) * 8;
+        r[q] = LdShared16(w_addr + row * kGvCols + ((gid ^ (row & 6)) << 4));
+      }
+      const uint32_t wa[4] = {r[0].x, r[0].y, r[0].z, r[0].w}, wb[4] = {r[1].x, r[1].y, r[1].z, r[1].w};
+      const uint32_t wc[4] = {r[2].x, r[2].y, r[2].z, r[2].w}, wd[4] = {r[3].x, r[3].y, r[3].z, r[3].w};
+#pragma unroll
+      for (int wi = 0; wi < 4; ++wi) {
+        // Bytes 0, 1 of word wi are columns 4wi, 4wi + 1 (MMA j = 2wi); bytes 2, 3 are MMA j = 2wi + 1.
+        uint32_t a0[4], a1[4];
+        a0[0] = CodesToBf16x2<0>(wa[wi], wb[wi]);
+        a0[1] = CodesToBf16x2<1>(wa[wi], wb[wi]);
+        a0[2] = CodesToBf16x2<0>(wc[wi], wd[wi]);
+        a0[3] = CodesToBf16x2<1>(wc[wi], wd[wi]);
+        a1[0] = CodesToBf16x2<2>(wa[wi], wb[wi]);
+        a1[1] = CodesToBf16x2<3>(wa[wi], wb[wi]);
+        a1[2] = CodesToBf16x2<2>(wc[wi], wd[wi]);
+        a1[3] = CodesToBf16x2<3>(wc[wi], wd[wi]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          MmaBf16(acc[2 * wi][nt], a0, b[nt][0], b[nt][1]);
+          MmaBf16(acc[2 * wi + 1][nt], a1, b[nt][0], b[nt][1]);
+        }
       }
     }
-  };
-
-  // Warp `warp` takes steps warp, warp + 8, ...; U of them form a group whose weights are loaded together,
-  // one group ahead of the one being multiplied.
-  uint4 wcur[U][4], wnxt[U][4];
-  auto load_group = [&](int g, uint4 (&buf)[U][4]) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) load_w(warp + kGvWarps * (g * U + u), buf[u]);
-  };
-  auto compute_group = [&](int g, const uint4 (&buf)[U][4], const __nv_bfloat16* xbuf) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) compute(warp + kGvWarps * (g * U + u), buf[u], xbuf);
-  };
-
-  if (nchunks > 0) {
-    stage_x(0);
-    CpAsyncCommit();
-    load_group(0, wcur);
-  }
-  for (int c = 0; c < nchunks; ++c) {
-    if (c + 1 < nchunks) stage_x(c + 1);
-    CpAsyncCommit();
-    CpAsyncWait<1>();
-    __syncthreads();  // chunk c is in shared memory for every warp
-    const __nv_bfloat16* xbuf = xs + (c & 1) * (L::kRows * kGvXStride);
-    static_assert(kGroupsPerChunk % 2 == 0, "groups alternate between two register sets");
-#pragma unroll 1
-    for (int gg = 0; gg < kGroupsPerChunk; gg += 2) {
-      const int g = c * kGroupsPerChunk + gg;
-      load_group(g + 1, wnxt);
-      compute_group(g, wcur, xbuf);
-      load_group(g + 2, wcur);
-      compute_group(g + 1, wnxt, xbuf);
-    }
-    __syncthreads();  // before chunk c + 2 overwrites this buffer
+    __syncwarp();  // the stage is free for the copy the next iteration issues
   }
   CpAsyncWait<0>();
-  __syncthreads();
+  __syncthreads();  // every warp is done with the pipeline space
 
-  // The eight warps' partial tiles -> shared memory -> one tile, summed in warp order.
+  // The four warps' partial tiles -> shared memory -> one tile, summed in warp order.
+  float* red = reinterpret_cast<float*>(smem);                  // [kGvWarps][kRows][kGvRedStride]
+  float* tile = red + kGvWarps * (L::kRows * kGvRedStride);     // [kRows][kGvRedStride]
   {
     float* mine = red + warp * (L::kRows * kGvRedStride);
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
+    for (int j = 0; j < 8; ++j) {
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
-        // accumulator columns 2*tig, 2*tig+1 of n-tile nt are output columns col0 + (2*tig + e)*16 + nt
-        const int m0 = mt * 16 + gid;
-        mine[m0 * kGvRedStride + (2 * tig) * 16 + nt] = acc[mt][nt][0];
-        mine[m0 * kGvRedStride + (2 * tig + 1) * 16 + nt] = acc[mt][nt][1];
-        mine[(m0 + 8) * kGvRedStride + (2 * tig) * 16 + nt] = acc[mt][nt][2];
-        mine[(m0 + 8) * kGvRedStride + (2 * tig + 1) * 16 + nt] = acc[mt][nt][3];
+      for (int nt = 0; nt < NT; ++nt) {
+        const int m = nt * 8 + 2 * tig, c = gid * 16 + 2 * j;
+        mine[m * kGvRedStride + c] = acc[j][nt][0];
+        mine[(m + 1) * kGvRedStride + c] = acc[j][nt][1];
+        mine[m * kGvRedStride + c + 1] = acc[j][nt][2];
+        mine[(m + 1) * kGvRedStride + c + 1] = acc[j][nt][3];
       }
     }
   }
@@ -252,11 +235,10 @@ __global__ void __launch_bounds__(kGvThreads, 1) Int8GemvKernel(GemmParams p)
   cluster.sync();
   YT* y = static_cast<YT*>(p.y);
   for (int m = rank; m < p.M; m += nranks) {
-    for (int c = tid; c < kGvCols; c += kGvThreads) {
-      const int col = col0 + c;
-      if (col >= p.N) continue;
+    const int col = col0 + tid;
+    if (col < p.N) {
       float v = 0.f;
-      for (unsigned q = 0; q < nranks; ++q) v += cluster.map_shared_rank(tile, q)[m * kGvRedStride + c];
+      for (unsigned q = 0; q < nranks; ++q) v += cluster.map_shared_rank(tile, q)[m * kGvRedStride + tid];
       if (p.scales != nullptr) v *= __ldg(p.scales + col);
       if (p.residual != nullptr) v += __ldg(p.residual + static_cast<size_t>(m) * p.N + col);
       y[static_cast<size_t>(m) * p.N + col] = FromF32<YT>(v);
@@ -296,20 +278,19 @@ __global__ void __launch_bounds__(256) GemmExactKernel(const XT* x, const WT* w,
   y[static_cast<size_t>(i) * N + j] = FromF32<YT>(acc);
 }
 
-template <int MT, int U, typename YT>
+template <int NT, typename YT>
 cudaError_t PrepareGemv()
 {
-  return cudaFuncSetAttribute(Int8GemvKernel<MT, U, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              GvLayout<MT>::kBytes);
+  return cudaFuncSetAttribute(Int8GemvKernel<NT, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize, GvLayout<NT>::kBytes);
 }
 
-template <int MT, int U, typename YT>
+template <int NT, typename YT>
 cudaError_t LaunchGemv(const GemmParams& p, cudaStream_t stream)
 {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + kGvCols - 1) / kGvCols, p.ks, 1);
   cfg.blockDim = dim3(kGvThreads, 1, 1);
-  cfg.dynamicSmemBytes = GvLayout<MT>::kBytes;
+  cfg.dynamicSmemBytes = GvLayout<NT>::kBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -318,11 +299,12 @@ cudaError_t LaunchGemv(const GemmParams& p, cudaStream_t stream)
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, Int8GemvKernel<MT, U, YT>, p);
+  return cudaLaunchKernelEx(&cfg, Int8GemvKernel<NT, YT>, p);
 }
 
-// K slices for a shape: enough CTAs to fill the 148 SMs a few times over, each slice at least one full round of
-// the eight warps; 1, 2, 4 or 8 (the portable cluster sizes).  $TLALOC_B200_GEMV_KS overrides.
+// K slices for a shape (1, 2, 4 or 8: the portable cluster sizes): the count that wastes the least of the last
+// wave of CTAs over the 148 SMs (four CTAs each), among those that leave every warp at least four stages.
+// $TLALOC_B200_GEMV_KS overrides.
 int ChooseSlices(int k, int n)
 {
   static const int forced = [] {
@@ -331,9 +313,20 @@ int ChooseSlices(int k, int n)
   }();
   if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return forced;
   const int tiles = (n + kGvCols - 1) / kGvCols;
-  int ks = 1;
-  while (ks < 8 && tiles * ks < 3 * 148 && k / (ks * 2) >= 16 * kGvWarps * 2) ks *= 2;
-  return ks;
+  const int slots = 148 * 4;
+  int best = 1;
+  double best_eff = -1.0;
+  for (int ks = 1; ks <= 8; ks *= 2) {
+    if (ks > 1 && k / ks < kGvStageK * kGvWarps * 4) break;
+    const int items = tiles * ks;
+    const int waves = (items + slots - 1) / slots;
+    const double eff = static_cast<double>(items) / (static_cast<double>(waves) * slots);
+    if (eff > best_eff + 0.02) {
+      best_eff = eff;
+      best = ks;
+    }
+  }
+  return best;
 }
 
 }  // namespace
@@ -344,10 +337,12 @@ cudaError_t PrepareInt8GemmKernels()
   static bool done = false;
   std::lock_guard<std::mutex> lock(mu);
   if (done) return cudaSuccess;
-  cudaError_t e = PrepareGemv<1, 4, float>();
-  if (e == cudaSuccess) e = PrepareGemv<1, 4, __nv_bfloat16>();
-  if (e == cudaSuccess) e = PrepareGemv<2, 2, float>();
-  if (e == cudaSuccess) e = PrepareGemv<2, 2, __nv_bfloat16>();
+  cudaError_t e = PrepareGemv<1, float>();
+  if (e == cudaSuccess) e = PrepareGemv<1, __nv_bfloat16>();
+  if (e == cudaSuccess) e = PrepareGemv<2, float>();
+  if (e == cudaSuccess) e = PrepareGemv<2, __nv_bfloat16>();
+  if (e == cudaSuccess) e = PrepareGemv<4, float>();
+  if (e == cudaSuccess) e = PrepareGemv<4, __nv_bfloat16>();
   if (e == cudaSuccess) done = true;
   return e;
 }
@@ -373,6 +368,14 @@ cudaError_t LaunchExact(const void* x, const void* w, const float* scales, const
                                           static_cast<__nv_bfloat16*>(y), m, k, n, round_x);
   }
   return cudaGetLastError();
+}
+
+template <typename YT>
+cudaError_t LaunchGemvRows(const GemmParams& p, int rows, cudaStream_t st)
+{
+  if (rows <= 8) return LaunchGemv<1, YT>(p, st);
+  if (rows <= 16) return LaunchGemv<2, YT>(p, st);
+  return LaunchGemv<4, YT>(p, st);
 }
 
 }  // namespace
@@ -428,7 +431,8 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
   p.N = n;
   p.ks = ChooseSlices(k, n);
   const int per = (k + p.ks - 1) / p.ks;
-  p.Kc = (per + 16 * kGvWarps - 1) / (16 * kGvWarps) * (16 * kGvWarps);
+  const int unit = kGvStageK * kGvWarps;
+  p.Kc = (per + unit - 1) / unit * unit;
   const size_t ybytes = DtypeBytes(y_dtype);
   for (int m0 = 0; m0 < m; m0 += 32) {
     const int rows = std::min(32, m - m0);
@@ -436,11 +440,7 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
     p.x = xb + static_cast<size_t>(m0) * k;
     p.residual = residual ? residual + static_cast<size_t>(m0) * n : nullptr;
     p.y = static_cast<unsigned char*>(y) + static_cast<size_t>(m0) * n * ybytes;
-    if (rows <= 16) {
-      e = y_dtype == TLALOC_B200_F32 ? LaunchGemv<1, 4, float>(p, st) : LaunchGemv<1, 4, __nv_bfloat16>(p, st);
-    } else {
-      e = y_dtype == TLALOC_B200_F32 ? LaunchGemv<2, 2, float>(p, st) : LaunchGemv<2, 2, __nv_bfloat16>(p, st);
-    }
+    e = y_dtype == TLALOC_B200_F32 ? LaunchGemvRows<float>(p, rows, st) : LaunchGemvRows<__nv_bfloat16>(p, rows, st);
     if (e != cudaSuccess) return CudaFail("INT8_PROJ launch", e);
     CountLaunches(1);
   }

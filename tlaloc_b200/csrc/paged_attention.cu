@@ -221,10 +221,16 @@ __global__ void __launch_bounds__(kGenThreads) PaSliceGeneric(PaParams p)
 
 // ------------------------------------------------------------------------------------------
 // The tensor-core slice kernel (bf16 pools).
+//
+// Orientation: the 16 positions of a group are the M dimension of every MMA and the (<= 8 per n-tile) queries
+// the N dimension, so a group costs D/16 MMAs for S^T = K Q^T and D/16 (x2: hi and lo parts of P) for
+// O^T = V^T P^T, and nothing is padded beyond 8 queries.  Q^T lives in registers as B fragments for the whole
+// kernel; K is read from shared memory as A fragments (ldmatrix), V^T as A fragments (ldmatrix.trans); the
+// probabilities go from accumulator layout to B-fragment layout with movmatrix.
 
 constexpr int kMmaThreads = 128;
 constexpr int kMmaWarps = 4;
-constexpr int kMmaQ = 16;  // query rows of one m16 tile
+constexpr int kMmaQ = 16;  // the most queries per (table, kv head) this kernel takes: two n-tiles of 8
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -254,6 +260,12 @@ __device__ __forceinline__ void LdMatrixX4Trans(uint32_t (&r)[4], uint32_t addr)
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
+__device__ __forceinline__ uint32_t MovMatrixTrans(uint32_t a)
+{
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
+}
 __device__ __forceinline__ void MmaBf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
 {
   asm volatile(
@@ -277,32 +289,29 @@ __device__ __forceinline__ void SplitPack(float x, float y, uint32_t& hi, uint32
   lo = static_cast<uint32_t>(__bfloat16_as_ushort(xl)) | (static_cast<uint32_t>(__bfloat16_as_ushort(yl)) << 16);
 }
 
-// Dynamic shared memory of PaSliceMma, in bytes: the query tile(s), the four warps'
-// stages, then the slice's block-table entries.
-template <int D, bool QLO, int NS>
+// Dynamic shared memory of PaSliceMma, in bytes: the four warps' stages, then the slice's block-table entries.
+template <int D, int NS>
 struct MmaLayout {
   static constexpr int kRowBytes = D * 2;
-  static constexpr int kTileBytes = 16 * kRowBytes;  // 16 positions of K (or V), or the 16 query rows
+  static constexpr int kTileBytes = 16 * kRowBytes;  // 16 positions of K (or V)
   static constexpr int kStageBytes = 2 * kTileBytes;
   static constexpr int kWarpBytes = NS * kStageBytes;
-  static constexpr int kQBytes = (QLO ? 2 : 1) * kTileBytes;
-  static constexpr int kTabOffset = kQBytes + kMmaWarps * kWarpBytes;
+  static constexpr int kTabOffset = kMmaWarps * kWarpBytes;
   static_assert(kWarpBytes >= static_cast<int>(sizeof(float)) * kMmaQ * (D + 2), "a warp's stages hold its partial record");
   static size_t Bytes(int tab_entries) { return kTabOffset + sizeof(int) * static_cast<size_t>(tab_entries); }
 };
 
-template <typename QT, int D, int NS>
+// QT: the query's element type (an f32 query is carried as hi + lo bf16 parts); NT: n-tiles of 8 queries.
+template <typename QT, int D, int NS, int NT>
 __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
 {
   constexpr bool QLO = sizeof(QT) == 4;
-  using L = MmaLayout<D, QLO, NS>;
+  using L = MmaLayout<D, NS>;
   constexpr int CPR = L::kRowBytes / 16;  // 16-byte chunks per row
+  constexpr int KS = D / 16;              // k-steps of Q K^T, m-tiles of V^T P^T
   extern __shared__ __align__(1024) unsigned char smem[];
-  unsigned char* qhi = smem;
-  unsigned char* qlo = smem + L::kTileBytes;
-  unsigned char* stages = smem + L::kQBytes;
+  unsigned char* stages = smem;
   int* tab = reinterpret_cast<int*>(smem + L::kTabOffset);
-  __shared__ int qlen_s[kMmaQ], qfirst_s[kMmaQ];
 
   const int s = blockIdx.x, kv = blockIdx.y, tb = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -310,7 +319,7 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
   const int ctx = p.M * p.bs;
   const int c0 = s * p.slice;
 
-  // Every thread derives the CTA's live range from its (<= 16) rows' lengths.
+  // Every thread derives the CTA's live range from its rows' lengths.
   int maxlen = 0, minfirst = ctx;
   for (int r = 0; r < p.rpt; ++r) {
     const int len = ClampI(__ldg(p.lens + tb * p.rpt + r), 0, ctx);
@@ -318,58 +327,76 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
     minfirst = min(minfirst, p.window > 0 ? max(0, len - p.window) : 0);
   }
   const int c1 = min(min(c0 + p.slice, ctx), maxlen);
-  const int t_begin = max(c0, minfirst);
+  const int t_begin = max(c0, minfirst) & ~15;  // groups start on multiples of 16 (the slice start is one)
   if (t_begin >= c1) return;
   const int ngroups = (c1 - t_begin + 15) >> 4;
 
-  if (tid < kMmaQ) {
-    int len = 0, first = 0;
-    if (tid < p.NQ) {
-      const int full = ClampI(__ldg(p.lens + tb * p.rpt + tid / p.group), 0, ctx);
-      first = p.window > 0 ? max(0, full - p.window) : 0;
-      len = min(full, c1);
-    }
-    qlen_s[tid] = len;
-    qfirst_s[tid] = first;
-  }
   const int b0 = p.bs_shift >= 0 ? (t_begin >> p.bs_shift) : t_begin / p.bs;
   const int b1 = p.bs_shift >= 0 ? ((c1 - 1) >> p.bs_shift) : (c1 - 1) / p.bs;
   for (int j = tid; j <= b1 - b0; j += kMmaThreads) {
     tab[j] = ClampI(__ldg(p.tables + static_cast<size_t>(tb) * p.M + b0 + j), 0, p.P - 1);
   }
-  // The query tile: rows i < NQ hold query i (row i / group of the table, head kv*group + i % group), the
-  // rest zero; bf16 hi part (and lo part for an f32 query), chunk-swizzled like the K/V rows.
-  {
-    const QT* q = static_cast<const QT*>(p.q);
-    for (int idx = tid; idx < kMmaQ * (D / 2); idx += kMmaThreads) {
-      const int i = idx / (D / 2), d = (idx - i * (D / 2)) * 2;
-      float x = 0.f, y = 0.f;
+
+  // This lane's queries: column 2*tig + e of n-tile nt is query nt*8 + 2*tig + e (row / head as below).
+  int qlen[NT][2], qfirst[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int i = nt * 8 + 2 * tig + e;
+      int len = 0, first = 0;
       if (i < p.NQ) {
-        const QT* src = q + (static_cast<size_t>(tb * p.rpt + i / p.group) * p.H + kv * p.group + i % p.group) * D + d;
-        x = ToF32(src[0]);
-        y = ToF32(src[1]);
+        const int full = ClampI(__ldg(p.lens + tb * p.rpt + i / p.group), 0, ctx);
+        first = p.window > 0 ? max(0, full - p.window) : 0;
+        len = min(full, c1);
       }
-      uint32_t hi, lo;
-      SplitPack(x, y, hi, lo);
-      const int byte = d * 2, chunk = byte >> 4, within = byte & 15;
-      const int at = i * L::kRowBytes + ((chunk ^ (i & 7)) << 4) + within;
-      *reinterpret_cast<uint32_t*>(qhi + at) = hi;
-      if (QLO) *reinterpret_cast<uint32_t*>(qlo + at) = lo;
+      qlen[nt][e] = len;
+      qfirst[nt][e] = first;
     }
   }
-  __syncthreads();
+  // Q^T as B fragments: for k-step kk, b0b1 = Q[query gid][16kk + 2tig, +1], b2b3 = Q[query gid][16kk + 8 + 2tig, +1].
+  uint32_t qh[NT][KS][2], ql[QLO ? NT : 1][QLO ? KS : 1][2];
+  {
+    const QT* q = static_cast<const QT*>(p.q);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int i = nt * 8 + gid;
+      const bool have = i < p.NQ;
+      const QT* src = q + (static_cast<size_t>(tb * p.rpt + (have ? i / p.group : 0)) * p.H + kv * p.group + (have ? i % p.group : 0)) * D;
+#pragma unroll
+      for (int kk = 0; kk < KS; ++kk) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int d = 16 * kk + 8 * h + 2 * tig;
+          const float x = have ? ToF32(src[d]) : 0.f, y = have ? ToF32(src[d + 1]) : 0.f;
+          uint32_t hi, lo;
+          SplitPack(x, y, hi, lo);
+          qh[nt][kk][h] = hi;
+          if (QLO) ql[nt][kk][h] = lo;
+        }
+      }
+    }
+  }
+  __syncthreads();  // tab is staged
 
   const __nv_bfloat16* kc = static_cast<const __nv_bfloat16*>(p.kc);
   const __nv_bfloat16* vc = static_cast<const __nv_bfloat16*>(p.vc);
   unsigned char* my_stages = stages + warp * L::kWarpBytes;
   const uint32_t my_stages_addr = SmemAddr(my_stages);
   const int my_n = warp < ngroups ? (ngroups - warp + kMmaWarps - 1) / kMmaWarps : 0;
+  const size_t row_elems = static_cast<size_t>(p.Hkv) * D;  // elements between consecutive positions of a block
+  const bool one_block_per_group = p.bs_shift >= 4;          // block size a power of two >= 16: a group never straddles blocks
 
-  // One group of 16 positions: each lane copies 16-byte chunks of the K and V rows; a row's chunk c
-  // lands at chunk c ^ (row & 7) so that the ldmatrix reads below are conflict-free.
+  // One group of 16 positions: each lane copies 16-byte chunks of the K and V rows; a row's chunk c lands at
+  // chunk c ^ (row & 7) so that the ldmatrix reads below are conflict-free.  Rows at or past c1 are zero-filled.
   auto issue = [&](int it) {
     const int t_base = t_begin + ((warp + kMmaWarps * it) << 4);
     const uint32_t dst_base = my_stages_addr + (it % NS) * L::kStageBytes;
+    size_t group_off = 0;
+    if (one_block_per_group) {
+      const int blk = tab[(t_base >> p.bs_shift) - b0];
+      group_off = ((static_cast<size_t>(blk) << p.bs_shift) + (t_base & (p.bs - 1))) * row_elems + static_cast<size_t>(kv) * D;
+    }
 #pragma unroll
     for (int i = 0; i < 16 * CPR / 32; ++i) {
       const int c = lane + 32 * i;
@@ -378,9 +405,13 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
       const bool valid = t < c1;
       size_t off = 0;
       if (valid) {
-        const int blk_i = p.bs_shift >= 0 ? (t >> p.bs_shift) : t / p.bs;
-        const int slot = t - blk_i * p.bs;
-        off = ((static_cast<size_t>(tab[blk_i - b0]) * p.bs + slot) * p.Hkv + kv) * D + col * 8;
+        if (one_block_per_group) {
+          off = group_off + r * row_elems + col * 8;
+        } else {
+          const int blk_i = p.bs_shift >= 0 ? (t >> p.bs_shift) : t / p.bs;
+          const int slot = t - blk_i * p.bs;
+          off = ((static_cast<size_t>(tab[blk_i - b0]) * p.bs + slot) * p.Hkv + kv) * D + col * 8;
+        }
       }
       const uint32_t dst = dst_base + r * L::kRowBytes + ((col ^ (r & 7)) << 4);
       CpAsync16(dst, kc + off, valid ? 16 : 0);
@@ -393,16 +424,18 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
     CpAsyncCommit();
   }
 
-  float o[D / 8][4];
+  float o[NT][KS][4];
+  float m_run[NT][2], l_run[NT][2];
 #pragma unroll
-  for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
-  const int len_lo = qlen_s[gid], len_hi = qlen_s[gid + 8];
-  const int first_lo = qfirst_s[gid], first_hi = qfirst_s[gid + 8];
+  for (int nt = 0; nt < NT; ++nt) {
+    m_run[nt][0] = m_run[nt][1] = -INFINITY;
+    l_run[nt][0] = l_run[nt][1] = 0.f;
+#pragma unroll
+    for (int mt = 0; mt < KS; ++mt) o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.f;
+  }
   const float sl2 = p.scale * kLog2e;
-  const uint32_t qhi_addr = SmemAddr(qhi), qlo_addr = SmemAddr(qlo);
-  const int row_a = (lane & 7) + ((lane >> 3) & 1) * 8;  // A (query) and V: matrices 1, 3 are rows 8..15
-  const int row_b = (lane & 7) + (lane >> 4) * 8;        // K: matrices 2, 3 are positions 8..15
+  const int row_k = (lane & 7) + ((lane >> 3) & 1) * 8;  // K as A: matrices 1, 3 are positions 8..15; 2, 3 the next 8 dims
+  const int row_v = (lane & 7) + (lane >> 4) * 8;        // V^T as A: matrices 2, 3 are positions 8..15; 1, 3 the next 8 dims
 
   for (int it = 0; it < my_n; ++it) {
     if (it + NS - 1 < my_n) issue(it + NS - 1);
@@ -413,78 +446,74 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
     const uint32_t k_addr = my_stages_addr + (it % NS) * L::kStageBytes;
     const uint32_t v_addr = k_addr + L::kTileBytes;
 
-    float sacc[2][4];
+    float sacc[NT][4];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+    for (int nt = 0; nt < NT; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
 #pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-      uint32_t a[4], b[4];
-      LdMatrixX4(a, qhi_addr + row_a * L::kRowBytes + (((2 * kk + (lane >> 4)) ^ (row_a & 7)) << 4));
-      LdMatrixX4(b, k_addr + row_b * L::kRowBytes + (((2 * kk + ((lane >> 3) & 1)) ^ (row_b & 7)) << 4));
-      MmaBf16(sacc[0], a, b[0], b[1]);
-      MmaBf16(sacc[1], a, b[2], b[3]);
-      if (QLO) {
-        LdMatrixX4(a, qlo_addr + row_a * L::kRowBytes + (((2 * kk + (lane >> 4)) ^ (row_a & 7)) << 4));
-        MmaBf16(sacc[0], a, b[0], b[1]);
-        MmaBf16(sacc[1], a, b[2], b[3]);
+    for (int kk = 0; kk < KS; ++kk) {
+      uint32_t a[4];
+      LdMatrixX4(a, k_addr + row_k * L::kRowBytes + (((2 * kk + (lane >> 4)) ^ (row_k & 7)) << 4));
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        MmaBf16(sacc[nt], a, qh[nt][kk][0], qh[nt][kk][1]);
+        if (QLO) MmaBf16(sacc[nt], a, ql[nt][kk][0], ql[nt][kk][1]);
       }
     }
-    // Scale into the log2 domain, mask, and fold the group into the running softmax state.
-    float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
+    // sacc[nt]: [0], [1] = position t_base + gid against queries 2tig, 2tig + 1; [2], [3] = position t_base + gid + 8.
+    uint32_t pb_hi[NT][2], pb_lo[NT][2];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int nt = 0; nt < NT; ++nt) {
+      float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int tok = t_base + 8 * j + 2 * tig + (e & 1);
-        const bool live = e < 2 ? (tok < len_lo && tok >= first_lo) : (tok < len_hi && tok >= first_hi);
-        const float v = live ? sacc[j][e] * sl2 : -INFINITY;
-        sacc[j][e] = v;
-        if (e < 2) tmax_lo = fmaxf(tmax_lo, v);
-        else tmax_hi = fmaxf(tmax_hi, v);
+      for (int x = 0; x < 4; ++x) {
+        const int e = x & 1;
+        const int tok = t_base + gid + (x >> 1) * 8;
+        const bool live = tok < qlen[nt][e] && tok >= qfirst[nt][e];
+        const float v = live ? sacc[nt][x] * sl2 : -INFINITY;
+        sacc[nt][x] = v;
+        tmax[e] = fmaxf(tmax[e], v);
       }
-    }
-    tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 1));
-    tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 2));
-    tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 1));
-    tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 2));
-    const float mn_lo = fmaxf(m_lo, tmax_lo), mn_hi = fmaxf(m_hi, tmax_hi);
-    const float alpha_lo = mn_lo == -INFINITY ? 1.f : Exp2(m_lo - mn_lo);
-    const float alpha_hi = mn_hi == -INFINITY ? 1.f : Exp2(m_hi - mn_hi);
-    const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo, base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-    m_lo = mn_lo;
-    m_hi = mn_hi;
-    float ps_lo = 0.f, ps_hi = 0.f;
+      float alpha[2];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      sacc[j][0] = Exp2(sacc[j][0] - base_lo);
-      sacc[j][1] = Exp2(sacc[j][1] - base_lo);
-      sacc[j][2] = Exp2(sacc[j][2] - base_hi);
-      sacc[j][3] = Exp2(sacc[j][3] - base_hi);
-      ps_lo += sacc[j][0] + sacc[j][1];
-      ps_hi += sacc[j][2] + sacc[j][3];
-    }
-    l_lo = l_lo * alpha_lo + ps_lo;
-    l_hi = l_hi * alpha_hi + ps_hi;
+      for (int e = 0; e < 2; ++e) {
+        float t = tmax[e];
+        t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 4));
+        t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 8));
+        t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 16));
+        const float mn = fmaxf(m_run[nt][e], t);
+        alpha[e] = mn == -INFINITY ? 1.f : Exp2(m_run[nt][e] - mn);
+        const float base = mn == -INFINITY ? 0.f : mn;
+        m_run[nt][e] = mn;
+        const float p0 = Exp2(sacc[nt][e] - base), p1 = Exp2(sacc[nt][2 + e] - base);
+        sacc[nt][e] = p0;
+        sacc[nt][2 + e] = p1;
+        l_run[nt][e] = l_run[nt][e] * alpha[e] + p0 + p1;
+      }
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
-      o[n][0] *= alpha_lo;
-      o[n][1] *= alpha_lo;
-      o[n][2] *= alpha_hi;
-      o[n][3] *= alpha_hi;
+      for (int mt = 0; mt < KS; ++mt) {
+        o[nt][mt][0] *= alpha[0];
+        o[nt][mt][1] *= alpha[1];
+        o[nt][mt][2] *= alpha[0];
+        o[nt][mt][3] *= alpha[1];
+      }
+      // P (positions x queries, accumulator layout) -> P^T as B fragments: transpose the two 8x8 blocks.
+      uint32_t h0, l0, h1, l1;
+      SplitPack(sacc[nt][0], sacc[nt][1], h0, l0);
+      SplitPack(sacc[nt][2], sacc[nt][3], h1, l1);
+      pb_hi[nt][0] = MovMatrixTrans(h0);
+      pb_hi[nt][1] = MovMatrixTrans(h1);
+      pb_lo[nt][0] = MovMatrixTrans(l0);
+      pb_lo[nt][1] = MovMatrixTrans(l1);
     }
-    uint32_t ph[4], pl[4];
-    SplitPack(sacc[0][0], sacc[0][1], ph[0], pl[0]);
-    SplitPack(sacc[0][2], sacc[0][3], ph[1], pl[1]);
-    SplitPack(sacc[1][0], sacc[1][1], ph[2], pl[2]);
-    SplitPack(sacc[1][2], sacc[1][3], ph[3], pl[3]);
 #pragma unroll
-    for (int c = 0; c < CPR; c += 2) {
-      uint32_t b[4];
-      LdMatrixX4Trans(b, v_addr + row_a * L::kRowBytes + (((c + (lane >> 4)) ^ (row_a & 7)) << 4));
-      MmaBf16(o[c], ph, b[0], b[1]);
-      MmaBf16(o[c + 1], ph, b[2], b[3]);
-      MmaBf16(o[c], pl, b[0], b[1]);
-      MmaBf16(o[c + 1], pl, b[2], b[3]);
+    for (int mt = 0; mt < KS; ++mt) {
+      uint32_t a[4];
+      LdMatrixX4Trans(a, v_addr + row_v * L::kRowBytes + (((2 * mt + ((lane >> 3) & 1)) ^ (row_v & 7)) << 4));
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        MmaBf16(o[nt][mt], a, pb_hi[nt][0], pb_hi[nt][1]);
+        MmaBf16(o[nt][mt], a, pb_lo[nt][0], pb_lo[nt][1]);
+      }
     }
     __syncwarp();  // the stage is free for the copy the next iteration issues
   }
@@ -492,24 +521,29 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
   __syncwarp();
 
   // Each warp leaves {m, l, o} of its positions in its own stage space; the CTA then merges the four.
-  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
   {
     float* wm = reinterpret_cast<float*>(my_stages);
     float* wl = wm + kMmaQ;
     float* wo = wl + kMmaQ;
-    if (tig == 0) {
-      wm[gid] = m_lo;
-      wm[gid + 8] = m_hi;
-      wl[gid] = l_lo;
-      wl[gid + 8] = l_hi;
-    }
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
-      *reinterpret_cast<float2*>(wo + gid * D + n * 8 + 2 * tig) = make_float2(o[n][0], o[n][1]);
-      *reinterpret_cast<float2*>(wo + (gid + 8) * D + n * 8 + 2 * tig) = make_float2(o[n][2], o[n][3]);
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float l = l_run[nt][e];
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        const int i = nt * 8 + 2 * tig + e;
+        if (gid == 0) {
+          wm[i] = m_run[nt][e];
+          wl[i] = l;
+        }
+#pragma unroll
+        for (int mt = 0; mt < KS; ++mt) {
+          wo[i * D + 16 * mt + gid] = o[nt][mt][e];
+          wo[i * D + 16 * mt + gid + 8] = o[nt][mt][2 + e];
+        }
+      }
     }
   }
   __syncthreads();
@@ -598,24 +632,59 @@ __global__ void KvCacheWriteKernel(PT* pool, const NT* new_kv, const int* slots,
 // ------------------------------------------------------------------------------------------
 // Host side.
 
-constexpr int kMmaStages = 3;
+// Stages per warp: 2 by default (three CTAs per SM; occupancy matters more than depth here) ($TLALOC_B200_PA_STAGES = 2, 3 or 4).
+int MmaStages()
+{
+  static const int v = [] {
+    const char* e = std::getenv("TLALOC_B200_PA_STAGES");
+    const int x = e != nullptr ? std::atoi(e) : 0;
+    return x >= 2 && x <= 4 ? x : 2;
+  }();
+  return v;
+}
+
+// Room for the table entries of the longest slice a launch may choose (8192 positions of 8-position blocks).
+constexpr int kMaxTabEntries = 1024 + 2;
+
+template <typename QT, int D, int NS>
+cudaError_t PrepareMmaNs()
+{
+  cudaError_t e = cudaFuncSetAttribute(PaSliceMma<QT, D, NS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(MmaLayout<D, NS>::Bytes(kMaxTabEntries)));
+  if (e == cudaSuccess) {
+    e = cudaFuncSetAttribute(PaSliceMma<QT, D, NS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(MmaLayout<D, NS>::Bytes(kMaxTabEntries)));
+  }
+  return e;
+}
 
 template <typename QT, int D>
 cudaError_t PrepareMma()
 {
-  using L = MmaLayout<D, sizeof(QT) == 4, kMmaStages>;
-  // Room for the table entries of the longest slice a launch may choose (8192 positions of 8-position blocks).
-  return cudaFuncSetAttribute(PaSliceMma<QT, D, kMmaStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(L::Bytes(1024 + 2)));
+  cudaError_t e = PrepareMmaNs<QT, D, 2>();
+  if (e == cudaSuccess) e = PrepareMmaNs<QT, D, 3>();
+  if (e == cudaSuccess) e = PrepareMmaNs<QT, D, 4>();
+  return e;
+}
+
+template <typename QT, int D, int NS>
+cudaError_t LaunchMmaNs(const PaParams& p, cudaStream_t stream)
+{
+  const size_t smem = MmaLayout<D, NS>::Bytes(p.slice / p.bs + 2);
+  const dim3 grid(p.S, p.Hkv, p.Tb);
+  if (p.NQ <= 8) PaSliceMma<QT, D, NS, 1><<<grid, kMmaThreads, smem, stream>>>(p);
+  else PaSliceMma<QT, D, NS, 2><<<grid, kMmaThreads, smem, stream>>>(p);
+  return cudaGetLastError();
 }
 
 template <typename QT, int D>
 cudaError_t LaunchMma(const PaParams& p, cudaStream_t stream)
 {
-  using L = MmaLayout<D, sizeof(QT) == 4, kMmaStages>;
-  const size_t smem = L::Bytes(p.slice / p.bs + 2);
-  PaSliceMma<QT, D, kMmaStages><<<dim3(p.S, p.Hkv, p.Tb), kMmaThreads, smem, stream>>>(p);
-  return cudaGetLastError();
+  switch (MmaStages()) {
+    case 3: return LaunchMmaNs<QT, D, 3>(p, stream);
+    case 4: return LaunchMmaNs<QT, D, 4>(p, stream);
+    default: return LaunchMmaNs<QT, D, 2>(p, stream);
+  }
 }
 
 template <typename QT, typename KVT>
@@ -632,7 +701,7 @@ int PreferredSlice()
   static const int v = [] {
     const char* e = std::getenv("TLALOC_B200_PA_SLICE");
     const int x = e != nullptr ? std::atoi(e) : 0;
-    return x >= 16 ? x : 512;
+    return x >= 16 ? x : 1024;
   }();
   return v;
 }

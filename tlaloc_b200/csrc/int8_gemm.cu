@@ -84,10 +84,11 @@ template <int B>
 __device__ __forceinline__ uint32_t CodesToBf16x2(uint32_t w_lo_k, uint32_t w_hi_k)
 {
   const uint32_t q = __byte_perm(w_lo_k, w_hi_k, B | (B << 4) | ((4 + B) << 8) | ((4 + B) << 12));
-  const uint32_t t = (q & 0x007F007Fu) | 0x43004300u;
-  const uint32_t c = (q & 0x00800080u) | 0xC300C300u;
+  uint32_t t, c;  // (q & mask) | magic as one three-input logic op each
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(t) : "r"(q), "r"(0x007F007Fu), "r"(0x43004300u));
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(c) : "r"(q), "r"(0x00800080u), "r"(0xC300C300u));
   uint32_t r;
-  asm("add.rn.bf16x2 %0, %1, %2;\n" : "=r"(r) : "r"(t), "r"(c));
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;\n" : "=r"(r) : "r"(t), "r"(0x3F803F80u), "r"(c));
   return r;
 }
 
@@ -116,30 +117,54 @@ __global__ void __launch_bounds__(kGvThreads) Int8GemvKernel(GemmParams p)
   const int ke = min(p.K, kb + p.Kc);
   const int nstages = ke > kb ? (ke - kb + kGvStageK - 1) / kGvStageK : 0;
   const int my_n = warp < nstages ? (nstages - warp + kGvWarps - 1) / kGvWarps : 0;
-  unsigned char* my_pipe = smem + warp * L::kWarpBytes;
-  const uint32_t my_pipe_addr = SmemAddr(my_pipe);
+  const uint32_t my_pipe_addr = SmemAddr(smem + warp * L::kWarpBytes);
 
-  // Stage `it` of this warp: k rows [k0, k0 + 32).  Weight row r's 16-byte chunk c lands at chunk c ^ (r & 6), the
-  // activation row m's chunk c at c ^ ((m >> 1) & 3), so the reads below are conflict-free.  K is a multiple of 8
-  // and N of 16 on this path, so a chunk is wholly inside or outside the matrix; outside is zero-filled.
+  // Copies of one stage (k rows [k0, k0 + 32) of this warp), all lane-invariant parts computed once.
+  //   weights: copy i of lane (l3 = lane >> 3, ch = lane & 7) moves row l3 + 4i, 16-byte chunk ch, to chunk
+  //            ch ^ (row & 6): (row & 6) is (l3 & 2) for even i and (l3 & 2) | 4 for odd i;
+  //   activations: copy i moves row (lane >> 2) + 8i, 16-byte piece lane & 3, to piece ^ ((row >> 1) & 3).
+  // The reads further down are then conflict-free.  K is a multiple of 8 and N of 16 on this path, so a chunk is
+  // wholly inside or outside the matrix; outside is zero-filled.
+  const int l3 = lane >> 3, ch = lane & 7;
+  const bool col_ok = col0 + ch * 16 < p.N;
+  const uint32_t wdst_even = l3 * kGvCols + ((ch ^ (l3 & 2)) << 4);
+  const uint32_t wdst_odd = (l3 + 4) * kGvCols + ((ch ^ ((l3 & 2) | 4)) << 4);
+  const size_t w_row4 = static_cast<size_t>(4) * p.N;
+  const int8_t* w_lane = p.w + static_cast<size_t>(kb + warp * kGvStageK + l3) * p.N + col0 + (col_ok ? ch * 16 : 0);
+  const size_t w_stage = static_cast<size_t>(kGvWarps * kGvStageK) * p.N;
+  const int xm = lane >> 2, xpiece = lane & 3;
+  const uint32_t xdst = kGvWBytes + xm * (kGvStageK * 2) + ((xpiece ^ ((xm >> 1) & 3)) << 4);
+  const __nv_bfloat16* x_lane = p.x + static_cast<size_t>(xm) * p.K + kb + warp * kGvStageK + xpiece * 8;
+
   auto issue = [&](int it) {
     const int k0 = kb + (warp + kGvWarps * it) * kGvStageK;
     const uint32_t dst = my_pipe_addr + (it % kGvStages) * L::kStageBytes;
+    const int8_t* src = w_lane + it * w_stage;
+    if (k0 + kGvStageK <= ke) {  // the whole stage is inside K
+      const int bytes = col_ok ? 16 : 0;
 #pragma unroll
-    for (int i = 0; i < kGvWBytes / 16 / 32; ++i) {
-      const int c = lane + 32 * i;
-      const int r = c >> 3, ch = c & 7;
-      const bool valid = k0 + r < ke && col0 + ch * 16 < p.N;
-      const int8_t* src = p.w + (valid ? static_cast<size_t>(k0 + r) * p.N + col0 + ch * 16 : 0);
-      CpAsync16(dst + r * kGvCols + ((ch ^ (r & 6)) << 4), src, valid ? 16 : 0);
-    }
+      for (int i = 0; i < 8; i += 2) {
+        CpAsync16(dst + wdst_even + i * (4 * kGvCols), src + i * w_row4, bytes);
+        CpAsync16(dst + wdst_odd + i * (4 * kGvCols), src + (i + 1) * w_row4, bytes);
+      }
 #pragma unroll
-    for (int i = 0; i < L::kXBytes / 16 / 32; ++i) {
-      const int c = lane + 32 * i;
-      const int m = c >> 2, piece = c & 3;
-      const bool valid = m < p.M && k0 + piece * 8 < ke;
-      const __nv_bfloat16* src = p.x + (valid ? static_cast<size_t>(m) * p.K + k0 + piece * 8 : 0);
-      CpAsync16(dst + kGvWBytes + m * (kGvStageK * 2) + ((piece ^ ((m >> 1) & 3)) << 4), src, valid ? 16 : 0);
+      for (int i = 0; i < NT; ++i) {
+        const bool valid = xm + 8 * i < p.M;
+        CpAsync16(dst + xdst + i * (8 * kGvStageK * 2), x_lane + (valid ? static_cast<size_t>(8 * i) * p.K + it * (kGvWarps * kGvStageK) : 0),
+                  valid ? 16 : 0);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const bool valid = col_ok && k0 + l3 + 4 * i < ke;
+        CpAsync16(dst + ((i & 1) ? wdst_odd - 4 * kGvCols : wdst_even) + i * (4 * kGvCols), valid ? src + i * w_row4 : p.w, valid ? 16 : 0);
+      }
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        const bool valid = xm + 8 * i < p.M && k0 + xpiece * 8 < ke;
+        CpAsync16(dst + xdst + i * (8 * kGvStageK * 2),
+                  valid ? x_lane + static_cast<size_t>(8 * i) * p.K + it * (kGvWarps * kGvStageK) : p.x, valid ? 16 : 0);
+      }
     }
   };
 
@@ -155,31 +180,30 @@ __global__ void __launch_bounds__(kGvThreads) Int8GemvKernel(GemmParams p)
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[j][nt][0] = acc[j][nt][1] = acc[j][nt][2] = acc[j][nt][3] = 0.f;
 
+  // Reads of a stage.  Weights: this lane's 16 columns (chunk gid) of rows 2tig + {0, 1, 8, 9} of each 16-row step;
+  // for all of them (row & 6) == 2tig.  Activations (ldmatrix): row lane & 7 of the n-tile, piece 2h + ((lane >> 3) & 1).
+  const uint32_t wread = (2 * tig) * kGvCols + ((gid ^ (2 * tig)) << 4);
+  const int xr = lane & 7, xsw = (xr >> 1) & 3, xp0 = (lane >> 3) & 1;
+  const uint32_t xread0 = kGvWBytes + xr * (kGvStageK * 2) + ((xp0 ^ xsw) << 4);
+  const uint32_t xread1 = kGvWBytes + xr * (kGvStageK * 2) + (((xp0 + 2) ^ xsw) << 4);
+
   for (int it = 0; it < my_n; ++it) {
     if (it + kGvStages - 1 < my_n) issue(it + kGvStages - 1);
     CpAsyncCommit();
     CpAsyncWait<kGvStages - 1>();
     __syncwarp();
-    const uint32_t w_addr = my_pipe_addr + (it % kGvStages) * L::kStageBytes;
-    const uint32_t x_addr = w_addr + kGvWBytes;
+    const uint32_t st_addr = my_pipe_addr + (it % kGvStages) * L::kStageBytes;
 #pragma unroll
     for (int h = 0; h < kGvStageK / 16; ++h) {
       // x^T as B fragments: b0b1 = x[row gid][16h + 2tig, +1], b2b3 = x[row gid][16h + 8 + 2tig, +1].
       uint32_t b[NT][2];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const int m = nt * 8 + (lane & 7), piece = 2 * h + ((lane >> 3) & 1);
-        LdMatrixX2(b[nt], x_addr + m * (kGvStageK * 2) + ((piece ^ ((m >> 1) & 3)) << 4));
-      }
-      // This lane's 16 columns of rows 16h + 2tig + {0, 1, 8, 9}.
-      uint4 r[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int row = 16 * h + 2 * tig + (q & 1) + (q >> 1) * 8;
-        r[q] = LdShared16(w_addr + row * kGvCols + ((gid ^ (row & 6)) << 4));
-      }
-      const uint32_t wa[4] = {r[0].x, r[0].y, r[0].z, r[0].w}, wb[4] = {r[1].x, r[1].y, r[1].z, r[1].w};
-      const uint32_t wc[4] = {r[2].x, r[2].y, r[2].z, r[2].w}, wd[4] = {r[3].x, r[3].y, r[3].z, r[3].w};
+      for (int nt = 0; nt < NT; ++nt) LdMatrixX2(b[nt], st_addr + (h ? xread1 : xread0) + nt * (8 * kGvStageK * 2));
+      const uint32_t wbase = st_addr + wread + h * (16 * kGvCols);
+      const uint4 ra = LdShared16(wbase), rb = LdShared16(wbase + kGvCols);
+      const uint4 rc = LdShared16(wbase + 8 * kGvCols), rd = LdShared16(wbase + 9 * kGvCols);
+      const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w}, wb[4] = {rb.x, rb.y, rb.z, rb.w};
+      const uint32_t wc[4] = {rc.x, rc.y, rc.z, rc.w}, wd[4] = {rd.x, rd.y, rd.z, rd.w};
 #pragma unroll
       for (int wi = 0; wi < 4; ++wi) {
         // Bytes 0, 1 of word wi are columns 4wi, 4wi + 1 (MMA j = 2wi); bytes 2, 3 are MMA j = 2wi + 1.

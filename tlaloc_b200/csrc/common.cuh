@@ -60,5 +60,12 @@ void CountLaunches(int n);
 // has to change a function attribute.
 cudaError_t PreparePagedAttentionKernels();
 cudaError_t PrepareInt8GemmKernels();
+cudaError_t PrepareInt8GemmTcKernels();
+
+// The tensor-core projection (int8_gemm_tc.cu): rows [0, m) of y = (x @ codes) * scales (+ residual), x bf16.
+cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const float* scales, const float* residual,
+                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches);
+// 1 if a bounded device-side wait has timed out since the last call (synchronous read), 0 if not, -1 on a CUDA error.
+int ReadTcStatus();
 
 }  // namespace tlaloc_b200

@@ -279,10 +279,13 @@ extern "C" const char* tlaloc_b200_last_error(void) { return ErrorBuffer(); }
 
 extern "C" long long tlaloc_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+extern "C" int tlaloc_b200_device_status(void) { return ReadTcStatus(); }
+
 extern "C" int tlaloc_b200_init(void)
 {
   cudaError_t e = PreparePagedAttentionKernels();
   if (e == cudaSuccess) e = PrepareInt8GemmKernels();
+  if (e == cudaSuccess) e = PrepareInt8GemmTcKernels();
   if (e != cudaSuccess) return CudaFail("kernel set-up", e);
   return kOk;
 }

@@ -448,6 +448,19 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
     CountLaunches(1);
     xb = reinterpret_cast<const __nv_bfloat16*>(scratch);
   }
+  static const int tc_min = [] {
+    const char* v = std::getenv("TLALOC_B200_GEMM_TC_MIN");
+    return v != nullptr ? std::atoi(v) : 17;
+  }();
+  if (m >= tc_min) {  // batches of rows: the tcgen05 kernel
+    e = PrepareInt8GemmTcKernels();
+    if (e != cudaSuccess) return CudaFail("INT8_PROJ set-up", e);
+    int launches = 0;
+    e = LaunchInt8GemmTc(xb, codes, scales, residual, y, y_dtype, m, k, n, st, &launches);
+    if (e != cudaSuccess) return CudaFail("INT8_PROJ tensor-core launch", e);
+    CountLaunches(launches);
+    return kOk;
+  }
   GemmParams p;
   p.w = codes;
   p.scales = scales;

@@ -61,6 +61,35 @@ def test_integer_activations_give_the_exact_integer_dot_product(m, k, n):
     assert np.array_equal(got.cpu().numpy(), want * scales[None, :])
 
 
+@pytest.mark.parametrize("m", [33, 64, 100, 128, 256, 300])
+@pytest.mark.parametrize("k,n", [(4096, 4096), (1024, 14336), (14336, 1024), (256, 688), (688, 256), (2048, 4112), (64, 256)])
+def test_batched_rows_on_the_tensor_core_kernel_are_exact_on_integer_activations(m, k, n):
+    """More than 32 rows take the tcgen05 kernel (int8 -> bf16 in shared memory, accumulators in TMEM)."""
+    from tlaloc_b200 import _native as N
+
+    rng = np.random.default_rng(m * 11 + k + n)
+    x, codes, _ = make(rng, m, k, n, x_int=True)
+    want = (x.astype(np.int64) @ codes.astype(np.int64)).astype(np.float32)
+    scales = np.exp2(rng.integers(-8, -2, size=n)).astype(np.float32)
+    res = rng.integers(-50, 50, size=(m, n)).astype(np.float32)
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), residual=dev(res))
+    torch.cuda.synchronize()
+    assert N.lib().tlaloc_b200_device_status() == 0
+    assert np.array_equal(got.cpu().numpy(), want * scales[None, :] + res)
+
+
+@pytest.mark.parametrize("m", [64, 256])
+def test_batched_rows_against_the_oracle(m):
+    rng = np.random.default_rng(8)
+    k, n = 4096, 14336
+    x, codes, scales = make(rng, m, k, n)
+    want = oracle.proj_int8(x, codes, scales, round_x_bf16=True, threads=8)
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales))
+    torch.cuda.synchronize()
+    worst = close(got.cpu().numpy(), want)
+    assert worst <= 1e-4 * max(1.0, np.abs(want).max())
+
+
 @pytest.mark.parametrize("m", [1, 8, 32])
 @pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 14336), (14336, 4096)])
 def test_sweep_shapes_against_the_oracle(m, k, n):

@@ -450,7 +450,7 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
   }
   static const int tc_min = [] {
     const char* v = std::getenv("TLALOC_B200_GEMM_TC_MIN");
-    return v != nullptr ? std::atoi(v) : 17;
+    return v != nullptr ? std::atoi(v) : 33;
   }();
   if (m >= tc_min) {  // batches of rows: the tcgen05 kernel
     e = PrepareInt8GemmTcKernels();

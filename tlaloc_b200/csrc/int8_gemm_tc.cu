@@ -396,7 +396,7 @@ int ChooseTcSlices(int k, int n, int mpad)
     const int items = tiles * ks;
     const int waves = (items + 147) / 148;
     const double eff = static_cast<double>(items) / (static_cast<double>(waves) * 148);
-    if (eff > best_eff + 0.02) {
+    if (eff > best_eff + 0.12) {  // more slices also cost a larger cluster reduction: ask for a clear gain
       best_eff = eff;
       best = ks;
     }

@@ -234,26 +234,48 @@ def run_ours(args) -> dict:
     h2d = int(sum(p.numel() * 4 for p in pinned))
     e2e = {"value": batch * K / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": batch * 4}
 
-    # ---- roofline of the dominant kernel: paged attention (slice + combine), timed alone over the layers' pools ----
+    # ---- roofline of the dominant kernel: paged attention (slice + combine), timed alone ---------------------------
+    # Timed on a pool of its own in which no two sequences share a block (one layer's worth, a few GB, far larger
+    # than L2), so the bytes it is credited with are bytes that come from HBM; the same launches over the step's own
+    # pools (which alias blocks when the logical KV does not fit the GPU) are reported beside it.
     lens_now = (lens0 + 1).astype(np.int64)
     att_bytes = 2 * int(lens_now.sum()) * hk * cfg.head_dim * 2 + 2 * batch * (cfg.num_heads // world) * cfg.head_dim * 3
-    reps = max(8, min(cfg.num_layers, 40))
+    reps = 20
     dec.set_inputs(*stage(0))
     torch.cuda.synchronize(dev)
 
-    def att(l):
-        ops.paged_attention(dec.q_rot, dec.key_pools[l % cfg.num_layers], dec.value_pools[l % cfg.num_layers],
-                            dec.block_tables, dec.seq_lens, scale=cfg.scale, out=dec.att, scratch=dec.att_scratch)
+    def time_attention(kpools, vpools, tables_dev):
+        def att(l):
+            ops.paged_attention(dec.q_rot, kpools[l % len(kpools)], vpools[l % len(vpools)], tables_dev, dec.seq_lens,
+                                scale=cfg.scale, out=dec.att, scratch=dec.att_scratch)
+        for l in range(3):
+            att(l)
+        torch.cuda.synchronize(dev)
+        a.record()
+        for l in range(reps):
+            att(l)
+        b.record()
+        torch.cuda.synchronize(dev)
+        return a.elapsed_time(b) / reps
 
-    for l in range(3):
-        att(l)
-    torch.cuda.synchronize(dev)
-    a.record()
-    for l in range(reps):
-        att(l)
-    b.record()
-    torch.cuda.synchronize(dev)
-    att_ms = a.elapsed_time(b) / reps
+    in_step_ms = time_attention(dec.key_pools, dec.value_pools, dec.block_tables)
+    need = np.asarray((lens_now + bs - 1) // bs, np.int64)
+    own_blocks = int(need.sum()) + 1
+    perm = 1 + np.random.default_rng(11).permutation(own_blocks - 1)
+    own_tables = np.zeros((batch, max_blocks), np.int32)
+    o = 0
+    for i in range(batch):
+        own_tables[i, :need[i]] = perm[o:o + need[i]]
+        o += int(need[i])
+    roof_k = torch.empty((own_blocks, bs, hk, cfg.head_dim), dtype=torch.bfloat16, device=dev)
+    roof_v = torch.empty_like(roof_k)
+    for pool in (roof_k, roof_v):
+        flat = pool.view(-1)
+        for o in range(0, flat.numel(), 1 << 28):
+            n = min(1 << 28, flat.numel() - o)
+            flat[o:o + n] = torch.randn((n,), device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    att_ms = time_attention([roof_k], [roof_v], torch.from_numpy(own_tables).to(dev))
+    del roof_k, roof_v
     peak, peak_kind = peaks()
     achieved = att_bytes / (att_ms / 1e3) / 1e9
     traffic = None
@@ -266,7 +288,9 @@ def run_ours(args) -> dict:
         pass
     roofline = {"kernel": "PaSliceMma+PaCombine", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind, "bytes_per_launch": att_bytes,
-                "ms_per_launch": att_ms}
+                "ms_per_launch": att_ms, "pool": "one block per (sequence, 16 positions): nothing shared",
+                "in_step_pools": {"ms_per_launch": in_step_ms, "logical_gbs": att_bytes / (in_step_ms / 1e3) / 1e9,
+                                  "aliased": bool(aliased)}}
     sb = dec.step_bytes(lens_now)
     step_gbs = (sb["weights"] + sb["kv"]) / (ms_step / 1e3) / 1e9
 
@@ -287,6 +311,105 @@ def run_ours(args) -> dict:
     if world > 1:
         torch.distributed.destroy_process_group()
     return line if rank == 0 else {}
+
+
+def _time_graph(torch, fn, reps, warm=3):
+    """Best and median device time (ms) of one CUDA-graph replay of fn()."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        b.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[0], ts[len(ts) // 2]
+
+
+def run_operator(args) -> dict:
+    """The two operators alone (single GPU): the paged-attention decode operator (bf16 Q [32, 32, 128], 8 KV heads,
+    block 16, 4096 physical blocks, permuted tables, lengths U[512, 8192], seed 1) or the int8 projection sweep
+    (N x K in {4096x4096, 14336x4096, 4096x14336, 128256x4096}, M in {1, 8, 32, 256}).  HBM GB/s on algorithmic bytes."""
+    import torch
+
+    from tlaloc_b200 import ops
+    from tlaloc_b200.attrs import parse_paged_attention
+
+    dev = torch.device("cuda", 0)
+    peak, peak_kind = peaks()
+    if args.workload == "paged_attn":
+        rng = np.random.default_rng(1)
+        B, H, Hkv, D, bs, nb, width = 32, 32, 8, 128, 16, 4096, 512
+        lens = rng.integers(512, 8193, size=B).astype(np.int32)
+        logical = 2 * int(lens.sum()) * Hkv * D * 2 + 2 * B * H * D * 2
+        g = torch.Generator(device=dev)
+        g.manual_seed(1)
+        out = {}
+        for name in ("as_configured", "no_shared_blocks"):
+            if name == "as_configured":
+                P = nb
+                tab = np.stack([rng.permutation(nb)[:width] for _ in range(B)]).astype(np.int32)
+            else:
+                need = (lens + bs - 1) // bs
+                P = int(need.sum()) + 1
+                perm = 1 + rng.permutation(P - 1)
+                tab = np.zeros((B, width), np.int32)
+                o = 0
+                for i in range(B):
+                    tab[i, :need[i]] = perm[o:o + need[i]]
+                    o += int(need[i])
+            k = torch.randn((P, bs, Hkv, D), device=dev, generator=g).to(torch.bfloat16)
+            v = torch.randn((P, bs, Hkv, D), device=dev, generator=g).to(torch.bfloat16)
+            q = torch.randn((B, H, D), device=dev, generator=g).to(torch.bfloat16)
+            tt, tl = torch.from_numpy(tab).to(dev), torch.from_numpy(lens).to(dev)
+            o_t = torch.empty((B, H, D), dtype=torch.bfloat16, device=dev)
+            scratch = ops.paged_attention_scratch(parse_paged_attention(q, k, v, tt, tl, scale=D ** -0.5), dev)
+            best, med = _time_graph(torch, lambda: ops.paged_attention(q, k, v, tt, tl, scale=D ** -0.5, out=o_t, scratch=scratch),
+                                    max(args.steps, 20))
+            out[name] = {"us": med * 1e3, "gbs": logical / med / 1e6, "best_gbs": logical / best / 1e6, "physical_blocks": P}
+            del k, v
+        head = out["no_shared_blocks"]
+        return {"metric": "paged_attention_hbm_gbs", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": max(args.steps, 20),
+                "warmup": 3, "higher_is_better": True, "data": "synthetic", "dtype": "bf16 KV and Q, f32 accumulate",
+                "config": {"workload": "paged-attention decode operator alone", "algorithmic_bytes": logical, "cases": out},
+                "roofline": {"kernel": "PaSliceMma+PaCombine", "bound": "hbm", "achieved": head["gbs"], "peak": peak,
+                             "unit": "GB/s", "frac": head["gbs"] / peak, "peak_kind": peak_kind, "traffic": None}}
+    rows = []
+    shapes, ms = [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)], (1, 8, 32, 256)
+    if args.only:  # one shape "NxKxM", for profiler captures
+        n, k, m = (int(v) for v in args.only.lower().split("x"))
+        shapes, ms = [(n, k)], (m,)
+    for (n, k) in shapes:
+        nbuf = max(4, int(400e6 // (k * n)) + 1)  # distinct weight buffers, > 3x L2 in total, visited round robin
+        ws = [torch.randint(-127, 128, (k, n), dtype=torch.int8, device=dev) for _ in range(nbuf)]
+        sc = torch.rand((n,), device=dev) * 0.019 + 0.001
+        for m in ms:
+            x = torch.randn((m, k), device=dev).to(torch.bfloat16)
+            y = torch.empty((m, n), dtype=torch.float32, device=dev)
+
+            def fn():
+                for w in ws:
+                    ops.int8_gemm(x, w, sc, out=y)
+            best, med = _time_graph(torch, fn, 10)
+            byts = k * n + 4 * n + 2 * m * k + 4 * m * n
+            rows.append({"N": n, "K": k, "M": m, "us": med / nbuf * 1e3, "gbs": byts / (med / nbuf) / 1e6,
+                         "tflops": 2.0 * m * n * k / (med / nbuf) / 1e9})
+        del ws
+    big = ([r for r in rows if r["N"] == 128256 and r["M"] == 8] or rows)[0]
+    return {"metric": "int8_projection_hbm_gbs", "value": big["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": 10, "warmup": 3,
+            "higher_is_better": True, "data": "synthetic", "dtype": "int8 weights x bf16, f32 accumulate",
+            "config": {"workload": "int8 weight-only projection sweep", "rows": rows},
+            "roofline": {"kernel": "Int8GemvKernel", "bound": "hbm", "achieved": big["gbs"], "peak": peak, "unit": "GB/s",
+                         "frac": big["gbs"] / peak, "peak_kind": peak_kind, "traffic": None}}
 
 
 def cpu_sample(cfg_kw, lens, b_sample, threads):
@@ -378,13 +501,17 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama70b", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="llama70b", choices=sorted(WORKLOADS) + ["paged_attn", "int8_proj"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; not a bench value)")
+    ap.add_argument("--only", default="", help="int8_proj: a single shape NxKxM")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.workload in ("paged_attn", "int8_proj"):
+        line = run_operator(args)
+    else:
+        line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line:
         print(json.dumps(line), flush=True)
 

@@ -50,7 +50,7 @@ def close(got, want):
 def test_integer_activations_give_the_exact_integer_dot_product(m, k, n):
     rng = np.random.default_rng(m * 7 + k + n)
     x, codes, _ = make(rng, m, k, n, x_int=True)
-    want = (x.astype(np.int64) @ codes.astype(np.int64)).astype(np.float32)  # |sum| <= 14336*8*127 < 2^24
+    want = (x.astype(np.float64) @ codes.astype(np.float64)).astype(np.float32)  # exact integers; |sum| <= 14336*8*127 < 2^24
     got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), None)
     torch.cuda.synchronize()
     assert np.array_equal(got.cpu().numpy(), want)
@@ -69,7 +69,7 @@ def test_batched_rows_on_the_tensor_core_kernel_are_exact_on_integer_activations
 
     rng = np.random.default_rng(m * 11 + k + n)
     x, codes, _ = make(rng, m, k, n, x_int=True)
-    want = (x.astype(np.int64) @ codes.astype(np.int64)).astype(np.float32)
+    want = (x.astype(np.float64) @ codes.astype(np.float64)).astype(np.float32)  # exact: every partial sum is an integer below 2^53
     scales = np.exp2(rng.integers(-8, -2, size=n)).astype(np.float32)
     res = rng.integers(-50, 50, size=(m, n)).astype(np.float32)
     got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), residual=dev(res))

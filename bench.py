@@ -309,8 +309,15 @@ def run_ours(args) -> dict:
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(cfg_kw, batch, lens_now, seconds=args.cpu_seconds)
     if world > 1:
-        torch.distributed.destroy_process_group()
-    return line if rank == 0 else {}
+        # Print first, then leave without tearing the communicator down: destroying a process group whose
+        # collectives live inside a CUDA graph blocks, and the process is about to exit anyway.
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        torch.cuda.synchronize(dev)
+        torch.distributed.barrier(group=group)
+        sys.stdout.flush()
+        os._exit(0)
+    return line
 
 
 def _time_graph(torch, fn, reps, warm=3):

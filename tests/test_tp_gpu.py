@@ -23,6 +23,6 @@ def test_two_gpu_tensor_parallel_decoder_matches_the_oracle():
         env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
                    MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
         procs.append(subprocess.Popen([sys.executable, worker], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
-    outs = [p.communicate(timeout=600)[0] for p in procs]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(o[-2000:] for o in outs)
     assert "TP2 ok" in outs[0]

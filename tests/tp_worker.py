@@ -54,9 +54,12 @@ def main():
         ids = want_tok
     assert swaps <= 2
     torch.distributed.barrier()
+    torch.cuda.synchronize(dev)
     if rank == 0:
-        print(f"TP{world} ok: worst logit |d| {worst:.2e}, near-tie swaps {swaps}")
-    torch.distributed.destroy_process_group()
+        print(f"TP{world} ok: worst logit |d| {worst:.2e}, near-tie swaps {swaps}", flush=True)
+    # No destroy_process_group(): it blocks while a CUDA graph still holds the captured collectives.
+    sys.stdout.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":

@@ -32,11 +32,43 @@ __device__ __forceinline__ float BlockSum(float v, float* red)
 
 // One CTA per row: x * rsqrt(mean(x^2) + eps) * gain.  mean = sum / n, rsqrt in double then narrowed, and the two
 // multiplies kept separate, as the interpreter evaluates the graph's nodes (DxirInterpreter.kt:567-572,1791-1807).
+// Rows of up to 8192 values (a multiple of 4) are read once with 16-byte loads, all in flight together, and kept
+// in registers for the second pass; other rows take the two-pass loop.
 template <typename OT>
 __global__ void __launch_bounds__(256) RmsNormKernel(const float* x, const float* gain, OT* out, int n, float eps)
 {
   __shared__ float red[8];
   const float* xr = x + static_cast<size_t>(blockIdx.x) * n;
+  OT* o = out + static_cast<size_t>(blockIdx.x) * n;
+  if ((n & 3) == 0 && n <= 8192 && (reinterpret_cast<uintptr_t>(xr) & 15) == 0) {
+    const int n4 = n >> 2;
+    float4 v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int j = threadIdx.x + i * 256;
+      v[i] = j < n4 ? reinterpret_cast<const float4*>(xr)[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, ss))));
+    ss = BlockSum(ss, red);
+    const float rsq = static_cast<float>(1.0 / sqrt(static_cast<double>(ss / static_cast<float>(n) + eps)));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int j = threadIdx.x + i * 256;
+      if (j < n4) {
+        float4 g = gain != nullptr ? reinterpret_cast<const float4*>(gain)[j] : make_float4(1.f, 1.f, 1.f, 1.f);
+        const float a = __fmul_rn(v[i].x, rsq), b = __fmul_rn(v[i].y, rsq), c = __fmul_rn(v[i].z, rsq), d = __fmul_rn(v[i].w, rsq);
+        const float r0 = gain != nullptr ? __fmul_rn(a, g.x) : a, r1 = gain != nullptr ? __fmul_rn(b, g.y) : b;
+        const float r2 = gain != nullptr ? __fmul_rn(c, g.z) : c, r3 = gain != nullptr ? __fmul_rn(d, g.w) : d;
+        o[4 * j] = FromF32<OT>(r0);
+        o[4 * j + 1] = FromF32<OT>(r1);
+        o[4 * j + 2] = FromF32<OT>(r2);
+        o[4 * j + 3] = FromF32<OT>(r3);
+      }
+    }
+    return;
+  }
   float ss = 0.f;
   for (int j = threadIdx.x; j < n; j += blockDim.x) {
     const float v = xr[j];
@@ -45,7 +77,6 @@ __global__ void __launch_bounds__(256) RmsNormKernel(const float* x, const float
   ss = BlockSum(ss, red);
   const float mean = ss / static_cast<float>(n);
   const float rsq = static_cast<float>(1.0 / sqrt(static_cast<double>(mean + eps)));
-  OT* o = out + static_cast<size_t>(blockIdx.x) * n;
   for (int j = threadIdx.x; j < n; j += blockDim.x) {
     float v = __fmul_rn(xr[j], rsq);
     if (gain != nullptr) v = __fmul_rn(v, gain[j]);

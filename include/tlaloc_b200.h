@@ -228,6 +228,38 @@ int tlaloc_b200_swiglu(const float* gate, const float* up, int32_t ld, void* out
 /* Greedy NEXT_TOKEN (DxirInterpreter.kt:2414-2426; triton/kernels/sample.cu greedy arm): first index of the maximum. */
 int tlaloc_b200_argmax(const float* logits, int32_t* out, int32_t rows, int32_t n, void* stream);
 
+/* ------------------------------------------------------------------ tensor parallelism: the sum over ranks */
+
+#define TLALOC_B200_MAX_PEERS 8
+#define TLALOC_B200_IPC_HANDLE_BYTES 64
+
+/*
+ * Peer-mapped device memory, one process per GPU.  tlaloc_b200_peer_alloc makes `bytes` of zeroed device memory on the
+ * current device and an opaque 64-byte handle; the handle travels to the other ranks over any host channel, and
+ * tlaloc_b200_peer_open maps that rank's buffer into this process (peer access over NVLink is enabled on first use).
+ * _peer_close unmaps, _peer_free releases the owner's allocation once every peer has closed it.
+ */
+int tlaloc_b200_peer_alloc(size_t bytes, void** ptr, unsigned char handle[TLALOC_B200_IPC_HANDLE_BYTES]);
+int tlaloc_b200_peer_open(const unsigned char handle[TLALOC_B200_IPC_HANDLE_BYTES], void** ptr);
+int tlaloc_b200_peer_close(void* ptr);
+int tlaloc_b200_peer_free(void* ptr);
+
+/*
+ * In-place sum over `world` ranks of `count` f32 values, the `stablehlo.all_reduce` with an add region that follows
+ * the row-parallel o_proj and down_proj (stablehlo/.../StablehloEmitter.kt:3048-3072; semantics checked by
+ * stablehlo/src/jvmTest/.../MultiDeviceCpuTest.kt:35-46).  One kernel per rank, all ranks launching the same call in
+ * the same order: reduce-scatter by peer loads, all-gather by peer stores, flag words in the same peer-mapped buffer.
+ *   bases[q]     device address, in THIS process, of rank q's peer buffer (bases[rank] is the local one); host array
+ *   data_offset  byte offset of the values inside every buffer (multiple of 16)
+ *   flag_offset  byte offset of 2 * world u32 flag words inside every buffer, zero before the first call
+ *   state        4 u32 words of LOCAL device memory, zero before the first call: [0] all-reduces finished,
+ *                [2] status (0, or 1 + 16 * phase + the rank that did not arrive within the time limit; once set,
+ *                later calls do not wait).  The sums are added in rank order: every rank gets identical bits.
+ * count must be a multiple of 4.  world == 1 is a no-op.
+ */
+int tlaloc_b200_peer_allreduce_f32(void* const* bases, size_t data_offset, size_t flag_offset, uint32_t* state,
+                                   int32_t rank, int32_t world, size_t count, void* stream);
+
 /* ------------------------------------------------------------------ XLA typed-FFI registration */
 
 struct PJRT_Api;

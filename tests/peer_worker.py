@@ -1,0 +1,76 @@
+"""Child process of tests/test_tp_gpu.py: one rank of the peer-memory sum (csrc/peer_allreduce.cu), checked against
+the sum of the ranks' inputs added in rank order, eagerly and replayed from a CUDA graph."""
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def rank_input(shape, rank, round_):
+    rng = np.random.default_rng(1000 * round_ + rank)
+    return (rng.standard_normal(shape) * 10.0 ** rng.integers(-3, 4)).astype(np.float32)
+
+
+def main():
+    from tlaloc_b200.peer import PeerBuffers
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    torch.distributed.init_process_group("nccl", device_id=dev)
+    shapes = [(4, 256), (128, 8192), (3, 4), (1, 131076)]  # the last: slices that do not divide evenly into 16-byte units
+    peer = PeerBuffers(shapes, rank=rank, world=world, group=torch.distributed.group.WORLD, device=dev)
+
+    def expected(shape, round_):
+        acc = rank_input(shape, 0, round_)
+        for q in range(1, world):
+            acc = acc + rank_input(shape, q, round_)  # f32 adds in rank order, as the kernel does
+        return acc
+
+    round_ = 0
+    for _ in range(3):
+        for i, shape in enumerate(shapes):
+            round_ += 1
+            peer.tensors[i].copy_(torch.from_numpy(rank_input(shape, rank, round_)))
+            out = peer.all_reduce_(i)
+            assert np.array_equal(out.cpu().numpy(), expected(shape, round_)), (i, round_)
+    # the same launches captured in a CUDA graph and replayed: 20 sums back to back on the two big buffers
+    src = [torch.empty(s, device=dev) for s in shapes]
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        for i in (0, 1):
+            peer.tensors[i].copy_(src[i])
+            peer.all_reduce_(i)
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    torch.distributed.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(10):
+            for i in (0, 1):
+                peer.tensors[i].copy_(src[i])
+                peer.all_reduce_(i)
+    for rep in range(3):
+        round_ += 1
+        for i in (0, 1):
+            src[i].copy_(torch.from_numpy(rank_input(shapes[i], rank, round_)))
+        graph.replay()
+        for i in (0, 1):
+            assert np.array_equal(peer.tensors[i].cpu().numpy(), expected(shapes[i], round_)), (i, rep)
+    assert peer.status() == 0
+    assert int(peer.state[0].item()) == 3 * len(shapes) + 2 + 3 * 20
+    torch.distributed.barrier()
+    torch.cuda.synchronize(dev)
+    if rank == 0:
+        print("peer sum ok", flush=True)
+    sys.stdout.flush()
+    os._exit(0)  # no process-group teardown over a live CUDA graph
+
+
+if __name__ == "__main__":
+    main()

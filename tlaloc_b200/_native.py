@@ -42,6 +42,11 @@ _SIGNATURES = {
     "tlaloc_b200_rope_kv_write": (ctypes.c_int, [_vp] * 8 + [_i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_swiglu": (ctypes.c_int, [_vp, _vp, _i32, _vp, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_argmax": (ctypes.c_int, [_vp, _vp, _i32, _i32, _vp]),
+    "tlaloc_b200_peer_alloc": (ctypes.c_int, [_sz, ctypes.POINTER(_vp), ctypes.c_char_p]),
+    "tlaloc_b200_peer_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
+    "tlaloc_b200_peer_close": (ctypes.c_int, [_vp]),
+    "tlaloc_b200_peer_free": (ctypes.c_int, [_vp]),
+    "tlaloc_b200_peer_allreduce_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _vp, _i32, _i32, _sz, _vp]),
     "TlalocRegisterKernels": (ctypes.c_char_p, [_vp]),
     "tlaloc_b200_ffi_handler": (_vp, [ctypes.c_char_p]),
 }

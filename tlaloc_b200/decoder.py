@@ -9,17 +9,20 @@ CUDA graph and (for tensor parallelism) the NCCL communicator.  There is no CPU 
 
 Per layer the step launches: rmsnorm, fused q|k|v projection, rope + KV write, attention slice + combine,
 o projection (+ residual), rmsnorm, fused gate|up projection, swiglu, down projection (+ residual); with
-tensor parallelism an all-reduce follows the o and down projections.  The whole step is captured once into a
-CUDA graph and replayed.
+tensor parallelism a sum over the ranks follows the o and down projections: one kernel per rank that reduce-scatters
+by peer loads and all-gathers by peer stores over NVLink (peer.py, csrc/peer_allreduce.cu).  The whole step is
+captured once into a CUDA graph and replayed.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import numpy as np
 import torch
 
 from . import ops, sharding
+from .peer import PeerBuffers
 
 
 @dataclass
@@ -90,8 +93,15 @@ class Decoder:
         self.slot_mapping = torch.full((B,), -1, **i32)
         # step buffers
         nqkv = (self.hq + 2 * self.hk) * hd
-        self.h = torch.empty((B, d), **f32)
-        self.h2 = torch.empty((B, d), **f32)
+        # the two residual-stream buffers; under tensor parallelism they live in peer-mapped memory and are summed by
+        # the library's own exchange kernel (TLALOC_B200_TP_REDUCE=nccl keeps them private and calls NCCL instead)
+        self.peer = None
+        if world > 1 and os.environ.get("TLALOC_B200_TP_REDUCE", "peer") == "peer":
+            self.peer = PeerBuffers([(B, d), (B, d)], rank=rank, world=world, group=group, device=dev)
+            self.h, self.h2 = self.peer.tensors
+        else:
+            self.h = torch.empty((B, d), **f32)
+            self.h2 = torch.empty((B, d), **f32)
         self.hn = torch.empty((B, d), **bf)
         self.qkv = torch.empty((B, nqkv), **f32)
         self.q_rot = torch.empty((B, self.hq, hd), **f32)
@@ -169,7 +179,11 @@ class Decoder:
             dst.copy_(src.reshape(dst.shape), non_blocking=True)
 
     def _all_reduce(self, x: torch.Tensor) -> None:
-        if self.world > 1:
+        if self.world == 1:
+            return
+        if self.peer is not None:
+            self.peer.all_reduce_(0 if x is self.h else 1)
+        else:
             torch.distributed.all_reduce(x, group=self.group)
 
     def _run_step(self) -> None:

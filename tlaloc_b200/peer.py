@@ -1,0 +1,100 @@
+"""Peer-mapped step buffers and the in-place sum over tensor-parallel ranks (one process per GPU).
+
+The reference leaves the `stablehlo.all_reduce` after o_proj and down_proj to XLA
+(stablehlo/.../StablehloEmitter.kt:3048-3072).  Here each rank allocates ONE device buffer that holds the tensors to be
+summed plus the flag words, every rank maps every other rank's buffer (CUDA IPC handles exchanged over the process
+group), and `PeerBuffers.all_reduce_(i)` launches the library's one-kernel exchange (csrc/peer_allreduce.cu) on the
+current stream.  The launch has no host synchronisation, so it can be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _native as N
+
+_ALIGN = 256
+
+
+class _DeviceSpan:
+    """A raw device address range, exposed to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, words: int):
+        self.__cuda_array_interface__ = {"shape": (words,), "typestr": "<f4", "data": (ptr, False), "version": 3}
+
+
+class PeerBuffers:
+    """`shapes` f32 tensors living in a buffer every rank of `group` can read and write, with `all_reduce_` over them.
+
+    All ranks must construct it with the same shapes (a collective: handles are all-gathered), call `all_reduce_`
+    in the same order, and `close()` it together.
+    """
+
+    def __init__(self, shapes, *, rank: int, world: int, group=None, device="cuda:0"):
+        if not 1 <= world <= 8:
+            raise ValueError(f"world {world} outside [1, 8]")
+        self.rank, self.world, self.group, self.device = rank, world, group, torch.device(device)
+        self.offsets, off = [], 0
+        for shp in shapes:
+            n = int(np.prod(shp))
+            if n % 4:
+                raise ValueError(f"a summed tensor needs a multiple of 4 elements, got shape {tuple(shp)}")
+            self.offsets.append(off)
+            off += (4 * n + _ALIGN - 1) // _ALIGN * _ALIGN
+        self.flag_offset = off
+        self.nbytes = off + _ALIGN
+        lib = N.lib()
+        torch.cuda.set_device(self.device)
+        local, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        N.check(lib.tlaloc_b200_peer_alloc(self.nbytes, ctypes.byref(local), handle))
+        self._local = local.value
+        handles = [None] * world
+        if world > 1:
+            torch.distributed.all_gather_object(handles, handle.raw, group=group)
+        else:
+            handles[0] = handle.raw
+        self._bases = (ctypes.c_void_p * world)()
+        self._opened = []
+        for q in range(world):
+            if q == rank:
+                self._bases[q] = self._local
+                continue
+            p = ctypes.c_void_p()
+            N.check(lib.tlaloc_b200_peer_open(handles[q], ctypes.byref(p)))
+            self._bases[q] = p.value
+            self._opened.append(p.value)
+        whole = torch.as_tensor(_DeviceSpan(self._local, self.nbytes // 4), device=self.device)
+        self.tensors = [whole[o // 4:o // 4 + int(np.prod(s))].view(*s) for o, s in zip(self.offsets, shapes)]
+        self.state = torch.zeros((4,), dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        if world > 1:
+            torch.distributed.barrier(group=group)  # every rank has mapped every buffer before the first exchange
+
+    def all_reduce_(self, index: int) -> torch.Tensor:
+        """Sum tensor `index` over the ranks, in place, on the current stream; every rank ends with identical bits."""
+        t = self.tensors[index]
+        N.check(N.lib().tlaloc_b200_peer_allreduce_f32(self._bases, self.offsets[index], self.flag_offset,
+                                                       self.state.data_ptr(), self.rank, self.world, t.numel(),
+                                                       torch.cuda.current_stream(self.device).cuda_stream))
+        return t
+
+    def status(self) -> int:
+        """0, or the code a timed-out wait left (1 + 16 * phase + the rank that did not arrive).  Synchronises."""
+        return int(self.state[2].item())
+
+    def close(self) -> None:
+        """Unmap the peers' buffers, then (after a barrier) free the local one.  The tensors must not be used after."""
+        if self._local is None:
+            return
+        torch.cuda.synchronize(self.device)
+        lib = N.lib()
+        for p in self._opened:
+            lib.tlaloc_b200_peer_close(p)
+        self._opened = []
+        if self.world > 1:
+            torch.distributed.barrier(group=self.group)
+        self.tensors = []
+        lib.tlaloc_b200_peer_free(self._local)
+        self._local = None

@@ -17,11 +17,14 @@
 //                   each an independent cp.async pipeline over its own 16-position
 //                   groups (16-byte coalesced copies of each position's 2*D-byte row,
 //                   gathered through the block table, XOR-swizzled in shared memory);
-//                   Q.K^T and P.V on mma.sync m16n8k16 bf16 with fp32 accumulators, the
-//                   probabilities (and an f32 query) carried as hi + lo bf16 parts so
-//                   the result keeps ~16 bits; warp-shuffle online softmax in the log2
-//                   domain.  HBM-bound: the tensor work is two to three small MMAs per
-//                   position, far below what the SM can issue while the copies land.
+//                   the 16 positions of a group are the M rows of mma.sync m16n8k16 bf16
+//                   (S = K.Q^T with Q^T held in registers as B fragments for the whole
+//                   slice; O^T += V^T.P with P moved between fragment layouts by
+//                   movmatrix), the queries the N columns, fp32 accumulators; the
+//                   probabilities (and an f32 query) are carried as hi + lo bf16 parts so
+//                   the result keeps ~16 bits; online softmax in the log2 domain.
+//                   HBM-bound once the per-group instruction count is low enough: with the
+//                   queries as M rows the kernel was bound by instruction issue instead.
 //   PaSliceGeneric  any D <= 256, any block size, f32 or bf16 pools, keep masks, up to
 //                   any number of queries (in passes of 8): plain fp32 FMA, warp per
 //                   position for the scores and thread per head dimension for the values.

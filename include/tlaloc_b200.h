@@ -183,6 +183,9 @@ size_t tlaloc_b200_int8_gemm_scratch_bytes(int32_t m, int32_t k, int32_t n);
  */
 #define TLALOC_B200_GEMM_EXACT 1
 #define TLALOC_B200_GEMM_X_F32_EXACT 2 /* with GEMM_EXACT: do not round an F32 x to bf16 (weight dtype F32) */
+/* codes and scales are constants of the program: no kernel placed just before this call in the stream writes them.
+ * Lets the batched-row kernel request its first weights while that kernel is still finishing (results are the same). */
+#define TLALOC_B200_GEMM_WEIGHTS_CONST 4
 int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_t* codes, const float* scales,
                           const float* residual, void* y, int32_t y_dtype, float* scratch, size_t scratch_bytes,
                           int32_t m, int32_t k, int32_t n, int32_t flags, void* stream);

@@ -12,7 +12,7 @@ from . import build as _build
 
 F32, BF16, S8, S32 = 11, 16, 2, 4
 OK, INVALID_ARGUMENT, UNSUPPORTED, INTERNAL = 0, -1, -2, -3
-GEMM_EXACT, GEMM_X_F32_EXACT = 1, 2
+GEMM_EXACT, GEMM_X_F32_EXACT, GEMM_WEIGHTS_CONST = 1, 2, 4
 
 _lib = None
 

@@ -54,6 +54,52 @@ __device__ __forceinline__ __nv_bfloat16 FromF32<__nv_bfloat16>(float x) { retur
 // Kernels launched by this library since it was loaded (tlaloc_b200_launch_count); a plain statistic.
 void CountLaunches(int n);
 
+// Programmatic dependent launch.  A decode step is ~800 small launches in one stream, and the gap between a kernel's
+// last CTA and the next kernel's first one is a few microseconds each.  Every kernel of the library is launched with
+// the programmatic-serialization attribute and starts with GridDependencySync(): the kernel may be scheduled (and run
+// whatever comes before that call: shared-memory carve-up, mbarrier and TMEM setup) while its predecessor drains, and
+// the call then waits until the predecessor grid has COMPLETED and its writes are visible.  So no global memory is
+// read or written before it, and correctness is exactly that of plain stream order.  The trigger for the kernel's
+// own successors is issued right after the wait, never before it, so at most one kernel is ever waiting behind a
+// running one.  A launch without the attribute (another library's kernel, $TLALOC_B200_PDL=0) makes the call a no-op.
+__device__ __forceinline__ void GridDependencySync()
+{
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+bool PdlEnabled();
+// The launch attributes every kernel gets; `attrs` must have room for 2.  Returns the count.
+inline int ChainAttributes(cudaLaunchAttribute* attrs, int cluster_y = 0)
+{
+  int n = 0;
+  if (cluster_y > 0) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = 1;
+    attrs[n].val.clusterDim.y = static_cast<unsigned>(cluster_y);
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (PdlEnabled()) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  return n;
+}
+template <typename... KArgs, typename... Args>
+cudaError_t LaunchChained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args)
+{
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attrs[2];
+  cfg.numAttrs = ChainAttributes(attrs);
+  cfg.attrs = attrs;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Once-per-process kernel attribute setup (dynamic shared memory opt-in) of each
 // translation unit; called from tlaloc_b200_init and from the typed-FFI
 // handlers' INITIALIZE stage, so that no launch inside a CUDA graph capture
@@ -64,7 +110,7 @@ cudaError_t PrepareInt8GemmTcKernels();
 
 // The tensor-core projection (int8_gemm_tc.cu): rows [0, m) of y = (x @ codes) * scales (+ residual), x bf16.
 cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const float* scales, const float* residual,
-                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches);
+                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches, bool weights_const);
 // 1 if a bounded device-side wait has timed out since the last call (synchronous read), 0 if not, -1 on a CUDA error.
 int ReadTcStatus();
 

@@ -10,6 +10,7 @@ namespace {
 template <typename TT>
 __global__ void EmbeddingKernel(const TT* table, const int* ids, float* out, int vocab, int dim)
 {
+  GridDependencySync();
   const int p = blockIdx.x;
   int v = __ldg(ids + p);
   v = v < 0 ? 0 : (v >= vocab ? vocab - 1 : v);
@@ -37,6 +38,7 @@ __device__ __forceinline__ float BlockSum(float v, float* red)
 template <typename OT>
 __global__ void __launch_bounds__(256) RmsNormKernel(const float* x, const float* gain, OT* out, int n, float eps)
 {
+  GridDependencySync();
   __shared__ float red[8];
   const float* xr = x + static_cast<size_t>(blockIdx.x) * n;
   OT* o = out + static_cast<size_t>(blockIdx.x) * n;
@@ -93,6 +95,7 @@ __global__ void RopeKvWriteKernel(const float* q, const float* k, const float* v
                                   KVT* vc, int H, int Hkv, int hd, int num_slots, int max_pos, int ldq, int ldk,
                                   int ldv)
 {
+  GridDependencySync();
   const int t = blockIdx.x, hs = blockIdx.y;
   const int half = hd >> 1;
   int pos = __ldg(positions + t);
@@ -129,6 +132,7 @@ __global__ void RopeKvWriteKernel(const float* q, const float* k, const float* v
 template <typename OT>
 __global__ void SwigluKernel(const float* gate, const float* up, int ld, OT* out, int rows, int n)
 {
+  GridDependencySync();
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= static_cast<size_t>(rows) * n) return;
   const int r = static_cast<int>(i / n), c = static_cast<int>(i - static_cast<size_t>(r) * n);
@@ -140,6 +144,7 @@ __global__ void SwigluKernel(const float* gate, const float* up, int ld, OT* out
 // One CTA per row; the first index of the maximum wins (DxirInterpreter.kt:2414-2426).
 __global__ void __launch_bounds__(256) ArgmaxKernel(const float* x, int* out, int n)
 {
+  GridDependencySync();
   __shared__ float bv[8];
   __shared__ int bi[8];
   const float* xr = x + static_cast<size_t>(blockIdx.x) * n;
@@ -192,12 +197,12 @@ extern "C" int tlaloc_b200_embedding(const void* table, int32_t table_dtype, con
   if (positions < 0 || vocab < 1 || dim < 1) return Fail(kInvalid, "EMBEDDING: bad sizes");
   if (positions == 0) return kOk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
   if (table_dtype == TLALOC_B200_F32) {
-    EmbeddingKernel<<<positions, 256, 0, st>>>(static_cast<const float*>(table), ids, out, vocab, dim);
+    e = LaunchChained(EmbeddingKernel<float>, positions, 256, 0, st, static_cast<const float*>(table), ids, out, vocab, dim);
   } else {
-    EmbeddingKernel<<<positions, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(table), ids, out, vocab, dim);
+    e = LaunchChained(EmbeddingKernel<__nv_bfloat16>, positions, 256, 0, st, static_cast<const __nv_bfloat16*>(table), ids, out, vocab, dim);
   }
-  const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return CudaFail("EMBEDDING launch", e);
   CountLaunches(1);
   return kOk;
@@ -211,12 +216,12 @@ extern "C" int tlaloc_b200_rmsnorm(const float* x, const float* gain, void* out,
   if (rows < 0 || n < 1) return Fail(kInvalid, "RMSNORM: bad sizes");
   if (rows == 0) return kOk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
   if (out_dtype == TLALOC_B200_F32) {
-    RmsNormKernel<<<rows, 256, 0, st>>>(x, gain, static_cast<float*>(out), n, eps);
+    e = LaunchChained(RmsNormKernel<float>, rows, 256, 0, st, x, gain, static_cast<float*>(out), n, eps);
   } else {
-    RmsNormKernel<<<rows, 256, 0, st>>>(x, gain, static_cast<__nv_bfloat16*>(out), n, eps);
+    e = LaunchChained(RmsNormKernel<__nv_bfloat16>, rows, 256, 0, st, x, gain, static_cast<__nv_bfloat16*>(out), n, eps);
   }
-  const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return CudaFail("RMSNORM launch", e);
   CountLaunches(1);
   return kOk;
@@ -245,17 +250,17 @@ extern "C" int tlaloc_b200_rope_kv_write(const float* q, const float* k, const f
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const dim3 grid(num_tokens, num_heads + 2 * num_kv_heads);
   const int threads = head_dim >= 128 ? 128 : 64;
+  cudaError_t e;
 #define TLALOC_LAUNCH(QT, KVT)                                                                                      \
-  RopeKvWriteKernel<<<grid, threads, 0, st>>>(q, k, v, positions, cos_table, sin_table, slot_mapping,               \
-                                              static_cast<QT*>(q_out), static_cast<KVT*>(key_cache),                \
-                                              static_cast<KVT*>(value_cache), num_heads, num_kv_heads, head_dim,    \
-                                              num_slots, max_pos, ld_q, ld_k, ld_v)
+  e = LaunchChained(RopeKvWriteKernel<QT, KVT>, grid, threads, 0, st, q, k, v, positions, cos_table, sin_table,     \
+                    slot_mapping, static_cast<QT*>(q_out), static_cast<KVT*>(key_cache),                           \
+                    static_cast<KVT*>(value_cache), num_heads, num_kv_heads, head_dim, num_slots, max_pos, ld_q,   \
+                    ld_k, ld_v)
   if (q_out_dtype == TLALOC_B200_F32 && kv_dtype == TLALOC_B200_F32) TLALOC_LAUNCH(float, float);
   else if (q_out_dtype == TLALOC_B200_F32) TLALOC_LAUNCH(float, __nv_bfloat16);
   else if (kv_dtype == TLALOC_B200_F32) TLALOC_LAUNCH(__nv_bfloat16, float);
   else TLALOC_LAUNCH(__nv_bfloat16, __nv_bfloat16);
 #undef TLALOC_LAUNCH
-  const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return CudaFail("ROPE_KV_WRITE launch", e);
   CountLaunches(1);
   return kOk;
@@ -271,12 +276,12 @@ extern "C" int tlaloc_b200_swiglu(const float* gate, const float* up, int32_t ld
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t total = static_cast<size_t>(rows) * n;
   const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  cudaError_t e;
   if (out_dtype == TLALOC_B200_F32) {
-    SwigluKernel<<<blocks, 256, 0, st>>>(gate, up, ld, static_cast<float*>(out), rows, n);
+    e = LaunchChained(SwigluKernel<float>, blocks, 256, 0, st, gate, up, ld, static_cast<float*>(out), rows, n);
   } else {
-    SwigluKernel<<<blocks, 256, 0, st>>>(gate, up, ld, static_cast<__nv_bfloat16*>(out), rows, n);
+    e = LaunchChained(SwigluKernel<__nv_bfloat16>, blocks, 256, 0, st, gate, up, ld, static_cast<__nv_bfloat16*>(out), rows, n);
   }
-  const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return CudaFail("SWIGLU launch", e);
   CountLaunches(1);
   return kOk;
@@ -287,8 +292,7 @@ extern "C" int tlaloc_b200_argmax(const float* logits, int32_t* out, int32_t row
   if (!logits || !out) return Fail(kInvalid, "ARGMAX: a required device pointer is null");
   if (rows < 0 || n < 1) return Fail(kInvalid, "ARGMAX: bad sizes");
   if (rows == 0) return kOk;
-  ArgmaxKernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(logits, out, n);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = LaunchChained(ArgmaxKernel, rows, 256, 0, static_cast<cudaStream_t>(stream), logits, out, n);
   if (e != cudaSuccess) return CudaFail("ARGMAX launch", e);
   CountLaunches(1);
   return kOk;

@@ -273,6 +273,17 @@ AbiFfiError* KvCacheWriteHandler(AbiFfiCallFrame* frame)
 
 using namespace tlaloc_b200;
 
+namespace tlaloc_b200 {
+bool PdlEnabled()
+{
+  static const bool on = [] {
+    const char* e = std::getenv("TLALOC_B200_PDL");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  return on;
+}
+}  // namespace tlaloc_b200
+
 extern "C" int tlaloc_b200_abi_version(void) { return TLALOC_B200_ABI_VERSION; }
 
 extern "C" const char* tlaloc_b200_last_error(void) { return ErrorBuffer(); }

@@ -108,6 +108,7 @@ struct GvLayout {
 template <int NT, typename YT>
 __global__ void __launch_bounds__(kGvThreads) Int8GemvKernel(GemmParams p)
 {
+  GridDependencySync();
   using L = GvLayout<NT>;
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -276,6 +277,7 @@ __global__ void __launch_bounds__(kGvThreads) Int8GemvKernel(GemmParams p)
 template <typename XT>
 __global__ void ToBf16Kernel(const XT* x, __nv_bfloat16* out, size_t n)
 {
+  GridDependencySync();
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) out[i] = __float2bfloat16_rn(ToF32(x[i]));
 }
@@ -287,6 +289,7 @@ __global__ void __launch_bounds__(256) GemmExactKernel(const XT* x, const WT* w,
                                                        const float* residual, YT* y, int M, int K, int N,
                                                        int round_x)
 {
+  GridDependencySync();
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   const int i = blockIdx.y;
   if (j >= N) return;
@@ -316,13 +319,9 @@ cudaError_t LaunchGemv(const GemmParams& p, cudaStream_t stream)
   cfg.blockDim = dim3(kGvThreads, 1, 1);
   cfg.dynamicSmemBytes = GvLayout<NT>::kBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = p.ks;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  cfg.numAttrs = ChainAttributes(attr, p.ks);
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, Int8GemvKernel<NT, YT>, p);
 }
 
@@ -385,13 +384,11 @@ cudaError_t LaunchExact(const void* x, const void* w, const float* scales, const
 {
   const dim3 grid((n + 255) / 256, m);
   if (y_dtype == TLALOC_B200_F32) {
-    GemmExactKernel<<<grid, 256, 0, st>>>(static_cast<const XT*>(x), static_cast<const WT*>(w), scales, residual,
-                                          static_cast<float*>(y), m, k, n, round_x);
-  } else {
-    GemmExactKernel<<<grid, 256, 0, st>>>(static_cast<const XT*>(x), static_cast<const WT*>(w), scales, residual,
-                                          static_cast<__nv_bfloat16*>(y), m, k, n, round_x);
+    return LaunchChained(GemmExactKernel<XT, WT, float>, grid, 256, 0, st, static_cast<const XT*>(x),
+                         static_cast<const WT*>(w), scales, residual, static_cast<float*>(y), m, k, n, round_x);
   }
-  return cudaGetLastError();
+  return LaunchChained(GemmExactKernel<XT, WT, __nv_bfloat16>, grid, 256, 0, st, static_cast<const XT*>(x),
+                       static_cast<const WT*>(w), scales, residual, static_cast<__nv_bfloat16*>(y), m, k, n, round_x);
 }
 
 template <typename YT>
@@ -441,9 +438,8 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
       return Fail(kInvalid, "%s: an f32 x needs %zu bytes of scratch for its bf16 copy, got %zu", op, need, scratch_bytes);
     }
     const size_t count = static_cast<size_t>(m) * k;
-    ToBf16Kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, st>>>(static_cast<const float*>(x),
-                                                                            reinterpret_cast<__nv_bfloat16*>(scratch), count);
-    e = cudaGetLastError();
+    e = LaunchChained(ToBf16Kernel<float>, static_cast<unsigned>((count + 255) / 256), 256, 0, st,
+                      static_cast<const float*>(x), reinterpret_cast<__nv_bfloat16*>(scratch), count);
     if (e != cudaSuccess) return CudaFail("INT8_PROJ activation cast", e);
     CountLaunches(1);
     xb = reinterpret_cast<const __nv_bfloat16*>(scratch);
@@ -456,7 +452,8 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
     e = PrepareInt8GemmTcKernels();
     if (e != cudaSuccess) return CudaFail("INT8_PROJ set-up", e);
     int launches = 0;
-    e = LaunchInt8GemmTc(xb, codes, scales, residual, y, y_dtype, m, k, n, st, &launches);
+    e = LaunchInt8GemmTc(xb, codes, scales, residual, y, y_dtype, m, k, n, st, &launches,
+                         (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0);
     if (e != cudaSuccess) return CudaFail("INT8_PROJ tensor-core launch", e);
     CountLaunches(launches);
     return kOk;

@@ -43,6 +43,7 @@ struct TcParams {
   void* y;
   int M, K, N;
   int Kc, ks;
+  int weights_const;  // codes and scales are not written by the preceding kernel: fetch them before the dependency wait
 };
 
 constexpr int kTcThreads = 512;                    // converter threads (16 warps)
@@ -71,10 +72,13 @@ struct TcLayout {
   static constexpr int kChunks = kTcBK / kRowsPerPass;        // 16-code chunks per thread per block
   static constexpr int kXRowsPerPass = kGroupThreads / 8;     // activation rows a group's threads cover with one copy each
   static constexpr int kWOffset = kBufs * kXBytes;
-  static constexpr int kBarOffset = kWOffset + kBufs * kTcWBytes;  // mma_done[kBufs], conv_done[kBufs], then the TMEM base
-  static constexpr int kPipeBytes = kBarOffset + 128;
-  static constexpr int kTileBytes = MPAD <= 128 ? MPAD * kTcTileStride * 4 : 0;  // cluster reduction tile (aliases the pipeline)
-  static constexpr int kBytes = (kPipeBytes > kTileBytes ? kPipeBytes : kTileBytes) + 1024;  // slack to align to 1024
+  static constexpr int kPipeEnd = kWOffset + kBufs * kTcWBytes;
+  static constexpr int kTileRows = MPAD < 128 ? MPAD : 128;
+  static constexpr int kTileBytes = kTileRows * kTcTileStride * 4;  // epilogue tile of one accumulator; aliases the pipeline
+  // mma_done[kBufs], conv_done[kBufs], the TMEM base, then the tile's 256 scales: past both the pipeline and the tile
+  static constexpr int kBarOffset = (kPipeEnd > kTileBytes ? kPipeEnd : kTileBytes + 15) / 16 * 16;
+  static constexpr int kScaleOffset = kBarOffset + 128;
+  static constexpr int kBytes = kScaleOffset + kTcBN * 4 + 1024;  // slack to align to 1024
   static constexpr int kAccs = MPAD > 128 ? 2 : 1;  // accumulators of 128 activation rows x 256 columns
   static constexpr int kTmemCols = kAccs * kTcBN;
   static_assert(kXBytes % 1024 == 0, "operand tiles start on 1024-byte boundaries");
@@ -175,37 +179,74 @@ __device__ __forceinline__ void TcCommit(uint32_t bar)
 {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void TcLd8(uint32_t taddr, uint32_t (&r)[8])
+__device__ __forceinline__ void TcLd32(uint32_t taddr, uint32_t* r)
 {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr));
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
 }
-
-// Eight consecutive outputs of one row; 16-byte stores when the address allows.
-__device__ __forceinline__ void StoreRow8(float* dst, const float (&o)[8])
+// Four consecutive outputs of one row.
+__device__ __forceinline__ void StoreRow4(float* dst, float4 v, bool vec)
 {
-  if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-    reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
-    reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
+  if (vec) {
+    *reinterpret_cast<float4*>(dst) = v;
   } else {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) dst[e] = o[e];
+    dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
   }
 }
-__device__ __forceinline__ void StoreRow8(__nv_bfloat16* dst, const float (&o)[8])
+__device__ __forceinline__ void StoreRow4(__nv_bfloat16* dst, float4 v, bool vec)
 {
-  if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-    uint4 v;
-    __nv_bfloat162 h;
-    h = __floats2bfloat162_rn(o[0], o[1]); v.x = *reinterpret_cast<uint32_t*>(&h);
-    h = __floats2bfloat162_rn(o[2], o[3]); v.y = *reinterpret_cast<uint32_t*>(&h);
-    h = __floats2bfloat162_rn(o[4], o[5]); v.z = *reinterpret_cast<uint32_t*>(&h);
-    h = __floats2bfloat162_rn(o[6], o[7]); v.w = *reinterpret_cast<uint32_t*>(&h);
-    *reinterpret_cast<uint4*>(dst) = v;
+  if (vec) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&lo);
+    u.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = u;
   } else {
+    dst[0] = __float2bfloat16_rn(v.x); dst[1] = __float2bfloat16_rn(v.y);
+    dst[2] = __float2bfloat16_rn(v.z); dst[3] = __float2bfloat16_rn(v.w);
+  }
+}
+
+// The K slices of a column tile are the NR ranks of one cluster, each holding its partial tile in shared memory.
+// Rank r finishes every NR-th row: a thread owns one column and takes its rows a few at a time, ALL of a trip's
+// NR x rows loads from distributed shared memory in flight before the first add (one remote latency per trip, not
+// one per rank); each row is summed in rank order, so the result does not depend on which CTA finishes first.
+template <int NR, typename YT>
+__device__ __forceinline__ void ClusterReduceRows(cg::cluster_group& cluster, float* tile, const float* residual, YT* y,
+                                                  int M, int N, float scale, int n_local, int col, int rank, int half)
+{
+  constexpr int kRows = NR <= 4 ? 32 / NR : 16 / NR;
+  constexpr int step = 2 * NR;
+  for (int m0 = rank + NR * half; m0 < M; m0 += kRows * step) {
+    float t[NR][kRows], res[kRows];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) dst[e] = __float2bfloat16_rn(o[e]);
+    for (int u = 0; u < kRows; ++u) {
+      const int m = m0 + u * step;
+      res[u] = (residual != nullptr && m < M) ? __ldg(residual + static_cast<size_t>(m) * N + col) : 0.f;
+    }
+#pragma unroll
+    for (int q = 0; q < NR; ++q) {
+      const float* peer = cluster.map_shared_rank(tile, q) + n_local;
+#pragma unroll
+      for (int u = 0; u < kRows; ++u) {
+        const int m = m0 + u * step;
+        t[q][u] = m < M ? peer[m * kTcTileStride] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kRows; ++u) {
+      const int m = m0 + u * step;
+      float v = t[0][u];
+#pragma unroll
+      for (int q = 1; q < NR; ++q) v += t[q][u];
+      if (m < M) y[static_cast<size_t>(m) * N + col] = FromF32<YT>(v * scale + res[u]);
+    }
   }
 }
 
@@ -246,39 +287,49 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  bool ok = true;
-  if (warp < kTcThreads / 32) {
-    // Converter warps, in kGroups groups; a group takes every kGroups-th block and does ALL of it, so the fixed costs
-    // of a block (barrier wait, strip request, proxy fence, arrival) are paid by a few warps instead of sixteen and
-    // the groups' phases interleave on the schedulers instead of coinciding.
-    // Within a block a warp owns k rows 2 wg + r + kRowsPerPass * i, all 256 columns: lane = atom * 8 + r * 4 + j
-    // holds 16 codes of columns atom * 64 + 16 j.  Global loads: two 256-byte runs per warp instruction.  Shared
-    // stores: a quarter-warp writes two adjacent k rows of one 64-column atom, whose swizzled 16-byte slots have
-    // opposite parity, so the eight stores of a phase hit eight different bank groups.
-    constexpr int kG = L::kGroups, kChunks = L::kChunks, kRP = L::kRowsPerPass, kXR = L::kXRowsPerPass;
-    const int grp = warp / L::kGroupWarps, wg = warp % L::kGroupWarps, gtid = tid % L::kGroupThreads;
-    const int j = lane & 3, r = (lane >> 2) & 1, atom = lane >> 3;
-    const int row0 = 2 * wg + r, k_in = row0 & 7;  // rows row0 + kRP * i; kRP is a multiple of 8, so k % 8 is fixed
-    const int ccol = atom * 64 + j * 16;
-    const bool col_ok = col0 + ccol < p.N;
-    const int8_t* wp = p.w + static_cast<size_t>(kb0 + row0) * p.N + col0 + ccol;
-    const size_t pass = static_cast<size_t>(kRP) * p.N, blk = static_cast<size_t>(kTcBK) * p.N;
-    // element (n, k) of the MN-major 128-byte-swizzled tile lives at
-    // (n / 64) * 8192 + (k / 8) * 1024 + (k % 8) * 128 + (((n % 64) / 8) ^ (k % 8)) * 16 + (n % 8) * 2
-    const uint32_t dst_off = atom * 8192 + (row0 >> 3) * 1024 + k_in * 128;
-    const uint32_t s0 = static_cast<uint32_t>((2 * j) ^ k_in) << 4, s1 = static_cast<uint32_t>((2 * j + 1) ^ k_in) << 4;
-    // The activation strip [MPAD][64] bf16 goes straight into the K-major 128-byte-swizzled operand layout: chunk
-    // c = gtid + kGroupThreads * i is row c / 8, 8 k from (c % 8) * 8, stored at (row / 8) * 1024 + (row % 8) * 128 with the
-    // 16-byte chunk index XORed with row % 8.  Outside the matrix: zero-filled.
-    const int xm0 = gtid >> 3, xch = gtid & 7;
-    const uint32_t xdst0 = (xm0 >> 3) * 1024 + (xm0 & 7) * 128 + ((xch ^ (xm0 & 7)) << 4);
-    const __nv_bfloat16* xsrc0 = p.x + static_cast<size_t>(xm0) * p.K + kb0 + xch * 8;
-    const size_t xstep = static_cast<size_t>(kXR) * p.K;
+  // Converter warps, in kGroups groups; a group takes every kGroups-th block and does ALL of it, so the fixed costs
+  // of a block (barrier wait, strip request, proxy fence, arrival) are paid by a few warps instead of sixteen and
+  // the groups' phases interleave on the schedulers instead of coinciding.
+  // Within a block a warp owns k rows 2 wg + r + kRowsPerPass * i, all 256 columns: lane = atom * 8 + r * 4 + j
+  // holds 16 codes of columns atom * 64 + 16 j.  Global loads: two 256-byte runs per warp instruction.  Shared
+  // stores: a quarter-warp writes two adjacent k rows of one 64-column atom, whose swizzled 16-byte slots have
+  // opposite parity.
+  constexpr int kG = L::kGroups, kChunks = L::kChunks, kRP = L::kRowsPerPass, kXR = L::kXRowsPerPass;
+  const bool conv = warp < kTcThreads / 32;
+  const int grp = warp / L::kGroupWarps, wg = warp % L::kGroupWarps, gtid = tid % L::kGroupThreads;
+  const int j = lane & 3, r = (lane >> 2) & 1, atom = lane >> 3;
+  const int row0 = 2 * wg + r, k_in = row0 & 7;  // rows row0 + kRP * i; kRP is a multiple of 8, so k % 8 is fixed
+  const int ccol = atom * 64 + j * 16;
+  const bool col_ok = conv && col0 + ccol < p.N;
+  const int8_t* wp = p.w + static_cast<size_t>(kb0 + row0) * p.N + col0 + ccol;
+  const size_t pass = static_cast<size_t>(kRP) * p.N, blk = static_cast<size_t>(kTcBK) * p.N;
+  // element (n, k) of the MN-major 128-byte-swizzled tile lives at
+  // (n / 64) * 8192 + (k / 8) * 1024 + (k % 8) * 128 + (((n % 64) / 8) ^ (k % 8)) * 16 + (n % 8) * 2
+  const uint32_t dst_off = atom * 8192 + (row0 >> 3) * 1024 + k_in * 128;
+  const uint32_t s0 = static_cast<uint32_t>((2 * j) ^ k_in) << 4, s1 = static_cast<uint32_t>((2 * j + 1) ^ k_in) << 4;
+  // The activation strip [MPAD][64] bf16 goes straight into the K-major 128-byte-swizzled operand layout: chunk
+  // c = gtid + kGroupThreads * i is row c / 8, 8 k from (c % 8) * 8, stored at (row / 8) * 1024 + (row % 8) * 128 with the
+  // 16-byte chunk index XORed with row % 8.  Outside the matrix: zero-filled.
+  const int xm0 = gtid >> 3, xch = gtid & 7;
+  const uint32_t xdst0 = (xm0 >> 3) * 1024 + (xm0 & 7) * 128 + ((xch ^ (xm0 & 7)) << 4);
+  const __nv_bfloat16* xsrc0 = p.x + static_cast<size_t>(xm0) * p.K + kb0 + xch * 8;
+  const size_t xstep = static_cast<size_t>(kXR) * p.K;
+  float* s_scales = reinterpret_cast<float*>(smem + L::kScaleOffset);
 
-    uint4 wreg[kChunks];
+  // Everything above touched only shared memory and TMEM.  The weights and scales are the first global reads; when
+  // the caller says no preceding kernel writes them they are requested BEFORE the dependency wait, so the coldest
+  // loads of the launch travel while the predecessor drains.  The activations always come after it.
+  uint4 wreg[kChunks];
+  if (!p.weights_const) GridDependencySync();
 #pragma unroll
-    for (int i = 0; i < kChunks; ++i)
-      wreg[i] = LdWeights16(wp + static_cast<size_t>(grp) * blk + i * pass, col_ok && kb0 + grp * kTcBK + row0 + kRP * i < ke);
+  for (int i = 0; i < kChunks; ++i)
+    wreg[i] = LdWeights16(wp + static_cast<size_t>(grp) * blk + i * pass, col_ok && kb0 + grp * kTcBK + row0 + kRP * i < ke);
+  // this thread's scale: requested now, parked in shared memory after the main loop (nobody waits for it here)
+  const float my_scale = (tid < kTcBN && p.scales != nullptr && col0 + tid < p.N) ? __ldg(p.scales + col0 + tid) : 1.f;
+  if (p.weights_const) GridDependencySync();
+
+  bool ok = true;
+  if (conv) {
     for (int b = grp; b < nblocks; b += kG) {
       const int buf = b % L::kBufs;
       // Block b - kBufs used this weight tile and this strip buffer.
@@ -343,72 +394,85 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
   }
   if (!ok) atomicExch(&g_tc_status, 1);
   if (warp < kTcThreads / 32) CpAsyncWait<0>();
+  if (tid < kTcBN) s_scales[tid] = my_scale;
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();  // every MMA has completed; the pipeline space is free
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 
-  // Epilogue.  TMEM lane = activation row, TMEM column = output column.  Warp w reads lanes 32 (w % 4) .. + 31 and the
-  // quarter w / 4 of the 256 columns, eight columns at a time.
+  // Epilogue.  TMEM lane = activation row, TMEM column = output column, but a row of the output is contiguous along
+  // the columns: storing straight from the tcgen05.ld registers would touch 32 different rows per warp instruction
+  // (measured: 12k cycles for a 128 x 256 tile).  So the accumulator first goes to a row-major tile in shared memory
+  // (warp w reads lanes 32 (w % 4) .. + 31 and the quarter w / 4 of the columns: two tcgen05.ld of 32 columns, one
+  // wait, sixteen 16-byte stores without bank conflicts), and leaves it row by row, 1 KB per row, coalesced.
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned rank = cluster.block_rank(), nranks = cluster.num_blocks();
   const int lg = warp & 3, wq = warp >> 2;
   float* tile = reinterpret_cast<float*>(smem);
   YT* y = static_cast<YT*>(p.y);
-  const bool direct = MPAD > 128 || nranks == 1;
-  if (warp < kTcThreads / 32 && lg * 32 < (MPAD < 128 ? MPAD : 128)) {
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0;
 #pragma unroll
-    for (int acc = 0; acc < L::kAccs; ++acc) {
-      const int m = acc * 128 + lg * 32 + lane;
-#pragma unroll 2
-      for (int c0 = wq * 64; c0 < wq * 64 + 64; c0 += 8) {
-        uint32_t rr[8];
-        if (nblocks > 0) {
-          TcLd8(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + acc * kTcBN + c0, rr);
-          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        } else {
+  for (int acc = 0; acc < L::kAccs; ++acc) {
+    if (conv && lg * 32 < L::kTileRows) {
+      const int m = lg * 32 + lane;
+      uint32_t rr[64];
+      if (nblocks > 0) {
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + acc * kTcBN + wq * 64;
+        TcLd32(taddr, rr);
+        TcLd32(taddr + 32, rr + 32);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+      } else {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) rr[e] = 0u;
-        }
-        if (direct) {
-          const int col = col0 + c0;  // N is a multiple of 16: eight columns are inside or outside together
-          if (m < p.M && col < p.N) {
-            float o[8];
+        for (int e = 0; e < 64; ++e) rr[e] = 0u;
+      }
+      float4* dst = reinterpret_cast<float4*>(tile + m * kTcTileStride + wq * 64);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(rr[e]) * (p.scales != nullptr ? __ldg(p.scales + col + e) : 1.f);
-            const size_t at = static_cast<size_t>(m) * p.N + col;
-            if (p.residual != nullptr) {
-              if ((reinterpret_cast<uintptr_t>(p.residual + at) & 15) == 0) {
-                const float4 r0 = __ldg(reinterpret_cast<const float4*>(p.residual + at));
-                const float4 r1 = __ldg(reinterpret_cast<const float4*>(p.residual + at + 4));
-                o[0] += r0.x; o[1] += r0.y; o[2] += r0.z; o[3] += r0.w;
-                o[4] += r1.x; o[5] += r1.y; o[6] += r1.z; o[7] += r1.w;
-              } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] += __ldg(p.residual + at + e);
-              }
+      for (int c = 0; c < 16; ++c)
+        dst[c] = make_float4(__uint_as_float(rr[4 * c]), __uint_as_float(rr[4 * c + 1]), __uint_as_float(rr[4 * c + 2]),
+                             __uint_as_float(rr[4 * c + 3]));
+    }
+    if (nranks == 1) {
+      __syncthreads();
+      // 64 threads per row (four columns each), eight rows per pass.
+      const int c4 = (tid & 63) * 4;
+      if (conv && col0 + c4 < p.N) {  // N is a multiple of 16: four columns are inside or outside together
+        const float4 sc = *reinterpret_cast<const float4*>(s_scales + c4);
+#pragma unroll 4
+        for (int m = tid >> 6; m < L::kTileRows; m += 8) {
+          const int row = acc * 128 + m;
+          if (row >= p.M) break;
+          float4 v = *reinterpret_cast<const float4*>(tile + m * kTcTileStride + c4);
+          const size_t at = static_cast<size_t>(row) * p.N + col0 + c4;
+          v.x *= sc.x; v.y *= sc.y; v.z *= sc.z; v.w *= sc.w;
+          if (p.residual != nullptr) {
+            if (vec_ok) {
+              const float4 rs = __ldg(reinterpret_cast<const float4*>(p.residual + at));
+              v.x += rs.x; v.y += rs.y; v.z += rs.z; v.w += rs.w;
+            } else {
+              v.x += __ldg(p.residual + at); v.y += __ldg(p.residual + at + 1);
+              v.z += __ldg(p.residual + at + 2); v.w += __ldg(p.residual + at + 3);
             }
-            StoreRow8(y + at, o);
           }
-        } else {
-          float4* dst = reinterpret_cast<float4*>(tile + m * kTcTileStride + c0);
-          dst[0] = make_float4(__uint_as_float(rr[0]), __uint_as_float(rr[1]), __uint_as_float(rr[2]), __uint_as_float(rr[3]));
-          dst[1] = make_float4(__uint_as_float(rr[4]), __uint_as_float(rr[5]), __uint_as_float(rr[6]), __uint_as_float(rr[7]));
+          StoreRow4(y + at, v, vec_ok);
         }
       }
+      if (acc + 1 < L::kAccs) __syncthreads();  // the tile is reused by the second accumulator
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  if (MPAD <= 128 && nranks > 1) {
-    // The K slices of this column tile are the ranks of one cluster: rank r finishes every nranks-th row.
+  if (nranks > 1) {  // only launched with one accumulator
     cluster.sync();
-    for (int m = rank + nranks * (tid >> 8); m < p.M && tid < kTcThreads; m += 2 * nranks) {
-      const int n_local = tid & 255, col = col0 + n_local;
-      if (col < p.N) {
-        float v = 0.f;
-        for (unsigned q = 0; q < nranks; ++q) v += cluster.map_shared_rank(tile, q)[m * kTcTileStride + n_local];
-        if (p.scales != nullptr) v *= __ldg(p.scales + col);
-        if (p.residual != nullptr) v += __ldg(p.residual + static_cast<size_t>(m) * p.N + col);
-        y[static_cast<size_t>(m) * p.N + col] = FromF32<YT>(v);
+    const int n_local = tid & 255, col = col0 + n_local;
+    if (conv && col < p.N) {
+      const float scale = s_scales[n_local];
+      const int half = tid >> 8, rk = static_cast<int>(rank);
+      switch (nranks) {
+        case 2: ClusterReduceRows<2>(cluster, tile, p.residual, y, p.M, p.N, scale, n_local, col, rk, half); break;
+        case 3: ClusterReduceRows<3>(cluster, tile, p.residual, y, p.M, p.N, scale, n_local, col, rk, half); break;
+        case 4: ClusterReduceRows<4>(cluster, tile, p.residual, y, p.M, p.N, scale, n_local, col, rk, half); break;
+        case 5: ClusterReduceRows<5>(cluster, tile, p.residual, y, p.M, p.N, scale, n_local, col, rk, half); break;
+        case 6: ClusterReduceRows<6>(cluster, tile, p.residual, y, p.M, p.N, scale, n_local, col, rk, half); break;
+        case 7: ClusterReduceRows<7>(cluster, tile, p.residual, y, p.M, p.N, scale, n_local, col, rk, half); break;
+        default: ClusterReduceRows<8>(cluster, tile, p.residual, y, p.M, p.N, scale, n_local, col, rk, half); break;
       }
     }
     cluster.sync();  // no CTA leaves while a peer may still read its tile
@@ -434,13 +498,9 @@ cudaError_t LaunchTc(const TcParams& p, cudaStream_t stream)
   cfg.blockDim = dim3(kTcLaunchThreads, 1, 1);
   cfg.dynamicSmemBytes = TcLayout<MPAD>::kBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = p.ks;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  cfg.numAttrs = ChainAttributes(attr, p.ks);
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT>, p);
 }
 
@@ -485,8 +545,8 @@ int ChooseTcSlices(int k, int n, int mpad, double* cost_out = nullptr)
   }();
   const int tiles = (n + kTcBN - 1) / kTcBN;
   const int nb = (k + kTcBK - 1) / kTcBK;
-  if (mpad > 128) {  // no cluster reduction for two accumulators; a block costs about 1.7x one of a single accumulator
-    if (cost_out != nullptr) *cost_out = 1.7 * ((tiles + 147) / 148) * (nb + 10.0);
+  if (mpad > 128) {  // no cluster reduction for two accumulators; a block costs about twice one of a single accumulator
+    if (cost_out != nullptr) *cost_out = 2.0 * ((tiles + 147) / 148) * (nb + 10.0);
     return 1;
   }
   if (forced >= 1 && forced <= 8) return forced;
@@ -544,9 +604,10 @@ cudaError_t PrepareInt8GemmTcKernels()
 
 // Rows [0, m) of the projection on the tensor-core kernel, at most 256 rows per launch.  x is bf16.
 cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const float* scales, const float* residual,
-                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches)
+                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches, bool weights_const)
 {
   TcParams p;
+  p.weights_const = weights_const ? 1 : 0;
   p.w = codes;
   p.scales = scales;
   p.K = k;

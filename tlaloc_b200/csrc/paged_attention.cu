@@ -76,6 +76,7 @@ constexpr int kGenQ = 8;       // queries per pass
 template <typename QT, typename KVT>
 __global__ void __launch_bounds__(kGenThreads) PaSliceGeneric(PaParams p)
 {
+  GridDependencySync();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* qs = reinterpret_cast<float*>(smem_raw);                      // [kGenQ][D]
   float* sc = qs + kGenQ * p.D;                                        // [kGenQ][kGenTile]
@@ -308,6 +309,7 @@ struct MmaLayout {
 template <typename QT, int D, int NS, int NT>
 __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
 {
+  GridDependencySync();
   constexpr bool QLO = sizeof(QT) == 4;
   using L = MmaLayout<D, NS>;
   constexpr int CPR = L::kRowBytes / 16;  // 16-byte chunks per row
@@ -583,6 +585,7 @@ constexpr int kCombineThreads = 128;
 template <typename OT>
 __global__ void __launch_bounds__(kCombineThreads) PaCombine(PaParams p)
 {
+  GridDependencySync();
   extern __shared__ float w_s[];  // [S]
   const int rh = blockIdx.x, row = rh / p.H, head = rh - row * p.H;
   const int tid = threadIdx.x;
@@ -624,6 +627,7 @@ __global__ void __launch_bounds__(kCombineThreads) PaCombine(PaParams p)
 template <typename PT, typename NT>
 __global__ void KvCacheWriteKernel(PT* pool, const NT* new_kv, const int* slots, int row_elems, int num_slots)
 {
+  GridDependencySync();
   const int i = blockIdx.x;
   const int slot = __ldg(slots + i);
   if (slot < 0 || slot >= num_slots) return;
@@ -675,9 +679,8 @@ cudaError_t LaunchMmaNs(const PaParams& p, cudaStream_t stream)
 {
   const size_t smem = MmaLayout<D, NS>::Bytes(p.slice / p.bs + 2);
   const dim3 grid(p.S, p.Hkv, p.Tb);
-  if (p.NQ <= 8) PaSliceMma<QT, D, NS, 1><<<grid, kMmaThreads, smem, stream>>>(p);
-  else PaSliceMma<QT, D, NS, 2><<<grid, kMmaThreads, smem, stream>>>(p);
-  return cudaGetLastError();
+  if (p.NQ <= 8) return LaunchChained(PaSliceMma<QT, D, NS, 1>, grid, kMmaThreads, smem, stream, p);
+  return LaunchChained(PaSliceMma<QT, D, NS, 2>, grid, kMmaThreads, smem, stream, p);
 }
 
 template <typename QT, int D>
@@ -694,8 +697,7 @@ template <typename QT, typename KVT>
 cudaError_t LaunchGeneric(const PaParams& p, cudaStream_t stream)
 {
   const size_t smem = sizeof(float) * (kGenQ * p.D + kGenQ * kGenTile) + sizeof(long long) * kGenTile;
-  PaSliceGeneric<QT, KVT><<<dim3(p.S, p.Hkv, p.Tb), kGenThreads, smem, stream>>>(p);
-  return cudaGetLastError();
+  return LaunchChained(PaSliceGeneric<QT, KVT>, dim3(p.S, p.Hkv, p.Tb), kGenThreads, smem, stream, p);
 }
 
 // Positions per slice of the tensor-core kernel when the scratch allows it; $TLALOC_B200_PA_SLICE overrides.
@@ -854,11 +856,10 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
   if (e != cudaSuccess) return CudaFail("PAGED_ATTENTION slice launch", e);
   const size_t csmem = sizeof(float) * p.S;
   if (out_dtype == TLALOC_B200_F32) {
-    PaCombine<float><<<p.R * p.H, kCombineThreads, csmem, st>>>(p);
+    e = LaunchChained(PaCombine<float>, p.R * p.H, kCombineThreads, csmem, st, p);
   } else {
-    PaCombine<__nv_bfloat16><<<p.R * p.H, kCombineThreads, csmem, st>>>(p);
+    e = LaunchChained(PaCombine<__nv_bfloat16>, p.R * p.H, kCombineThreads, csmem, st, p);
   }
-  e = cudaGetLastError();
   if (e != cudaSuccess) return CudaFail("PAGED_ATTENTION combine launch", e);
   CountLaunches(2);
   return kOk;
@@ -875,23 +876,22 @@ extern "C" int tlaloc_b200_kv_cache_write(void* pool, int32_t pool_dtype, const 
   if (num_tokens == 0) return kOk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int threads = row_elems >= 256 ? 256 : 128;
+  cudaError_t e;
   if (pool_dtype == TLALOC_B200_F32 && new_dtype == TLALOC_B200_F32) {
-    KvCacheWriteKernel<<<num_tokens, threads, 0, st>>>(static_cast<float*>(pool), static_cast<const float*>(new_kv),
-                                                       slot_mapping, row_elems, num_slots);
+    e = LaunchChained(KvCacheWriteKernel<float, float>, num_tokens, threads, 0, st, static_cast<float*>(pool),
+                      static_cast<const float*>(new_kv), slot_mapping, row_elems, num_slots);
   } else if (pool_dtype == TLALOC_B200_F32) {
-    KvCacheWriteKernel<<<num_tokens, threads, 0, st>>>(static_cast<float*>(pool),
-                                                       static_cast<const __nv_bfloat16*>(new_kv), slot_mapping,
-                                                       row_elems, num_slots);
+    e = LaunchChained(KvCacheWriteKernel<float, __nv_bfloat16>, num_tokens, threads, 0, st, static_cast<float*>(pool),
+                      static_cast<const __nv_bfloat16*>(new_kv), slot_mapping, row_elems, num_slots);
   } else if (new_dtype == TLALOC_B200_F32) {
-    KvCacheWriteKernel<<<num_tokens, threads, 0, st>>>(static_cast<__nv_bfloat16*>(pool),
-                                                       static_cast<const float*>(new_kv), slot_mapping, row_elems,
-                                                       num_slots);
+    e = LaunchChained(KvCacheWriteKernel<__nv_bfloat16, float>, num_tokens, threads, 0, st,
+                      static_cast<__nv_bfloat16*>(pool), static_cast<const float*>(new_kv), slot_mapping, row_elems,
+                      num_slots);
   } else {
-    KvCacheWriteKernel<<<num_tokens, threads, 0, st>>>(static_cast<__nv_bfloat16*>(pool),
-                                                       static_cast<const __nv_bfloat16*>(new_kv), slot_mapping,
-                                                       row_elems, num_slots);
+    e = LaunchChained(KvCacheWriteKernel<__nv_bfloat16, __nv_bfloat16>, num_tokens, threads, 0, st,
+                      static_cast<__nv_bfloat16*>(pool), static_cast<const __nv_bfloat16*>(new_kv), slot_mapping,
+                      row_elems, num_slots);
   }
-  const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return CudaFail("KV_CACHE_WRITE launch", e);
   CountLaunches(1);
   return kOk;

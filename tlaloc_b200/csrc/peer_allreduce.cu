@@ -80,6 +80,7 @@ __device__ __forceinline__ bool WaitFlag(const uint32_t* flag, uint32_t epoch)
 template <int W>
 __global__ void __launch_bounds__(kThreads) PeerAllReduceKernel(PeerTable t, uint32_t* state, int rank, int world_rt, size_t n4)
 {
+  GridDependencySync();
   const int world = W > 0 ? W : world_rt;
   __shared__ uint32_t s_epoch, s_last, s_dead;
   const int tid = threadIdx.x;
@@ -160,13 +161,13 @@ int LaunchPeerAllReduce(void* const* bases, size_t data_offset, size_t flag_offs
   const size_t slice = (n4 + world - 1) / world;
   int grid = static_cast<int>((slice + kThreads - 1) / kThreads);
   grid = grid < 1 ? 1 : grid > 148 ? 148 : grid;
+  cudaError_t e;
   switch (world) {
-    case 2: PeerAllReduceKernel<2><<<grid, kThreads, 0, st>>>(t, state, rank, world, n4); break;
-    case 4: PeerAllReduceKernel<4><<<grid, kThreads, 0, st>>>(t, state, rank, world, n4); break;
-    case 8: PeerAllReduceKernel<8><<<grid, kThreads, 0, st>>>(t, state, rank, world, n4); break;
-    default: PeerAllReduceKernel<0><<<grid, kThreads, 0, st>>>(t, state, rank, world, n4); break;
+    case 2: e = LaunchChained(PeerAllReduceKernel<2>, grid, kThreads, 0, st, t, state, rank, world, n4); break;
+    case 4: e = LaunchChained(PeerAllReduceKernel<4>, grid, kThreads, 0, st, t, state, rank, world, n4); break;
+    case 8: e = LaunchChained(PeerAllReduceKernel<8>, grid, kThreads, 0, st, t, state, rank, world, n4); break;
+    default: e = LaunchChained(PeerAllReduceKernel<0>, grid, kThreads, 0, st, t, state, rank, world, n4); break;
   }
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return CudaFail("peer_allreduce launch", e);
   CountLaunches(1);
   return kOk;

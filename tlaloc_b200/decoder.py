@@ -197,21 +197,21 @@ class Decoder:
         v3 = self.qkv[:, (hq + hk) * hd:].unflatten(1, (hk, hd))
         for l, lw in enumerate(self.layers):
             ops.rmsnorm(h, lw["ln1"], cfg.rms_eps, out=self.hn)
-            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv)
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True)
             ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
                               self.value_pools[l], q_out=self.q_rot)
             ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
                                 scale=cfg.scale, out=self.att, scratch=self.att_scratch)
-            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, weights_const=True)
             self._all_reduce(h2)
             ops.rmsnorm(h2, lw["ln2"], cfg.rms_eps, out=self.hn)
-            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu)
+            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True)
             ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
-            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h)
+            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True)
             self._all_reduce(h)
         ops.rmsnorm(h, self.final_norm, cfg.rms_eps, out=self.hn)
         if isinstance(self.head, tuple):
-            ops.int8_gemm(self.hn, *self.head, out=self.logits)
+            ops.int8_gemm(self.hn, *self.head, out=self.logits, weights_const=True)
         else:
             self.logits.copy_(ops.dense_gemm_exact(self.hn, self.head))
         ops.argmax(self.logits, out=self.next_ids)

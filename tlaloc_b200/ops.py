@@ -82,8 +82,9 @@ def kv_cache_write(pool, new_kv, slot_mapping):
 
 
 def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.float32, exact=False, x_f32_exact=False,
-              scratch=None):
-    """y = (cast(x) @ cast(codes)) * scales (+ residual): x [M, K], codes int8 [K, N] (in, out), scales f32 [N]."""
+              scratch=None, weights_const=False):
+    """y = (cast(x) @ cast(codes)) * scales (+ residual): x [M, K], codes int8 [K, N] (in, out), scales f32 [N].
+    `weights_const`: no kernel queued just before this call writes codes or scales (true of a loaded model)."""
     _dev(x, codes, scales, residual)
     M, K = x.shape
     K2, Nn = codes.shape
@@ -94,7 +95,8 @@ def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.floa
     if scratch is None and x.dtype == torch.float32 and not exact:
         scratch = torch.empty((N.lib().tlaloc_b200_int8_gemm_scratch_bytes(M, K, Nn) + 3) // 4, dtype=torch.float32,
                               device=x.device)
-    flags = (N.GEMM_EXACT if exact else 0) | (N.GEMM_X_F32_EXACT if x_f32_exact else 0)
+    flags = ((N.GEMM_EXACT if exact else 0) | (N.GEMM_X_F32_EXACT if x_f32_exact else 0)
+             | (N.GEMM_WEIGHTS_CONST if weights_const else 0))
     N.check(N.lib().tlaloc_b200_int8_gemm(_ptr(x), _dt(x), _ptr(codes), _ptr(scales), _ptr(residual), _ptr(out), _dt(out),
                                           _ptr(scratch), 0 if scratch is None else scratch.numel() * 4, M, K, Nn, flags,
                                           _stream()))

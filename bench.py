@@ -345,7 +345,7 @@ def _time_graph(torch, fn, reps, warm=3):
 def run_operator(args) -> dict:
     """The two operators alone (single GPU): the paged-attention decode operator (bf16 Q [32, 32, 128], 8 KV heads,
     block 16, 4096 physical blocks, permuted tables, lengths U[512, 8192], seed 1) or the int8 projection sweep
-    (N x K in {4096x4096, 14336x4096, 4096x14336, 128256x4096}, M in {1, 8, 32, 256}).  HBM GB/s on algorithmic bytes."""
+    (N x K in {4096x4096, 14336x4096, 4096x14336, 128256x4096}, M in {1, 8, 32, 128, 256}).  HBM GB/s on algorithmic bytes."""
     import torch
 
     from tlaloc_b200 import ops
@@ -391,7 +391,7 @@ def run_operator(args) -> dict:
                 "roofline": {"kernel": "PaSliceMma+PaCombine", "bound": "hbm", "achieved": head["gbs"], "peak": peak,
                              "unit": "GB/s", "frac": head["gbs"] / peak, "peak_kind": peak_kind, "traffic": None}}
     rows = []
-    shapes, ms = [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)], (1, 8, 32, 256)
+    shapes, ms = [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)], (1, 8, 32, 128, 256)
     if args.only:  # one shape "NxKxM", for profiler captures
         n, k, m = (int(v) for v in args.only.lower().split("x"))
         shapes, ms = [(n, k)], (m,)
@@ -405,7 +405,7 @@ def run_operator(args) -> dict:
 
             def fn():
                 for w in ws:
-                    ops.int8_gemm(x, w, sc, out=y)
+                    ops.int8_gemm(x, w, sc, out=y, weights_const=True)
             best, med = _time_graph(torch, fn, 10)
             byts = k * n + 4 * n + 2 * m * k + 4 * m * n
             rows.append({"N": n, "K": k, "M": m, "us": med / nbuf * 1e3, "gbs": byts / (med / nbuf) / 1e6,

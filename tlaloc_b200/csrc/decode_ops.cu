@@ -89,56 +89,79 @@ __global__ void __launch_bounds__(256) RmsNormKernel(const float* x, const float
 // Grid (tokens, H + 2*Hkv): head slot h < H rotates a query head into q_out; the next Hkv rotate a key head into
 // the key pool at the token's slot; the last Hkv copy a value head into the value pool.  x*cos + rotate_half(x)*sin
 // with each product and the sum rounded to f32 (HfDecoderGraph.kt:792-818).
+constexpr int kRopeHeadsPerCta = 8;
+
+// One warp per (token, head slot); lane j takes the channel pairs (j, j + hd/2), (j + 32, j + 32 + hd/2), ...: both
+// members of a pair need both inputs, and consecutive lanes touch consecutive addresses.
 template <typename QT, typename KVT>
-__global__ void RopeKvWriteKernel(const float* q, const float* k, const float* v, const int* positions,
-                                  const float* cos_t, const float* sin_t, const int* slots, QT* q_out, KVT* kc,
-                                  KVT* vc, int H, int Hkv, int hd, int num_slots, int max_pos, int ldq, int ldk,
-                                  int ldv)
+__global__ void __launch_bounds__(32 * kRopeHeadsPerCta)
+RopeKvWriteKernel(const float* q, const float* k, const float* v, const int* positions, const float* cos_t,
+                  const float* sin_t, const int* slots, QT* q_out, KVT* kc, KVT* vc, int H, int Hkv, int hd,
+                  int num_slots, int max_pos, int ldq, int ldk, int ldv)
 {
   GridDependencySync();
-  const int t = blockIdx.x, hs = blockIdx.y;
+  const int t = blockIdx.x, hs = blockIdx.y * kRopeHeadsPerCta + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (hs >= H + 2 * Hkv) return;
   const int half = hd >> 1;
-  int pos = __ldg(positions + t);
-  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
-  const float* c = cos_t + static_cast<size_t>(pos) * hd;
-  const float* s = sin_t + static_cast<size_t>(pos) * hd;
-  if (hs < H) {
-    const float* x = q + static_cast<size_t>(t) * ldq + hs * hd;
-    QT* o = q_out + (static_cast<size_t>(t) * H + hs) * hd;
-    for (int j = threadIdx.x; j < hd; j += blockDim.x) {
-      const float rot = j < half ? -x[j + half] : x[j - half];
-      o[j] = FromF32<QT>(__fadd_rn(__fmul_rn(x[j], c[j]), __fmul_rn(rot, s[j])));
+  if (hs < H + Hkv) {
+    int pos = __ldg(positions + t);
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* c = cos_t + static_cast<size_t>(pos) * hd;
+    const float* s = sin_t + static_cast<size_t>(pos) * hd;
+    if (hs < H) {
+      const float* x = q + static_cast<size_t>(t) * ldq + hs * hd;
+      QT* o = q_out + (static_cast<size_t>(t) * H + hs) * hd;
+      for (int j = lane; j < half; j += 32) {
+        const float lo = x[j], hi = x[j + half];
+        o[j] = FromF32<QT>(__fadd_rn(__fmul_rn(lo, c[j]), __fmul_rn(-hi, s[j])));
+        o[j + half] = FromF32<QT>(__fadd_rn(__fmul_rn(hi, c[j + half]), __fmul_rn(lo, s[j + half])));
+      }
+      return;
+    }
+    const int slot = __ldg(slots + t);
+    if (slot < 0 || slot >= num_slots) return;  // padding lane (negative) or a slot past the pool: no write
+    const int h = hs - H;
+    const float* x = k + static_cast<size_t>(t) * ldk + h * hd;
+    KVT* o = kc + (static_cast<size_t>(slot) * Hkv + h) * hd;
+    for (int j = lane; j < half; j += 32) {
+      const float lo = x[j], hi = x[j + half];
+      o[j] = FromF32<KVT>(__fadd_rn(__fmul_rn(lo, c[j]), __fmul_rn(-hi, s[j])));
+      o[j + half] = FromF32<KVT>(__fadd_rn(__fmul_rn(hi, c[j + half]), __fmul_rn(lo, s[j + half])));
     }
     return;
   }
   const int slot = __ldg(slots + t);
-  if (slot < 0 || slot >= num_slots) return;  // padding lane (negative) or a slot past the pool: no write
-  if (hs < H + Hkv) {
-    const int h = hs - H;
-    const float* x = k + static_cast<size_t>(t) * ldk + h * hd;
-    KVT* o = kc + (static_cast<size_t>(slot) * Hkv + h) * hd;
-    for (int j = threadIdx.x; j < hd; j += blockDim.x) {
-      const float rot = j < half ? -x[j + half] : x[j - half];
-      o[j] = FromF32<KVT>(__fadd_rn(__fmul_rn(x[j], c[j]), __fmul_rn(rot, s[j])));
-    }
-  } else {
-    const int h = hs - H - Hkv;
-    const float* x = v + static_cast<size_t>(t) * ldv + h * hd;
-    KVT* o = vc + (static_cast<size_t>(slot) * Hkv + h) * hd;
-    for (int j = threadIdx.x; j < hd; j += blockDim.x) o[j] = FromF32<KVT>(x[j]);
-  }
+  if (slot < 0 || slot >= num_slots) return;
+  const int h = hs - H - Hkv;
+  const float* x = v + static_cast<size_t>(t) * ldv + h * hd;
+  KVT* o = vc + (static_cast<size_t>(slot) * Hkv + h) * hd;
+  for (int j = lane; j < hd; j += 32) o[j] = FromF32<KVT>(x[j]);
 }
 
-template <typename OT>
+__device__ __forceinline__ float SiluMul(float g, float u) { return __fmul_rn(g / (1.f + expf(-g)), u); }
+
+// Four columns per thread when the rows allow 16-byte accesses (VEC), else one.
+template <typename OT, bool VEC>
 __global__ void SwigluKernel(const float* gate, const float* up, int ld, OT* out, int rows, int n)
 {
   GridDependencySync();
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= static_cast<size_t>(rows) * n) return;
-  const int r = static_cast<int>(i / n), c = static_cast<int>(i - static_cast<size_t>(r) * n);
-  const float g = gate[static_cast<size_t>(r) * ld + c];
-  const float silu = g / (1.f + expf(-g));
-  out[i] = FromF32<OT>(__fmul_rn(silu, up[static_cast<size_t>(r) * ld + c]));
+  if (VEC) {
+    const int n4 = n >> 2;
+    if (i >= static_cast<size_t>(rows) * n4) return;
+    const int r = static_cast<int>(i / n4), c = static_cast<int>(i - static_cast<size_t>(r) * n4) * 4;
+    const float4 g = *reinterpret_cast<const float4*>(gate + static_cast<size_t>(r) * ld + c);
+    const float4 u = *reinterpret_cast<const float4*>(up + static_cast<size_t>(r) * ld + c);
+    OT* o = out + static_cast<size_t>(r) * n + c;
+    o[0] = FromF32<OT>(SiluMul(g.x, u.x));
+    o[1] = FromF32<OT>(SiluMul(g.y, u.y));
+    o[2] = FromF32<OT>(SiluMul(g.z, u.z));
+    o[3] = FromF32<OT>(SiluMul(g.w, u.w));
+  } else {
+    if (i >= static_cast<size_t>(rows) * n) return;
+    const int r = static_cast<int>(i / n), c = static_cast<int>(i - static_cast<size_t>(r) * n);
+    out[i] = FromF32<OT>(SiluMul(gate[static_cast<size_t>(r) * ld + c], up[static_cast<size_t>(r) * ld + c]));
+  }
 }
 
 // One CTA per row; the first index of the maximum wins (DxirInterpreter.kt:2414-2426).
@@ -248,8 +271,8 @@ extern "C" int tlaloc_b200_rope_kv_write(const float* q, const float* k, const f
   }
   if (num_tokens == 0) return kOk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const dim3 grid(num_tokens, num_heads + 2 * num_kv_heads);
-  const int threads = head_dim >= 128 ? 128 : 64;
+  const dim3 grid(num_tokens, (num_heads + 2 * num_kv_heads + kRopeHeadsPerCta - 1) / kRopeHeadsPerCta);
+  const int threads = 32 * kRopeHeadsPerCta;
   cudaError_t e;
 #define TLALOC_LAUNCH(QT, KVT)                                                                                      \
   e = LaunchChained(RopeKvWriteKernel<QT, KVT>, grid, threads, 0, st, q, k, v, positions, cos_table, sin_table,     \
@@ -274,13 +297,17 @@ extern "C" int tlaloc_b200_swiglu(const float* gate, const float* up, int32_t ld
   if (rows < 0 || n < 1 || ld < n) return Fail(kInvalid, "SWIGLU: bad sizes");
   if (rows == 0) return kOk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t total = static_cast<size_t>(rows) * n;
+  const bool vec = n % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(gate) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(up) & 15) == 0;
+  const size_t total = static_cast<size_t>(rows) * (vec ? n / 4 : n);
   const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
   cudaError_t e;
   if (out_dtype == TLALOC_B200_F32) {
-    e = LaunchChained(SwigluKernel<float>, blocks, 256, 0, st, gate, up, ld, static_cast<float*>(out), rows, n);
+    e = vec ? LaunchChained(SwigluKernel<float, true>, blocks, 256, 0, st, gate, up, ld, static_cast<float*>(out), rows, n)
+            : LaunchChained(SwigluKernel<float, false>, blocks, 256, 0, st, gate, up, ld, static_cast<float*>(out), rows, n);
   } else {
-    e = LaunchChained(SwigluKernel<__nv_bfloat16>, blocks, 256, 0, st, gate, up, ld, static_cast<__nv_bfloat16*>(out), rows, n);
+    e = vec ? LaunchChained(SwigluKernel<__nv_bfloat16, true>, blocks, 256, 0, st, gate, up, ld, static_cast<__nv_bfloat16*>(out), rows, n)
+            : LaunchChained(SwigluKernel<__nv_bfloat16, false>, blocks, 256, 0, st, gate, up, ld, static_cast<__nv_bfloat16*>(out), rows, n);
   }
   if (e != cudaSuccess) return CudaFail("SWIGLU launch", e);
   CountLaunches(1);

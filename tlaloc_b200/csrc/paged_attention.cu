@@ -580,15 +580,27 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
 // Combine: grid R*H.  Row r's live slices are [first / slice, ceil(len / slice)); their records merge as
 // out = sum_s exp(m_s - max) acc_s / sum_s exp(m_s - max) l_s, in slice order (deterministic).
 
-constexpr int kCombineThreads = 128;
+constexpr int kCombineThreads = 128;  // four warps, one (row, head) each
+constexpr int kCombineMaxPairs = 4;   // channel pairs per lane: D <= 256
 
+__device__ __forceinline__ void StorePair(float* o, float a, float b) { *reinterpret_cast<float2*>(o) = make_float2(a, b); }
+__device__ __forceinline__ void StorePair(__nv_bfloat16* o, float a, float b)
+{
+  *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(a, b);
+}
+
+// Merges the records {max, sum, acc[D]} of a row's live slices, in slice order.  One warp per (row, head): lane l
+// holds the max and sum of slice s_lo + l (32 slices at a time), the weights travel by shuffle, and every lane owns
+// the channel pairs 2l, 2l + 1 (+ 64, ...).  The loads of a trip do not depend on one another, so a merge costs about
+// two trips to L2 rather than one per slice.  D is even (RoPE pairs) or the scalar tail handles the last channel.
 template <typename OT>
 __global__ void __launch_bounds__(kCombineThreads) PaCombine(PaParams p)
 {
   GridDependencySync();
-  extern __shared__ float w_s[];  // [S]
-  const int rh = blockIdx.x, row = rh / p.H, head = rh - row * p.H;
-  const int tid = threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int rh = blockIdx.x * (kCombineThreads / 32) + (threadIdx.x >> 5);
+  if (rh >= p.R * p.H) return;
+  const int row = rh / p.H, head = rh - row * p.H;
   const int ctx = p.M * p.bs;
   const int len = ClampI(__ldg(p.lens + row), 0, ctx);
   const int first = p.window > 0 ? max(0, len - p.window) : 0;
@@ -596,29 +608,71 @@ __global__ void __launch_bounds__(kCombineThreads) PaCombine(PaParams p)
   const size_t stride = static_cast<size_t>(p.R) * p.H * (p.D + 2);
   const float* base = Record(p, 0, row, head);
   float mx = -INFINITY;
-  for (int s = s_lo; s < s_hi; ++s) mx = fmaxf(mx, base[s * stride]);
+  for (int s = s_lo + lane; s < s_hi; s += 32) mx = fmaxf(mx, base[s * stride]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   float denom = 0.f;
-  for (int s = s_lo; s < s_hi; ++s) {
-    const float m = base[s * stride];
-    const float w = m == -INFINITY ? 0.f : expf(m - mx);
-    if (tid == 0) w_s[s] = w;
-    if (w != 0.f) denom += w * base[s * stride + 1];
+  float acc[2 * kCombineMaxPairs];
+#pragma unroll
+  for (int i = 0; i < 2 * kCombineMaxPairs; ++i) acc[i] = 0.f;
+  const int pairs = p.D >> 1;
+  const bool even = (p.D & 1) == 0 && (reinterpret_cast<uintptr_t>(p.scratch) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7) == 0;
+  for (int c0 = s_lo; c0 < s_hi; c0 += 32) {
+    const int mine = c0 + lane;
+    float w_l = 0.f, ws_l = 0.f;
+    if (mine < s_hi) {
+      const float m = base[mine * stride];
+      w_l = m == -INFINITY ? 0.f : expf(m - mx);
+      ws_l = w_l != 0.f ? w_l * base[mine * stride + 1] : 0.f;
+    }
+    const int n = min(32, s_hi - c0);
+    for (int i = 0; i < n; ++i) {
+      const float w = __shfl_sync(0xffffffffu, w_l, i), ws = __shfl_sync(0xffffffffu, ws_l, i);
+      if (w != 0.f) {  // uniform over the warp
+        denom += ws;
+        const float* rec = base + (c0 + i) * stride + 2;
+#pragma unroll
+        for (int j = 0; j < kCombineMaxPairs; ++j) {
+          const int pr = lane + 32 * j;
+          if (pr < pairs) {
+            float2 v;
+            if (even) v = *reinterpret_cast<const float2*>(rec + 2 * pr);  // records start on 8-byte boundaries only for even D
+            else v = make_float2(rec[2 * pr], rec[2 * pr + 1]);
+            acc[2 * j] += w * v.x;
+            acc[2 * j + 1] += w * v.y;
+          }
+        }
+      }
+    }
   }
-  __syncthreads();
   OT* out = static_cast<OT*>(p.out) + static_cast<size_t>(rh) * p.D;
   const bool empty = mx == -INFINITY || denom == 0.f;
-  for (int d = tid; d < p.D; d += kCombineThreads) {
+#pragma unroll
+  for (int j = 0; j < kCombineMaxPairs; ++j) {
+    const int pr = lane + 32 * j;
+    if (pr < pairs) {
+      const float a = empty ? 0.f : acc[2 * j] / denom, b = empty ? 0.f : acc[2 * j + 1] / denom;
+      if (even) {
+        StorePair(out + 2 * pr, a, b);
+      } else {
+        out[2 * pr] = FromF32<OT>(a);
+        out[2 * pr + 1] = FromF32<OT>(b);
+      }
+    }
+  }
+  if ((p.D & 1) != 0 && lane == 0) {  // an odd head dimension: the last channel, not part of any pair
     float a = 0.f;
     if (!empty) {
       for (int s = s_lo; s < s_hi; ++s) {
-        const float w = w_s[s];
-        if (w != 0.f) a += w * base[s * stride + 2 + d];
+        const float m = base[s * stride];
+        const float w = m == -INFINITY ? 0.f : expf(m - mx);
+        if (w != 0.f) a += w * base[s * stride + 2 + p.D - 1];
       }
       a /= denom;
     }
-    out[d] = FromF32<OT>(a);
+    out[p.D - 1] = FromF32<OT>(a);
   }
-  if (tid == 0 && p.lse != nullptr) p.lse[rh] = empty ? -INFINITY : mx + logf(denom);
+  if (lane == 0 && p.lse != nullptr) p.lse[rh] = empty ? -INFINITY : mx + logf(denom);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -854,11 +908,11 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
     e = LaunchGeneric<__nv_bfloat16, __nv_bfloat16>(p, st);
   }
   if (e != cudaSuccess) return CudaFail("PAGED_ATTENTION slice launch", e);
-  const size_t csmem = sizeof(float) * p.S;
+  const unsigned cgrid = static_cast<unsigned>((p.R * p.H + kCombineThreads / 32 - 1) / (kCombineThreads / 32));
   if (out_dtype == TLALOC_B200_F32) {
-    e = LaunchChained(PaCombine<float>, p.R * p.H, kCombineThreads, csmem, st, p);
+    e = LaunchChained(PaCombine<float>, cgrid, kCombineThreads, 0, st, p);
   } else {
-    e = LaunchChained(PaCombine<__nv_bfloat16>, p.R * p.H, kCombineThreads, csmem, st, p);
+    e = LaunchChained(PaCombine<__nv_bfloat16>, cgrid, kCombineThreads, 0, st, p);
   }
   if (e != cudaSuccess) return CudaFail("PAGED_ATTENTION combine launch", e);
   CountLaunches(2);

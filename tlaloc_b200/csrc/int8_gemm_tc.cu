@@ -27,6 +27,7 @@
 #include <cooperative_groups.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -107,21 +108,33 @@ __device__ __forceinline__ uint4 LdWeights16(const int8_t* ptr, bool valid)
   }
   return v;
 }
+__device__ __forceinline__ uint4 LdWeights16Always(const int8_t* ptr)
+{
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+  return v;
+}
 __device__ __forceinline__ void StShared16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-// Two codes of one word (bytes selected by SEL into the low byte of each half) as an exact bf16 pair: for a code v
+// Two codes in the LOW bytes of the two halves of q (the high bytes are ignored) as an exact bf16 pair: for a code v
 // with bits s:lo7, 0x4300|lo7 is the bf16 128 + lo7 and 0xC300|s<<7 is -128 or -256; their sum is v.
-template <int SEL>
-__device__ __forceinline__ uint32_t CodePairToBf16x2(uint32_t w)
+__device__ __forceinline__ uint32_t LowBytesToBf16x2(uint32_t q)
 {
-  const uint32_t q = __byte_perm(w, 0u, SEL);
   uint32_t t, c, r;
   asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(t) : "r"(q), "r"(0x007F007Fu), "r"(0x43004300u));
   asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(c) : "r"(q), "r"(0x00800080u), "r"(0xC300C300u));
   asm("fma.rn.bf16x2 %0, %1, %2, %3;\n" : "=r"(r) : "r"(t), "r"(0x3F803F80u), "r"(c));
   return r;
+}
+// The four codes c0..c3 of one word as the pairs (c0, c2) and (c1, c3): the even bytes already sit in the low byte of
+// each half, the odd ones after one shift, so no byte permute is needed.  The weight tile therefore holds its columns
+// in the order 0 2 1 3 within every group of four; the epilogue swaps them back on the way out of TMEM.
+__device__ __forceinline__ void WordToBf16(uint32_t w, uint32_t& even, uint32_t& odd)
+{
+  even = LowBytesToBf16x2(w);
+  odd = LowBytesToBf16x2(w >> 8);
 }
 
 __device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count)
@@ -315,6 +328,8 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
   const __nv_bfloat16* xsrc0 = p.x + static_cast<size_t>(xm0) * p.K + kb0 + xch * 8;
   const size_t xstep = static_cast<size_t>(kXR) * p.K;
   float* s_scales = reinterpret_cast<float*>(smem + L::kScaleOffset);
+  const int x_rows = p.M > xm0 ? (p.M - xm0 + kXR - 1) / kXR : 0;  // strip rows this thread copies: xm0 + kXR * i < M
+  const bool tile_full = col0 + kTcBN <= p.N;
 
   // Everything above touched only shared memory and TMEM.  The weights and scales are the first global reads; when
   // the caller says no preceding kernel writes them they are requested BEFORE the dependency wait, so the coldest
@@ -338,28 +353,45 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
       {
         const uint32_t st = smem_base + buf * L::kXBytes + xdst0;
         const __nv_bfloat16* src = xsrc0 + b * kTcBK;
-        const bool k_ok = k0 + xch * 8 < ke;
+        if (k0 + kTcBK <= ke) {
+          // A full block: only rows that exist are requested.  The rows past M keep whatever the buffer held; they
+          // feed accumulator lanes that are never read.  (A partial block must zero-fill its missing k instead:
+          // garbage there would meet the zero weights of those k and 0 x NaN is NaN.)
 #pragma unroll
-        for (int i = 0; i < MPAD / kXR; ++i) {
-          const bool valid = k_ok && xm0 + kXR * i < p.M;
-          CpAsync16(st + i * (kXR * 128), valid ? src + i * xstep : p.x, valid ? 16 : 0);
+          for (int i = 0; i < MPAD / kXR; ++i)
+            if (i < x_rows) CpAsync16(st + i * (kXR * 128), src + i * xstep, 16);
+        } else {
+          const bool k_ok = k0 + xch * 8 < ke;
+#pragma unroll
+          for (int i = 0; i < MPAD / kXR; ++i) {
+            const bool valid = k_ok && i < x_rows;
+            CpAsync16(st + i * (kXR * 128), valid ? src + i * xstep : p.x, valid ? 16 : 0);
+          }
         }
         CpAsyncCommit();
       }
       const uint32_t bt = smem_base + L::kWOffset + buf * kTcWBytes + dst_off;
       const int8_t* next = wp + static_cast<size_t>(b + kG) * blk;
       const int next_k = k0 + kG * kTcBK + row0;  // at or past ke when this was the group's last block
+      auto convert_block = [&](auto fast) {
 #pragma unroll
-      for (int i = 0; i < kChunks; ++i) {
-        const uint4 v = wreg[i];
-        const uint32_t o0 = CodePairToBf16x2<0x1100>(v.x), o1 = CodePairToBf16x2<0x3322>(v.x);
-        const uint32_t o2 = CodePairToBf16x2<0x1100>(v.y), o3 = CodePairToBf16x2<0x3322>(v.y);
-        const uint32_t o4 = CodePairToBf16x2<0x1100>(v.z), o5 = CodePairToBf16x2<0x3322>(v.z);
-        const uint32_t o6 = CodePairToBf16x2<0x1100>(v.w), o7 = CodePairToBf16x2<0x3322>(v.w);
-        StShared16(bt + i * (kRP * 128) + s0, o0, o1, o2, o3);
-        StShared16(bt + i * (kRP * 128) + s1, o4, o5, o6, o7);
-        wreg[i] = LdWeights16(next + i * pass, col_ok && next_k + kRP * i < ke);  // the group's next block, a period ahead
-      }
+        for (int i = 0; i < kChunks; ++i) {
+          const uint4 v = wreg[i];
+          uint32_t o0, o1, o2, o3, o4, o5, o6, o7;
+          WordToBf16(v.x, o0, o1);
+          WordToBf16(v.y, o2, o3);
+          WordToBf16(v.z, o4, o5);
+          WordToBf16(v.w, o6, o7);
+          StShared16(bt + i * (kRP * 128) + s0, o0, o1, o2, o3);
+          StShared16(bt + i * (kRP * 128) + s1, o4, o5, o6, o7);
+          // the group's next block, one group period ahead
+          if constexpr (decltype(fast)::value) wreg[i] = LdWeights16Always(next + i * pass);
+          else wreg[i] = LdWeights16(next + i * pass, col_ok && next_k + kRP * i < ke);
+        }
+      };
+      // Uniform over the CTA: the next block exists, is a whole block, and the tile has all its 256 columns.
+      if (tile_full && k0 + (kG + 1) * kTcBK <= ke) convert_block(std::true_type{});
+      else convert_block(std::false_type{});
       CpAsyncWait<0>();  // this thread's part of the strip has landed
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // these writes (and the cp.async strip) -> tensor core
       __syncwarp();
@@ -427,8 +459,8 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
       float4* dst = reinterpret_cast<float4*>(tile + m * kTcTileStride + wq * 64);
 #pragma unroll
       for (int c = 0; c < 16; ++c)
-        dst[c] = make_float4(__uint_as_float(rr[4 * c]), __uint_as_float(rr[4 * c + 1]), __uint_as_float(rr[4 * c + 2]),
-                             __uint_as_float(rr[4 * c + 3]));
+        dst[c] = make_float4(__uint_as_float(rr[4 * c]), __uint_as_float(rr[4 * c + 2]), __uint_as_float(rr[4 * c + 1]),
+                             __uint_as_float(rr[4 * c + 3]));  // TMEM holds the columns as 0 2 1 3 (see WordToBf16)
     }
     if (nranks == 1) {
       __syncthreads();

@@ -185,6 +185,8 @@ def run_ours(args) -> dict:
 
     dec.set_inputs(*stage(0))
     torch.cuda.synchronize(dev)
+    if world > 1:  # the ranks enter their first exchange together (its waits are bounded)
+        torch.distributed.barrier(group=group)
     before = _native.lib().tlaloc_b200_launch_count()
     dec.capture()
     launches_per_step = (_native.lib().tlaloc_b200_launch_count() - before) // 2  # one eager warm-up + one captured
@@ -306,6 +308,9 @@ def run_ours(args) -> dict:
         "clocks": clocks.summary(), "roofline": roofline,
         "step_hbm": {"weights_bytes": sb["weights"], "kv_bytes": sb["kv"], "achieved_gbs": step_gbs, "frac": step_gbs / peak},
     }
+    if world > 1:
+        line["config"]["rank_sum"] = "peer-memory kernel" if dec.peer is not None else "nccl"
+        line["exchange_status"] = dec.exchange_status()  # 0: no bounded wait of the exchange kernel ever gave up
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(cfg_kw, batch, lens_now, seconds=args.cpu_seconds)
     if world > 1:

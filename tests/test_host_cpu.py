@@ -150,3 +150,25 @@ def test_abi_structs_match_the_vendored_xla_headers():
             f.write("\n".join(lines))
         r = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-I", REF_XLA, src], capture_output=True, text=True)
         assert r.returncode == 0, r.stderr[-3000:]
+
+
+def test_peer_sum_refuses_bad_arguments_before_touching_the_gpu():
+    """The tensor-parallel sum validates on the host first; world 1 is a no-op (no device is needed for either)."""
+    lib = N.lib()
+    bases = (ctypes.c_void_p * 2)(0x1000, 0x2000)
+    state = ctypes.c_void_p(0x3000)
+    call = lib.tlaloc_b200_peer_allreduce_f32
+    assert call(bases, 0, 0, state, 0, 9, 4, None) == N.INVALID_ARGUMENT and b"world 9" in lib.tlaloc_b200_last_error()
+    assert call(bases, 0, 0, state, 2, 2, 4, None) == N.INVALID_ARGUMENT and b"rank 2" in lib.tlaloc_b200_last_error()
+    assert call(bases, 0, 0, state, 0, 2, 6, None) == N.INVALID_ARGUMENT  # count not a multiple of 4
+    assert call(bases, 8, 0, state, 0, 2, 4, None) == N.INVALID_ARGUMENT  # values not 16-byte aligned
+    assert call(None, 0, 0, state, 0, 2, 4, None) == N.INVALID_ARGUMENT
+    misaligned = (ctypes.c_void_p * 2)(0x1000, 0x2004)
+    assert call(misaligned, 0, 0, state, 0, 2, 4, None) == N.INVALID_ARGUMENT and b"rank 1" in lib.tlaloc_b200_last_error()
+    assert call(bases, 0, 0, state, 0, 1, 4, None) == N.OK  # one rank: nothing to exchange, nothing launched
+    assert call(bases, 0, 0, state, 0, 2, 0, None) == N.OK
+
+    from tlaloc_b200.peer import PeerBuffers
+
+    with pytest.raises(ValueError):
+        PeerBuffers([(4, 4)], rank=0, world=9)

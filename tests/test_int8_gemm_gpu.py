@@ -88,6 +88,10 @@ def test_batched_rows_against_the_oracle(m):
     torch.cuda.synchronize()
     worst = close(got.cpu().numpy(), want)
     assert worst <= 1e-4 * max(1.0, np.abs(want).max())
+    # declaring the weights constant only moves their first loads ahead of the dependency wait: same bits
+    again = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), weights_const=True)
+    torch.cuda.synchronize()
+    assert torch.equal(again, got)
 
 
 @pytest.mark.parametrize("m", [1, 8, 32])

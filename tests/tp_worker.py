@@ -53,6 +53,7 @@ def main():
             swaps += 1
         ids = want_tok
     assert swaps <= 2
+    assert dec.exchange_status() == 0
     torch.distributed.barrier()
     torch.cuda.synchronize(dev)
     if rank == 0:

@@ -243,6 +243,10 @@ class Decoder:
         with torch.cuda.graph(self._graph):
             self._run_step()
 
+    def exchange_status(self) -> int:
+        """0, or the code a timed-out wait of the tensor-parallel sum left behind (see PeerBuffers.status)."""
+        return self.peer.status() if self.peer is not None else 0
+
     def step(self) -> torch.Tensor:
         """One decode step over the current inputs; returns the device tensor of next token ids [batch]."""
         if self._graph is not None:

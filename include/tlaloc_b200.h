@@ -263,6 +263,18 @@ int tlaloc_b200_peer_free(void* ptr);
 int tlaloc_b200_peer_allreduce_f32(void* const* bases, size_t data_offset, size_t flag_offset, uint32_t* state,
                                    int32_t rank, int32_t world, size_t count, void* stream);
 
+/*
+ * The same sum with the RMSNorm that follows it in the decode step (HfDecoderGraph.kt:663-699) folded in: the values
+ * are an f32 [rows, cols] matrix at data_offset; the rank that reduces a row also normalises it and writes, into
+ * EVERY rank's buffer, the summed row (in place) and x * rsqrt(mean(x^2) + eps) * gain as bf16 [rows, cols] at
+ * norm_offset.  gain: f32 [cols] in local memory (the same values on every rank) or NULL.  rows must divide by
+ * world, cols must be a multiple of 16 and at most 32768; world >= 2.  Otherwise as tlaloc_b200_peer_allreduce_f32,
+ * with which it shares the flag words and the state (calls of the two may be mixed, in the same order on every rank).
+ */
+int tlaloc_b200_peer_allreduce_rmsnorm_f32(void* const* bases, size_t data_offset, size_t norm_offset, size_t flag_offset,
+                                           uint32_t* state, const float* gain, float eps, int32_t rank, int32_t world,
+                                           int32_t rows, int32_t cols, void* stream);
+
 /* ------------------------------------------------------------------ XLA typed-FFI registration */
 
 struct PJRT_Api;

@@ -23,7 +23,7 @@ def main():
     dev = torch.device("cuda", rank)
     torch.distributed.init_process_group("nccl", device_id=dev)
     shapes = [(4, 256), (128, 8192), (3, 4), (1, 131076)]  # the last: slices that do not divide evenly into 16-byte units
-    peer = PeerBuffers(shapes, rank=rank, world=world, group=torch.distributed.group.WORLD, device=dev)
+    peer = PeerBuffers(shapes, rank=rank, world=world, group=torch.distributed.group.WORLD, device=dev, norm_shape=shapes[1])
 
     def expected(shape, round_):
         acc = rank_input(shape, 0, round_)
@@ -38,6 +38,22 @@ def main():
             peer.tensors[i].copy_(torch.from_numpy(rank_input(shape, rank, round_)))
             out = peer.all_reduce_(i)
             assert np.array_equal(out.cpu().numpy(), expected(shape, round_)), (i, round_)
+    # the sum with the RMSNorm folded in: exact sums again, and the normalised rows (bf16) on every rank within one
+    # bf16 step of RMSNorm computed from those sums in double
+    assert peer.can_fuse_norm(1) and not peer.can_fuse_norm(0)
+    gain = torch.from_numpy(np.random.default_rng(77).uniform(0.5, 1.5, size=shapes[1][1]).astype(np.float32)).to(dev)
+    for use_gain in (True, False):
+        round_ += 1
+        peer.tensors[1].copy_(torch.from_numpy(rank_input(shapes[1], rank, round_)))
+        out, normed = peer.all_reduce_norm_(1, gain if use_gain else None, 1e-5)
+        want = expected(shapes[1], round_)
+        assert np.array_equal(out.cpu().numpy(), want), round_
+        w64 = want.astype(np.float64)
+        ref = w64 / np.sqrt((w64 * w64).mean(axis=1, keepdims=True) + 1e-5)
+        if use_gain:
+            ref = ref * gain.cpu().numpy().astype(np.float64)[None, :]
+        got = normed.float().cpu().numpy().astype(np.float64)
+        assert np.all(np.abs(got - ref) <= np.abs(ref) * 2.0 ** -7 + 1e-6), float(np.abs(got - ref).max())
     # the same launches captured in a CUDA graph and replayed: 20 sums back to back on the two big buffers
     src = [torch.empty(s, device=dev) for s in shapes]
     side = torch.cuda.Stream(device=dev)
@@ -63,7 +79,7 @@ def main():
         for i in (0, 1):
             assert np.array_equal(peer.tensors[i].cpu().numpy(), expected(shapes[i], round_)), (i, rep)
     assert peer.status() == 0
-    assert int(peer.state[0].item()) == 3 * len(shapes) + 2 + 3 * 20
+    assert int(peer.state[0].item()) == 3 * len(shapes) + 2 + 2 + 3 * 20
     torch.distributed.barrier()
     torch.cuda.synchronize(dev)
     if rank == 0:

@@ -172,3 +172,17 @@ def test_peer_sum_refuses_bad_arguments_before_touching_the_gpu():
 
     with pytest.raises(ValueError):
         PeerBuffers([(4, 4)], rank=0, world=9)
+
+
+def test_fused_peer_sum_and_norm_refuses_bad_shapes_before_touching_the_gpu():
+    lib = N.lib()
+    bases = (ctypes.c_void_p * 2)(0x1000, 0x2000)
+    state = ctypes.c_void_p(0x3000)
+    call = lib.tlaloc_b200_peer_allreduce_rmsnorm_f32
+    assert call(bases, 0, 4096, 8192, state, None, 1e-5, 0, 1, 4, 256, None) == N.INVALID_ARGUMENT  # one rank: use rmsnorm
+    assert call(bases, 0, 4096, 8192, state, None, 1e-5, 0, 2, 3, 256, None) == N.INVALID_ARGUMENT  # rows do not divide
+    assert b"3 rows" in lib.tlaloc_b200_last_error()
+    assert call(bases, 0, 4096, 8192, state, None, 1e-5, 0, 2, 4, 250, None) == N.INVALID_ARGUMENT  # cols not a multiple of 16
+    assert call(bases, 0, 4096, 8192, state, None, 1e-5, 0, 2, 4, 65536, None) == N.INVALID_ARGUMENT  # a row too long for registers
+    assert call(bases, 0, 4100, 8192, state, None, 1e-5, 0, 2, 4, 256, None) == N.INVALID_ARGUMENT  # norm region misaligned
+    assert call(bases, 0, 4096, 8192, state, ctypes.c_void_p(0x4004), 1e-5, 0, 2, 4, 256, None) == N.INVALID_ARGUMENT  # gain misaligned

@@ -21,6 +21,8 @@
 // reads the status.  No multimem, no TMA, no cluster multicast: plain loads and stores on peer pointers only.
 #include <cstring>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace tlaloc_b200 {
@@ -78,7 +80,7 @@ __device__ __forceinline__ bool WaitFlag(const uint32_t* flag, uint32_t epoch)
 // state[0] = epoch of the last finished all-reduce, state[1] = CTAs finished in this launch, state[2] = status
 // (0 ok, else 1 + 16 * phase + the rank that never arrived).
 template <int W>
-__global__ void __launch_bounds__(kThreads) PeerAllReduceKernel(PeerTable t, uint32_t* state, int rank, int world_rt, size_t n4)
+__global__ void __launch_bounds__(kThreads, 1) PeerAllReduceKernel(PeerTable t, uint32_t* state, int rank, int world_rt, size_t n4)
 {
   GridDependencySync();
   const int world = W > 0 ? W : world_rt;
@@ -139,6 +141,142 @@ __global__ void __launch_bounds__(kThreads) PeerAllReduceKernel(PeerTable t, uin
   }
 }
 
+// The same exchange with the RMSNorm that follows it in the decode step folded in.  The values are a [rows, cols]
+// matrix and rank r owns rows [r * rows / world, (r + 1) * rows / world): one CTA per row, the whole reduced row in
+// registers (cols <= 8192), so the rank that reduces a row also normalises it and pushes BOTH the f32 sums and the
+// bf16 normalised row to every peer.  Saves the norm kernel's pass over the sums and one launch per exchange.
+// Arithmetic of the norm as RmsNormKernel (decode_ops.cu): sum of squares by fused multiply-adds and a block
+// reduction, rsqrt in double, the two multiplies rounded separately.
+struct PeerNormTable
+{
+  float* data[kMaxRanks];
+  __nv_bfloat16* norm[kMaxRanks];
+  uint32_t* flags[kMaxRanks];
+};
+
+constexpr int kNormParts = 4;  // CTAs that share a row: a cluster, so the row's sum of squares meets in shared memory
+constexpr int kNormVec = 4;    // float4 per thread per row: cols <= 4 * kNormParts * kNormVec * 512
+
+__device__ __forceinline__ float BlockSum512(float v, float* red)
+{
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // red may still be read from the previous row
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < kThreads / 32 ? red[lane] : 0.f;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return __shfl_sync(0xffffffffu, t, 0);
+}
+
+// Grid (row CTAs, kNormParts), clusters (1, kNormParts, 1): blockIdx.y is the part of the row this CTA holds.
+template <int W>
+__global__ void __launch_bounds__(kThreads, 1)
+PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, float eps, int rank, int world_rt, int rows, int cols)
+{
+  GridDependencySync();
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int world = W > 0 ? W : world_rt;
+  __shared__ uint32_t s_epoch, s_last, s_dead;
+  __shared__ float red[kThreads / 32];
+  __shared__ float part[2];  // this CTA's share of a row's sum of squares, double-buffered over rows
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    s_epoch = *reinterpret_cast<volatile uint32_t*>(state) + 1u;
+    s_dead = reinterpret_cast<volatile uint32_t*>(state)[2];
+    s_last = 0;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const bool dead = s_dead != 0;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && tid < world) StoreFlag(t.flags[tid] + rank, epoch);
+  if (!dead && tid < world) {
+    if (!WaitFlag(t.flags[rank] + tid, epoch)) atomicCAS(state + 2, 0u, 1u + tid);
+  }
+  __syncthreads();
+
+  const int part4 = (cols >> 2) / kNormParts;  // float4 per part of a row
+  const int c_lo = blockIdx.y * part4;
+  const int r_lo = rows * rank / world, r_hi = rows * (rank + 1) / world;
+  int trip = 0;
+  for (int row = r_lo + blockIdx.x; row < r_hi; row += gridDim.x, ++trip) {
+    const size_t base = static_cast<size_t>(row) * cols;
+    float4 sum[kNormVec];
+#pragma unroll
+    for (int i = 0; i < kNormVec; ++i) {
+      const int c = tid + i * kThreads;
+      sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < part4) {
+        float4 v[kMaxRanks];
+#pragma unroll
+        for (int q = 0; q < kMaxRanks; ++q)
+          if (q < world) v[q] = LoadPeer(t.data[q] + base + 4 * (c_lo + c));
+        float4 a = v[0];
+#pragma unroll
+        for (int q = 1; q < kMaxRanks; ++q)
+          if (q < world) { a.x += v[q].x; a.y += v[q].y; a.z += v[q].z; a.w += v[q].w; }
+        sum[i] = a;
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormVec; ++i)
+      ss = fmaf(sum[i].x, sum[i].x, fmaf(sum[i].y, sum[i].y, fmaf(sum[i].z, sum[i].z, fmaf(sum[i].w, sum[i].w, ss))));
+    ss = BlockSum512(ss, red);
+    if (tid == 0) part[trip & 1] = ss;
+    cluster.sync();  // every part's share is written; the other buffer was last read a whole trip ago
+    float total = 0.f;
+#pragma unroll
+    for (int q = 0; q < kNormParts; ++q) total += cluster.map_shared_rank(part, q)[trip & 1];  // fixed order: same bits in every part
+    const float rsq = static_cast<float>(1.0 / sqrt(static_cast<double>(total / static_cast<float>(cols) + eps)));
+#pragma unroll
+    for (int i = 0; i < kNormVec; ++i) {
+      const int c = tid + i * kThreads;
+      if (c < part4) {
+        const int cc = c_lo + c;
+        const float4 g = gain != nullptr ? __ldg(reinterpret_cast<const float4*>(gain) + cc) : make_float4(1.f, 1.f, 1.f, 1.f);
+        const float4 a = sum[i];
+        float n0 = __fmul_rn(a.x, rsq), n1 = __fmul_rn(a.y, rsq), n2 = __fmul_rn(a.z, rsq), n3 = __fmul_rn(a.w, rsq);
+        if (gain != nullptr) { n0 = __fmul_rn(n0, g.x); n1 = __fmul_rn(n1, g.y); n2 = __fmul_rn(n2, g.z); n3 = __fmul_rn(n3, g.w); }
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(n0, n1), hi = __floats2bfloat162_rn(n2, n3);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+#pragma unroll
+        for (int q = 0; q < kMaxRanks; ++q) {
+          if (q < world) {
+            *reinterpret_cast<float4*>(t.data[q] + base + 4 * cc) = a;
+            *reinterpret_cast<uint2*>(t.norm[q] + base + 4 * cc) = packed;
+          }
+        }
+      }
+    }
+  }
+  cluster.sync();  // no CTA of a row's cluster leaves while another may still read its share
+
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    s_last = atomicAdd(state + 1, 1u) == gridDim.x * gridDim.y - 1 ? 1u : 0u;
+    __threadfence();
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (tid < world) {
+    __threadfence_system();
+    StoreFlag(t.flags[tid] + world + rank, epoch);
+    if (!dead && !WaitFlag(t.flags[rank] + world + tid, epoch)) atomicCAS(state + 2, 0u, 17u + tid);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    state[1] = 0;
+    state[0] = epoch;
+  }
+}
+
 }  // namespace
 
 int LaunchPeerAllReduce(void* const* bases, size_t data_offset, size_t flag_offset, uint32_t* state, int rank, int world,
@@ -169,6 +307,47 @@ int LaunchPeerAllReduce(void* const* bases, size_t data_offset, size_t flag_offs
     default: e = LaunchChained(PeerAllReduceKernel<0>, grid, kThreads, 0, st, t, state, rank, world, n4); break;
   }
   if (e != cudaSuccess) return CudaFail("peer_allreduce launch", e);
+  CountLaunches(1);
+  return kOk;
+}
+
+int LaunchPeerAllReduceNorm(void* const* bases, size_t data_offset, size_t norm_offset, size_t flag_offset, uint32_t* state,
+                            const float* gain, float eps, int rank, int world, int rows, int cols, cudaStream_t st)
+{
+  if (world < 2 || world > kMaxRanks) return Fail(kInvalid, "peer_allreduce_rmsnorm: world %d outside [2, %d]", world, kMaxRanks);
+  if (rank < 0 || rank >= world) return Fail(kInvalid, "peer_allreduce_rmsnorm: rank %d outside [0, %d)", rank, world);
+  if (!bases || !state) return Fail(kInvalid, "peer_allreduce_rmsnorm: null base table or state");
+  if (rows < 1 || cols < 16 || cols % (4 * kNormParts) != 0 || cols > 4 * kNormParts * kNormVec * kThreads) {
+    return Fail(kInvalid, "peer_allreduce_rmsnorm: %d x %d: rows >= 1, cols a multiple of 16 up to %d", rows, cols,
+                4 * kNormParts * kNormVec * kThreads);
+  }
+  if (rows % world != 0) return Fail(kInvalid, "peer_allreduce_rmsnorm: %d rows do not divide over %d ranks", rows, world);
+  if (data_offset % 16 != 0 || norm_offset % 16 != 0 || flag_offset % 4 != 0 || (reinterpret_cast<uintptr_t>(gain) & 15) != 0) {
+    return Fail(kInvalid, "peer_allreduce_rmsnorm: offsets and the gain must be 16-byte aligned");
+  }
+  PeerNormTable t{};
+  for (int q = 0; q < world; ++q) {
+    if (!bases[q] || reinterpret_cast<uintptr_t>(bases[q]) % 16 != 0)
+      return Fail(kInvalid, "peer_allreduce_rmsnorm: base of rank %d is null or not 16-byte aligned", q);
+    t.data[q] = reinterpret_cast<float*>(static_cast<char*>(bases[q]) + data_offset);
+    t.norm[q] = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(bases[q]) + norm_offset);
+    t.flags[q] = reinterpret_cast<uint32_t*>(static_cast<char*>(bases[q]) + flag_offset);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(rows / world < 36 ? rows / world : 36, kNormParts, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.stream = st;
+  cudaLaunchAttribute attrs[2];
+  cfg.numAttrs = ChainAttributes(attrs, kNormParts);
+  cfg.attrs = attrs;
+  cudaError_t e;
+  switch (world) {
+    case 2: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<2>, t, state, gain, eps, rank, world, rows, cols); break;
+    case 4: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<4>, t, state, gain, eps, rank, world, rows, cols); break;
+    case 8: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<8>, t, state, gain, eps, rank, world, rows, cols); break;
+    default: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<0>, t, state, gain, eps, rank, world, rows, cols); break;
+  }
+  if (e != cudaSuccess) return CudaFail("peer_allreduce_rmsnorm launch", e);
   CountLaunches(1);
   return kOk;
 }
@@ -223,4 +402,12 @@ extern "C" int tlaloc_b200_peer_allreduce_f32(void* const* bases, size_t data_of
                                               int32_t rank, int32_t world, size_t count, void* stream)
 {
   return LaunchPeerAllReduce(bases, data_offset, flag_offset, state, rank, world, count, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tlaloc_b200_peer_allreduce_rmsnorm_f32(void* const* bases, size_t data_offset, size_t norm_offset,
+                                                      size_t flag_offset, uint32_t* state, const float* gain, float eps,
+                                                      int32_t rank, int32_t world, int32_t rows, int32_t cols, void* stream)
+{
+  return LaunchPeerAllReduceNorm(bases, data_offset, norm_offset, flag_offset, state, gain, eps, rank, world, rows, cols,
+                                 static_cast<cudaStream_t>(stream));
 }

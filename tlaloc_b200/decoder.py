@@ -97,12 +97,15 @@ class Decoder:
         # the library's own exchange kernel (TLALOC_B200_TP_REDUCE=nccl keeps them private and calls NCCL instead)
         self.peer = None
         if world > 1 and os.environ.get("TLALOC_B200_TP_REDUCE", "peer") == "peer":
-            self.peer = PeerBuffers([(B, d), (B, d)], rank=rank, world=world, group=group, device=dev)
+            self.peer = PeerBuffers([(B, d), (B, d)], rank=rank, world=world, group=group, device=dev, norm_shape=(B, d))
             self.h, self.h2 = self.peer.tensors
         else:
             self.h = torch.empty((B, d), **f32)
             self.h2 = torch.empty((B, d), **f32)
-        self.hn = torch.empty((B, d), **bf)
+        # RMSNorm output; with the peer-memory sum it lives in the peer block and the exchange kernel fills it
+        self.fuse_norm = (self.peer is not None and self.peer.can_fuse_norm(0)
+                          and os.environ.get("TLALOC_B200_TP_FUSE_NORM", "0") != "0")
+        self.hn = self.peer.norm_out if self.fuse_norm else torch.empty((B, d), **bf)
         self.qkv = torch.empty((B, nqkv), **f32)
         self.q_rot = torch.empty((B, self.hq, hd), **f32)
         self.att = torch.empty((B, self.hq, hd), **bf)
@@ -195,21 +198,31 @@ class Decoder:
         q3 = self.qkv[:, :hq * hd].unflatten(1, (hq, hd))
         k3 = self.qkv[:, hq * hd:(hq + hk) * hd].unflatten(1, (hk, hd))
         v3 = self.qkv[:, (hq + hk) * hd:].unflatten(1, (hk, hd))
+        fused = self.fuse_norm  # the sum over ranks also produces the next RMSNorm's output
         for l, lw in enumerate(self.layers):
-            ops.rmsnorm(h, lw["ln1"], cfg.rms_eps, out=self.hn)
+            if l == 0 or not fused:
+                ops.rmsnorm(h, lw["ln1"], cfg.rms_eps, out=self.hn)
             ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True)
             ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
                               self.value_pools[l], q_out=self.q_rot)
             ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
                                 scale=cfg.scale, out=self.att, scratch=self.att_scratch)
             ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, weights_const=True)
-            self._all_reduce(h2)
-            ops.rmsnorm(h2, lw["ln2"], cfg.rms_eps, out=self.hn)
+            if fused:
+                self.peer.all_reduce_norm_(1, lw["ln2"], cfg.rms_eps)
+            else:
+                self._all_reduce(h2)
+                ops.rmsnorm(h2, lw["ln2"], cfg.rms_eps, out=self.hn)
             ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True)
             ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
             ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True)
-            self._all_reduce(h)
-        ops.rmsnorm(h, self.final_norm, cfg.rms_eps, out=self.hn)
+            if fused:
+                nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
+                self.peer.all_reduce_norm_(0, nxt, cfg.rms_eps)
+            else:
+                self._all_reduce(h)
+        if not fused:
+            ops.rmsnorm(h, self.final_norm, cfg.rms_eps, out=self.hn)
         if isinstance(self.head, tuple):
             ops.int8_gemm(self.hn, *self.head, out=self.logits, weights_const=True)
         else:

@@ -32,7 +32,7 @@ class PeerBuffers:
     in the same order, and `close()` it together.
     """
 
-    def __init__(self, shapes, *, rank: int, world: int, group=None, device="cuda:0"):
+    def __init__(self, shapes, *, rank: int, world: int, group=None, device="cuda:0", norm_shape=None):
         if not 1 <= world <= 8:
             raise ValueError(f"world {world} outside [1, 8]")
         self.rank, self.world, self.group, self.device = rank, world, group, torch.device(device)
@@ -43,6 +43,11 @@ class PeerBuffers:
                 raise ValueError(f"a summed tensor needs a multiple of 4 elements, got shape {tuple(shp)}")
             self.offsets.append(off)
             off += (4 * n + _ALIGN - 1) // _ALIGN * _ALIGN
+        # one bf16 matrix for the fused sum + RMSNorm (all_reduce_norm_): every rank receives every normalised row
+        self.norm_offset, self.norm_shape = off, None
+        if norm_shape is not None:
+            self.norm_shape = tuple(int(v) for v in norm_shape)
+            off += (2 * int(np.prod(self.norm_shape)) + _ALIGN - 1) // _ALIGN * _ALIGN
         self.flag_offset = off
         self.nbytes = off + _ALIGN
         lib = N.lib()
@@ -67,6 +72,10 @@ class PeerBuffers:
             self._opened.append(p.value)
         whole = torch.as_tensor(_DeviceSpan(self._local, self.nbytes // 4), device=self.device)
         self.tensors = [whole[o // 4:o // 4 + int(np.prod(s))].view(*s) for o, s in zip(self.offsets, shapes)]
+        self.norm_out = None
+        if self.norm_shape is not None:
+            n = int(np.prod(self.norm_shape))
+            self.norm_out = whole[self.norm_offset // 4:self.norm_offset // 4 + (n + 1) // 2].view(torch.bfloat16)[:n].view(*self.norm_shape)
         self.state = torch.zeros((4,), dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         if world > 1:
@@ -79,6 +88,22 @@ class PeerBuffers:
                                                        self.state.data_ptr(), self.rank, self.world, t.numel(),
                                                        torch.cuda.current_stream(self.device).cuda_stream))
         return t
+
+    def can_fuse_norm(self, index: int) -> bool:
+        """Whether all_reduce_norm_ takes tensor `index`: a [rows, cols] matrix the shape of the norm region, rows
+        divisible by the ranks, cols a multiple of 16 up to 32768."""
+        t = self.tensors[index]
+        return (self.world > 1 and self.norm_out is not None and t.dim() == 2 and tuple(t.shape) == self.norm_shape
+                and t.shape[0] % self.world == 0 and t.shape[1] % 16 == 0 and t.shape[1] <= 32768)
+
+    def all_reduce_norm_(self, index: int, gain, eps: float):
+        """Sum tensor `index` over the ranks in place AND leave RMSNorm(sum) * gain as bf16 in `norm_out`, on every rank."""
+        t = self.tensors[index]
+        N.check(N.lib().tlaloc_b200_peer_allreduce_rmsnorm_f32(
+            self._bases, self.offsets[index], self.norm_offset, self.flag_offset, self.state.data_ptr(),
+            None if gain is None else gain.data_ptr(), float(eps), self.rank, self.world, t.shape[0], t.shape[1],
+            torch.cuda.current_stream(self.device).cuda_stream))
+        return t, self.norm_out
 
     def status(self) -> int:
         """0, or the code a timed-out wait left (1 + 16 * phase + the rank that did not arrive).  Synchronises."""

@@ -462,18 +462,24 @@ def cpu_sample(cfg_kw, lens, b_sample, threads):
 
 
 def cpu_baseline(cfg_kw, batch, lens, seconds=15.0) -> dict:
+    """About `seconds` of CPU work: the largest batch slice whose one-layer sample stays under a third of the budget,
+    then as many one-layer samples as fit (each layer of the step does the same work)."""
     import oracle
 
     threads = oracle.host_threads()
     b = 1
     t = cpu_sample(cfg_kw, lens, b, threads)
-    while t < seconds / 3 and b * 2 <= min(batch, 16):
+    while t < seconds / 3 and b * 2 <= batch:
         b *= 2
         t = cpu_sample(cfg_kw, lens, b, threads)
-    step_s = t * cfg_kw["num_layers"] * (batch / b)
+    times = [t]
+    while sum(times) + t < seconds and len(times) < cfg_kw["num_layers"]:
+        times.append(cpu_sample(cfg_kw, lens, b, threads))
+    per_layer = float(np.mean(times))
+    step_s = per_layer * cfg_kw["num_layers"] * (batch / b)
     return {"value": batch / step_s, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"one of {cfg_kw['num_layers']} layers (int8 projections + paged attention) for {b} of {batch} "
-                      f"sequences took {t:.2f} s on {threads} threads; scaled by layers x batch/{b}"}
+            "sample": f"{len(times)} of {cfg_kw['num_layers']} layers (int8 projections + paged attention) for {b} of {batch} "
+                      f"sequences: {sum(times):.1f} s on {threads} threads, {per_layer:.2f} s per layer; scaled by layers x batch/{b}"}
 
 
 def run_reference(args) -> dict:
@@ -488,7 +494,7 @@ def run_reference(args) -> dict:
     rng = np.random.default_rng(5)
     lens = (rng.integers(lo, hi + 1, size=batch) + 1).astype(np.int64)
     threads = oracle.host_threads()
-    b = 1
+    b = min(16, batch)  # a step's sample: one layer for 16 sequences (about half a second on 16 threads)
     times = []
     for i in range(args.warmup + args.steps):
         t = cpu_sample(cfg_kw, lens, b, threads)

@@ -1,4 +1,4 @@
-// The int8 weight-only projection for batches of rows (17 <= M <= 256 per launch) on the 5th-generation tensor
+// The int8 weight-only projection for batches of rows (33 and more; at most 256 per launch) on the 5th-generation tensor
 // cores: y = (cast(x) @ cast(codes)) * scale (HfDecoderGraph.proj, ir/.../inference/HfDecoderGraph.kt:625-655).
 //
 // Formulation: D[m, n] = sum_k X[m, k] W[k, n].  The activation rows are the MMA's M dimension (TMEM lanes, always
@@ -9,7 +9,7 @@
 //      128-byte-swizzled operand layout;
 //   2. turns the block's int8 codes, which its threads loaded from global memory STRAIGHT INTO REGISTERS one group
 //      period earlier (the reference's own [K, N] layout: a warp reads two 256-byte runs), into exact bf16
-//      (byte-permute, two logic ops, one packed fma per pair) and stores them as the MN-major 128-byte-swizzled B
+//      (two logic ops and one packed fma per pair, plus one shift per word) and stores them as the MN-major 128-byte-swizzled B
 //      operand: W's rows are contiguous along N, which is exactly MN-major, so 16 codes become two 16-byte stores and
 //      nothing is transposed.  Each chunk's registers are refilled with the group's next block as soon as they are
 //      consumed.  Raw codes never touch shared memory: shared-memory bandwidth (operand reads by the tensor core +
@@ -20,9 +20,11 @@
 // Why groups: with all sixteen warps sharing every block, each warp's serial chain (wait, request, convert, fence,
 // arrive: ~1400 cycles, mostly instruction latency) was paid once per block and set the pace; a group pays the fixed
 // part once per FOUR blocks and the groups' chains overlap.
-// Epilogue: tcgen05.ld brings the accumulator to registers (lane = activation row, eight output columns at a time);
-// with one K slice they are scaled and stored directly (32 bytes per thread); with several, the slices of a column
-// tile form a thread-block cluster and meet in distributed shared memory, summed in rank order (deterministic).
+// Epilogue: tcgen05.ld brings the accumulator to registers (lane = activation row, 64 output columns per thread) and
+// a row-major tile in shared memory turns that into 1 KB coalesced row stores with scale and residual applied; with
+// several K slices, the slices of a column tile form a thread-block cluster and their tiles meet in distributed
+// shared memory, summed in rank order (deterministic).  The dependency wait of the programmatic launch sits after the
+// on-chip set-up (and, for constant weights, after the first weight loads have been requested).
 // Every mbarrier wait is bounded: on a time-out the kernel records it in a status word, frees its TMEM and returns.
 #include <cooperative_groups.h>
 

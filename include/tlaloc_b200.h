@@ -174,7 +174,11 @@ size_t tlaloc_b200_int8_gemm_scratch_bytes(int32_t m, int32_t k, int32_t n);
  *   scales  device f32 [N], or NULL for none
  *   residual device f32 [M, N] or NULL: added after the scale (the layer's residual add)
  *   y       device [M, N]  y_dtype F32 | BF16
- *   scratch device f32, scratch_bytes >= tlaloc_b200_int8_gemm_scratch_bytes(m, k, n)
+ *   scratch device memory, 16-byte aligned, contents undefined on entry and exit, or NULL.  An F32 x needs the
+ *           first 2 * m * k bytes (its bf16 copy).  With all of tlaloc_b200_int8_gemm_scratch_bytes(m, k, n) bytes a
+ *           batch of more than 32 rows may also spread its work evenly over the SMs (partial tiles handed over through
+ *           the scratch); with less, or NULL, it runs the form that needs none.  Two calls whose kernels can overlap
+ *           on the GPU need scratch of their own.
  *
  * flags: TLALOC_B200_GEMM_EXACT runs the order-faithful kernel (f32 accumulate
  * in increasing k with separate multiply and add, bit-identical to the

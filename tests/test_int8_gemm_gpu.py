@@ -163,3 +163,35 @@ def test_quantized_weights_round_trip_like_the_reference_identity():
     want = (x.astype(np.float64) @ deq.astype(np.float64)).astype(np.float32)
     assert np.abs(got - want).max() <= 4.7e-6 * max(1.0, np.abs(want).max()) * 4
     assert np.abs(deq.T - w).max() <= np.abs(w).max() / 127.0 * 0.5 + 1e-9
+
+
+def test_evenly_spread_launch_is_exact_too():
+    """The stream-K form of the tensor-core kernel (off by default, $TLALOC_B200_GEMM_STREAMK=2 forces it): CTAs take
+    equal runs of (column tile, k block) units, partial tiles cross CTAs through the caller's scratch.  The switch is
+    read once per process, so the check runs in a child process."""
+    import os
+    import subprocess
+    import sys
+
+    code = r'''
+import numpy as np, torch, sys
+sys.path.insert(0, %r)
+from tlaloc_b200 import ops, _native as N
+rng = np.random.default_rng(5)
+for (m, k, n) in [(128, 4096, 4096), (100, 1024, 14336), (64, 688, 256), (128, 8192, 1280)]:
+    x = rng.integers(-8, 9, size=(m, k)).astype(np.float32)
+    codes = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    scales = np.exp2(rng.integers(-8, -2, size=n)).astype(np.float32)
+    res = rng.integers(-50, 50, size=(m, n)).astype(np.float32)
+    want = (x.astype(np.float64) @ codes.astype(np.float64)).astype(np.float32) * scales[None, :] + res
+    t = lambda a, dt=None: torch.from_numpy(a).cuda() if dt is None else torch.from_numpy(a).cuda().to(dt)
+    for rep in range(2):  # twice: the second launch meets the first one's flags in the recycled scratch
+        got = ops.int8_gemm(t(x, torch.bfloat16), t(codes), t(scales), residual=t(res))
+        torch.cuda.synchronize()
+        assert N.lib().tlaloc_b200_device_status() == 0
+        assert np.array_equal(got.cpu().numpy(), want), (m, k, n, rep)
+print("stream ok")
+''' % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TLALOC_B200_GEMM_STREAMK="2")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=240)
+    assert out.returncode == 0 and "stream ok" in out.stdout, out.stdout[-1500:] + out.stderr[-1500:]

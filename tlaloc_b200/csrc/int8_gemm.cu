@@ -401,12 +401,15 @@ cudaError_t LaunchGemvRows(const GemmParams& p, int rows, cudaStream_t st)
 
 }  // namespace
 
+// Scratch layout: [bf16 copy of an f32 x, rounded up to 256 bytes][partial tiles and flags of the evenly spread
+// tensor-core launch].  The second part is optional: a shorter buffer only rules that launch form out.
+static size_t CastBytes(int m, int k) { return (sizeof(__nv_bfloat16) * static_cast<size_t>(m) * k + 255) / 256 * 256; }
+
 extern "C" size_t tlaloc_b200_int8_gemm_scratch_bytes(int32_t m, int32_t k, int32_t n)
 {
   (void)n;
   if (m <= 0 || k <= 0) return 0;
-  // Room for a bf16 copy of an f32 activation matrix.
-  return sizeof(__nv_bfloat16) * static_cast<size_t>(m) * k;
+  return CastBytes(m, k) + (m > 32 ? TcStreamScratchBytes() : 0);
 }
 
 extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_t* codes, const float* scales,
@@ -452,8 +455,12 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
     e = PrepareInt8GemmTcKernels();
     if (e != cudaSuccess) return CudaFail("INT8_PROJ set-up", e);
     int launches = 0;
+    const size_t cast_bytes = CastBytes(m, k);
+    const bool has_stream = scratch != nullptr && scratch_bytes >= cast_bytes + TcStreamScratchBytes();
     e = LaunchInt8GemmTc(xb, codes, scales, residual, y, y_dtype, m, k, n, st, &launches,
-                         (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0);
+                         (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0,
+                         has_stream ? reinterpret_cast<unsigned char*>(scratch) + cast_bytes : nullptr,
+                         has_stream ? scratch_bytes - cast_bytes : 0);
     if (e != cudaSuccess) return CudaFail("INT8_PROJ tensor-core launch", e);
     CountLaunches(launches);
     return kOk;

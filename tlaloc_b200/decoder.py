@@ -112,6 +112,9 @@ class Decoder:
         self.gu = torch.empty((B, 2 * self.f), **f32)
         self.act = torch.empty((B, self.f), **bf)
         self.logits = torch.empty((B, cfg.vocab // world), **f32)
+        # scratch of the projections (partial tiles of the evenly spread tensor-core launch); one buffer serves them all
+        kmax = max(d, self.hq * hd, self.f)
+        self.gemm_scratch = torch.empty((ops.int8_gemm_scratch_bytes(B, kmax, d) + 3) // 4, **f32)
         self.next_ids = torch.zeros((B,), **i32)
         self.best = torch.empty((B,), **f32)
         shape = ops.parse_paged_attention(self.q_rot, self.key_pools[0], self.value_pools[0], self.block_tables,
@@ -202,20 +205,20 @@ class Decoder:
         for l, lw in enumerate(self.layers):
             if l == 0 or not fused:
                 ops.rmsnorm(h, lw["ln1"], cfg.rms_eps, out=self.hn)
-            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True)
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True, scratch=self.gemm_scratch)
             ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
                               self.value_pools[l], q_out=self.q_rot)
             ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
                                 scale=cfg.scale, out=self.att, scratch=self.att_scratch)
-            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, weights_const=True)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, weights_const=True, scratch=self.gemm_scratch)
             if fused:
                 self.peer.all_reduce_norm_(1, lw["ln2"], cfg.rms_eps)
             else:
                 self._all_reduce(h2)
                 ops.rmsnorm(h2, lw["ln2"], cfg.rms_eps, out=self.hn)
-            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True)
+            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True, scratch=self.gemm_scratch)
             ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
-            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True)
+            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True, scratch=self.gemm_scratch)
             if fused:
                 nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
                 self.peer.all_reduce_norm_(0, nxt, cfg.rms_eps)
@@ -224,7 +227,7 @@ class Decoder:
         if not fused:
             ops.rmsnorm(h, self.final_norm, cfg.rms_eps, out=self.hn)
         if isinstance(self.head, tuple):
-            ops.int8_gemm(self.hn, *self.head, out=self.logits, weights_const=True)
+            ops.int8_gemm(self.hn, *self.head, out=self.logits, weights_const=True, scratch=self.gemm_scratch)
         else:
             self.logits.copy_(ops.dense_gemm_exact(self.hn, self.head))
         ops.argmax(self.logits, out=self.next_ids)

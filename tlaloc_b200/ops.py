@@ -92,7 +92,8 @@ def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.floa
         raise ValueError(f"INT8_PROJ: x [M, K] x codes int8 [K, N] with scales [N]; got {tuple(x.shape)}, {tuple(codes.shape)}")
     if out is None:
         out = torch.empty((M, Nn), dtype=out_dtype, device=x.device)
-    if scratch is None and x.dtype == torch.float32 and not exact:
+    if scratch is None and not exact and (x.dtype == torch.float32 or M > 32):
+        # an f32 x is cast to bf16 there; batches of rows also use it to spread their blocks evenly over the SMs
         scratch = torch.empty((N.lib().tlaloc_b200_int8_gemm_scratch_bytes(M, K, Nn) + 3) // 4, dtype=torch.float32,
                               device=x.device)
     flags = ((N.GEMM_EXACT if exact else 0) | (N.GEMM_X_F32_EXACT if x_f32_exact else 0)
@@ -101,6 +102,10 @@ def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.floa
                                           _ptr(scratch), 0 if scratch is None else scratch.numel() * 4, M, K, Nn, flags,
                                           _stream()))
     return out
+
+
+def int8_gemm_scratch_bytes(m: int, k: int, n: int) -> int:
+    return int(N.lib().tlaloc_b200_int8_gemm_scratch_bytes(m, k, n))
 
 
 def dense_gemm_exact(x, w, *, x_f32_exact=False):

@@ -104,7 +104,7 @@ class Decoder:
             self.h2 = torch.empty((B, d), **f32)
         # RMSNorm output; with the peer-memory sum it lives in the peer block and the exchange kernel fills it
         self.fuse_norm = (self.peer is not None and self.peer.can_fuse_norm(0)
-                          and os.environ.get("TLALOC_B200_TP_FUSE_NORM", "0") != "0")
+                          and os.environ.get("TLALOC_B200_TP_FUSE_NORM", "1") != "0")
         self.hn = self.peer.norm_out if self.fuse_norm else torch.empty((B, d), **bf)
         self.qkv = torch.empty((B, nqkv), **f32)
         self.q_rot = torch.empty((B, self.hq, hd), **f32)

@@ -581,7 +581,7 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
 // out = sum_s exp(m_s - max) acc_s / sum_s exp(m_s - max) l_s, in slice order (deterministic).
 
 constexpr int kCombineThreads = 128;  // four warps, one (row, head) each
-constexpr int kCombineMaxPairs = 4;   // channel pairs per lane: D <= 256
+constexpr int kCombineBatch = 8;      // slices whose records are in flight together
 
 __device__ __forceinline__ void StorePair(float* o, float a, float b) { *reinterpret_cast<float2*>(o) = make_float2(a, b); }
 __device__ __forceinline__ void StorePair(__nv_bfloat16* o, float a, float b)
@@ -593,7 +593,7 @@ __device__ __forceinline__ void StorePair(__nv_bfloat16* o, float a, float b)
 // holds the max and sum of slice s_lo + l (32 slices at a time), the weights travel by shuffle, and every lane owns
 // the channel pairs 2l, 2l + 1 (+ 64, ...).  The loads of a trip do not depend on one another, so a merge costs about
 // two trips to L2 rather than one per slice.  D is even (RoPE pairs) or the scalar tail handles the last channel.
-template <typename OT>
+template <typename OT, int PAIRS>  // PAIRS channel pairs per lane: D <= 64 * PAIRS
 __global__ void __launch_bounds__(kCombineThreads) PaCombine(PaParams p)
 {
   GridDependencySync();
@@ -607,39 +607,62 @@ __global__ void __launch_bounds__(kCombineThreads) PaCombine(PaParams p)
   const int s_lo = first / p.slice, s_hi = min(p.S, (len + p.slice - 1) / p.slice);
   const size_t stride = static_cast<size_t>(p.R) * p.H * (p.D + 2);
   const float* base = Record(p, 0, row, head);
-  float mx = -INFINITY;
-  for (int s = s_lo + lane; s < s_hi; s += 32) mx = fmaxf(mx, base[s * stride]);
+  const int pairs = p.D >> 1;
+  const bool even = (p.D & 1) == 0 && (reinterpret_cast<uintptr_t>(p.scratch) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7) == 0;
+  // Eight slices at a time: their records are requested together (a live slice's record is always written, so the
+  // loads need not wait for the weights), then folded in slice order.
+  auto load_batch = [&](int s0, int count, float2(&v)[kCombineBatch][PAIRS]) {
+#pragma unroll
+    for (int u = 0; u < kCombineBatch; ++u) {
+      const float* rec = base + (s0 + u) * stride + 2;
+#pragma unroll
+      for (int j = 0; j < PAIRS; ++j) {
+        const int pr = lane + 32 * j;
+        v[u][j] = make_float2(0.f, 0.f);
+        if (u < count && pr < pairs) {
+          if (even) v[u][j] = *reinterpret_cast<const float2*>(rec + 2 * pr);  // records start on 8-byte boundaries only for even D
+          else v[u][j] = make_float2(rec[2 * pr], rec[2 * pr + 1]);
+        }
+      }
+    }
+  };
+  // One trip to memory brings this lane's slice header {max, sum} of the first 32 slices AND the first eight records.
+  float hm = -INFINITY, hs = 0.f;
+  if (s_lo + lane < s_hi) {
+    hm = base[(s_lo + lane) * stride];
+    hs = base[(s_lo + lane) * stride + 1];
+  }
+  float2 v[kCombineBatch][PAIRS];
+  load_batch(s_lo, min(kCombineBatch, s_hi - s_lo), v);
+  float mx = hm;
+  for (int s = s_lo + 32 + lane; s < s_hi; s += 32) mx = fmaxf(mx, base[s * stride]);  // more than 32 slices: rare
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   float denom = 0.f;
-  float acc[2 * kCombineMaxPairs];
+  float acc[2 * PAIRS];
 #pragma unroll
-  for (int i = 0; i < 2 * kCombineMaxPairs; ++i) acc[i] = 0.f;
-  const int pairs = p.D >> 1;
-  const bool even = (p.D & 1) == 0 && (reinterpret_cast<uintptr_t>(p.scratch) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7) == 0;
+  for (int i = 0; i < 2 * PAIRS; ++i) acc[i] = 0.f;
   for (int c0 = s_lo; c0 < s_hi; c0 += 32) {
     const int mine = c0 + lane;
     float w_l = 0.f, ws_l = 0.f;
     if (mine < s_hi) {
-      const float m = base[mine * stride];
+      const float m = c0 == s_lo ? hm : base[mine * stride];
       w_l = m == -INFINITY ? 0.f : expf(m - mx);
-      ws_l = w_l != 0.f ? w_l * base[mine * stride + 1] : 0.f;
+      ws_l = w_l != 0.f ? w_l * (c0 == s_lo ? hs : base[mine * stride + 1]) : 0.f;
     }
     const int n = min(32, s_hi - c0);
-    for (int i = 0; i < n; ++i) {
-      const float w = __shfl_sync(0xffffffffu, w_l, i), ws = __shfl_sync(0xffffffffu, ws_l, i);
-      if (w != 0.f) {  // uniform over the warp
-        denom += ws;
-        const float* rec = base + (c0 + i) * stride + 2;
+    for (int i0 = 0; i0 < n; i0 += kCombineBatch) {
+      if (c0 != s_lo || i0 != 0) load_batch(c0 + i0, min(kCombineBatch, n - i0), v);
 #pragma unroll
-        for (int j = 0; j < kCombineMaxPairs; ++j) {
-          const int pr = lane + 32 * j;
-          if (pr < pairs) {
-            float2 v;
-            if (even) v = *reinterpret_cast<const float2*>(rec + 2 * pr);  // records start on 8-byte boundaries only for even D
-            else v = make_float2(rec[2 * pr], rec[2 * pr + 1]);
-            acc[2 * j] += w * v.x;
-            acc[2 * j + 1] += w * v.y;
+      for (int u = 0; u < kCombineBatch; ++u) {
+        const int i = i0 + u;
+        const float w = __shfl_sync(0xffffffffu, w_l, i & 31), ws = __shfl_sync(0xffffffffu, ws_l, i & 31);
+        if (i < n && w != 0.f) {  // uniform over the warp
+          denom += ws;
+#pragma unroll
+          for (int j = 0; j < PAIRS; ++j) {
+            acc[2 * j] += w * v[u][j].x;
+            acc[2 * j + 1] += w * v[u][j].y;
           }
         }
       }
@@ -648,7 +671,7 @@ __global__ void __launch_bounds__(kCombineThreads) PaCombine(PaParams p)
   OT* out = static_cast<OT*>(p.out) + static_cast<size_t>(rh) * p.D;
   const bool empty = mx == -INFINITY || denom == 0.f;
 #pragma unroll
-  for (int j = 0; j < kCombineMaxPairs; ++j) {
+  for (int j = 0; j < PAIRS; ++j) {
     const int pr = lane + 32 * j;
     if (pr < pairs) {
       const float a = empty ? 0.f : acc[2 * j] / denom, b = empty ? 0.f : acc[2 * j + 1] / denom;
@@ -910,9 +933,13 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
   if (e != cudaSuccess) return CudaFail("PAGED_ATTENTION slice launch", e);
   const unsigned cgrid = static_cast<unsigned>((p.R * p.H + kCombineThreads / 32 - 1) / (kCombineThreads / 32));
   if (out_dtype == TLALOC_B200_F32) {
-    e = LaunchChained(PaCombine<float>, cgrid, kCombineThreads, 0, st, p);
+    e = p.D <= 64    ? LaunchChained(PaCombine<float, 1>, cgrid, kCombineThreads, 0, st, p)
+        : p.D <= 128 ? LaunchChained(PaCombine<float, 2>, cgrid, kCombineThreads, 0, st, p)
+                     : LaunchChained(PaCombine<float, 4>, cgrid, kCombineThreads, 0, st, p);
   } else {
-    e = LaunchChained(PaCombine<__nv_bfloat16>, cgrid, kCombineThreads, 0, st, p);
+    e = p.D <= 64    ? LaunchChained(PaCombine<__nv_bfloat16, 1>, cgrid, kCombineThreads, 0, st, p)
+        : p.D <= 128 ? LaunchChained(PaCombine<__nv_bfloat16, 2>, cgrid, kCombineThreads, 0, st, p)
+                     : LaunchChained(PaCombine<__nv_bfloat16, 4>, cgrid, kCombineThreads, 0, st, p);
   }
   if (e != cudaSuccess) return CudaFail("PAGED_ATTENTION combine launch", e);
   CountLaunches(2);

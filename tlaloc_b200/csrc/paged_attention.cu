@@ -324,6 +324,15 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
   const int ctx = p.M * p.bs;
   const int c0 = s * p.slice;
 
+  // The slice's block-table entries are requested first and for the whole slice, whatever the rows' lengths turn out
+  // to be, so that this load and the lengths travel together instead of one after the other (entries past the live
+  // range are clamped and never used).
+  const int c_end = min(c0 + p.slice, ctx);
+  const int b0 = p.bs_shift >= 0 ? (c0 >> p.bs_shift) : c0 / p.bs;
+  const int b_last = c_end > c0 ? (p.bs_shift >= 0 ? ((c_end - 1) >> p.bs_shift) : (c_end - 1) / p.bs) : b0 - 1;
+  for (int j = tid; j <= b_last - b0; j += kMmaThreads) {
+    tab[j] = ClampI(__ldg(p.tables + static_cast<size_t>(tb) * p.M + b0 + j), 0, p.P - 1);
+  }
   // Every thread derives the CTA's live range from its rows' lengths.
   int maxlen = 0, minfirst = ctx;
   for (int r = 0; r < p.rpt; ++r) {
@@ -336,11 +345,6 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
   if (t_begin >= c1) return;
   const int ngroups = (c1 - t_begin + 15) >> 4;
 
-  const int b0 = p.bs_shift >= 0 ? (t_begin >> p.bs_shift) : t_begin / p.bs;
-  const int b1 = p.bs_shift >= 0 ? ((c1 - 1) >> p.bs_shift) : (c1 - 1) / p.bs;
-  for (int j = tid; j <= b1 - b0; j += kMmaThreads) {
-    tab[j] = ClampI(__ldg(p.tables + static_cast<size_t>(tb) * p.M + b0 + j), 0, p.P - 1);
-  }
 
   // This lane's queries: column 2*tig + e of n-tile nt is query nt*8 + 2*tig + e (row / head as below).
   int qlen[NT][2], qfirst[NT][2];
@@ -778,14 +782,23 @@ cudaError_t LaunchGeneric(const PaParams& p, cudaStream_t stream)
 }
 
 // Positions per slice of the tensor-core kernel when the scratch allows it; $TLALOC_B200_PA_SLICE overrides.
-int PreferredSlice()
+// A CTA pays about 3 us of latency before its first position (lengths and table entries, then the first K/V rows)
+// and again to merge its warps and write its records, so slices should be as long as the grid can afford: 1024
+// positions, doubled (up to 4096) while the launch would still have some 4000 CTAs at the longest context, i.e. a
+// few waves of the 444 resident ones at typical lengths.  Measured on the 70B step (1024 (table, KV head) pairs,
+// contexts up to 16K): 0.718 -> 0.670 -> 0.661 ms per layer at 1024 / 2048 / 4096; with 128 or 256 pairs 1024 stays
+// best (2048: 117 -> 128 us on one KV head per rank).
+int PreferredSlice(int ctx, long long pairs)
 {
-  static const int v = [] {
+  static const int forced = [] {
     const char* e = std::getenv("TLALOC_B200_PA_SLICE");
     const int x = e != nullptr ? std::atoi(e) : 0;
-    return x >= 16 ? x : 1024;
+    return x >= 16 ? x : 0;
   }();
-  return v;
+  if (forced > 0) return forced;
+  int slice = 1024;
+  while (slice < 4096 && pairs * ((ctx + 2 * slice - 1) / (2 * slice)) >= 4000) slice *= 2;
+  return slice;
 }
 
 }  // namespace
@@ -903,7 +916,7 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
   const bool mma = kv_dtype == TLALOC_B200_BF16 && (head_dim == 64 || head_dim == 128) && p.NQ <= kMmaQ &&
                    keep == nullptr && block_size >= 8;
   // Slice length: the preferred one (tensor-core kernel) or 256, stretched until `splits` slices cover the context.
-  int slice = mma ? PreferredSlice() : 256;
+  int slice = mma ? PreferredSlice(ctx, static_cast<long long>(num_tables) * num_kv_heads) : 256;
   if (static_cast<int64_t>(slice) * splits < ctx) slice = (ctx + splits - 1) / splits;
   if (mma) slice = std::min((slice + 15) / 16 * 16, 8192);
   if (static_cast<int64_t>(slice) * splits < ctx) {

@@ -784,10 +784,11 @@ cudaError_t LaunchGeneric(const PaParams& p, cudaStream_t stream)
 // Positions per slice of the tensor-core kernel when the scratch allows it; $TLALOC_B200_PA_SLICE overrides.
 // A CTA pays about 3 us of latency before its first position (lengths and table entries, then the first K/V rows)
 // and again to merge its warps and write its records, so slices should be as long as the grid can afford: 1024
-// positions, doubled (up to 4096) while the launch would still have some 4000 CTAs at the longest context, i.e. a
+// positions, doubled (up to 4096) while the launch would still have some 2000 CTAs at the longest context, i.e. a
 // few waves of the 444 resident ones at typical lengths.  Measured on the 70B step (1024 (table, KV head) pairs,
-// contexts up to 16K): 0.718 -> 0.670 -> 0.661 ms per layer at 1024 / 2048 / 4096; with 128 or 256 pairs 1024 stays
-// best (2048: 117 -> 128 us on one KV head per rank).
+// contexts up to 16K): 0.718 -> 0.670 -> 0.661 ms per layer at 1024 / 2048 / 4096; 512 pairs: 382 / 374 / 372 us; 256
+// pairs: 203 / 200 / 222 us; 128 pairs (one KV head per rank): 117 / 128 us, and 256 pairs at contexts up to 8K also
+// keep 1024.
 int PreferredSlice(int ctx, long long pairs)
 {
   static const int forced = [] {
@@ -797,7 +798,7 @@ int PreferredSlice(int ctx, long long pairs)
   }();
   if (forced > 0) return forced;
   int slice = 1024;
-  while (slice < 4096 && pairs * ((ctx + 2 * slice - 1) / (2 * slice)) >= 4000) slice *= 2;
+  while (slice < 4096 && pairs * ((ctx + 2 * slice - 1) / (2 * slice)) >= 2000) slice *= 2;
   return slice;
 }
 

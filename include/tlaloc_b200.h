@@ -47,9 +47,10 @@ int tlaloc_b200_abi_version(void);
 const char* tlaloc_b200_last_error(void);
 
 /*
- * One-time kernel set-up for the current device (opt-in dynamic shared
- * memory).  Call once per process before the first launch that may run inside
- * a CUDA graph capture; later launches call it lazily otherwise.
+ * Kernel set-up for the CURRENT device (opt-in dynamic shared memory; it is a
+ * per-device attribute).  Call it once on every device the process uses, with
+ * that device current, before the first launch that may run inside a CUDA graph
+ * capture; launches outside a capture do it lazily.
  * Replaces: tlaloc_kernels::AllowMaxSharedMemory at XLA's INITIALIZE stage
  * (triton/kernels/kernel_setup.cuh:24-47, paged_attention.cu:1347-1350).
  */
@@ -62,6 +63,17 @@ int tlaloc_b200_init(void);
  * its output is undefined.
  */
 int tlaloc_b200_device_status(void);
+
+/*
+ * Parity mode, process-wide: while on, every operator below evaluates in the reference interpreter's own order
+ * instead of the fast kernels' (the projections as with TLALOC_B200_GEMM_EXACT; paged attention with double
+ * accumulators, positions in ascending order and one narrowing at the end, DxirInterpreter.kt:2049-2140; RMSNorm's
+ * mean as a sequential f32 sum, :1450-1496,1791-1807; SiLU in double, :567-592), so that results equal the
+ * interpreter's up to the last bit of the library exponential.  Slow, for parity runs only: the fast kernels reorder
+ * f32 sums, which may flip a bf16 rounding of an activation and, on a near-tie, a greedy token.  Launches captured
+ * into a CUDA graph keep the mode they were captured in.  Returns the previous setting.
+ */
+int tlaloc_b200_set_order_faithful(int on);
 
 /* Kernels this library has launched (or captured into a graph) since it was loaded, over all threads. */
 long long tlaloc_b200_launch_count(void);
@@ -155,10 +167,7 @@ int tlaloc_b200_kv_cache_write(void* pool, int32_t pool_dtype, const void* new_k
 
 /* ------------------------------------------------------------------ int8 weight-only projection */
 
-/*
- * Bytes of f32 scratch the projection wants for this shape (split-K partials);
- * 0 when it needs none.
- */
+/* Bytes of scratch the projection wants for an F32 x of this shape (its bf16 copy). */
 size_t tlaloc_b200_int8_gemm_scratch_bytes(int32_t m, int32_t k, int32_t n);
 
 /*
@@ -174,11 +183,12 @@ size_t tlaloc_b200_int8_gemm_scratch_bytes(int32_t m, int32_t k, int32_t n);
  *   scales  device f32 [N], or NULL for none
  *   residual device f32 [M, N] or NULL: added after the scale (the layer's residual add)
  *   y       device [M, N]  y_dtype F32 | BF16
- *   scratch device memory, 16-byte aligned, contents undefined on entry and exit, or NULL.  An F32 x needs the
- *           first 2 * m * k bytes (its bf16 copy).  With all of tlaloc_b200_int8_gemm_scratch_bytes(m, k, n) bytes a
- *           batch of more than 32 rows may also spread its work evenly over the SMs (partial tiles handed over through
- *           the scratch); with less, or NULL, it runs the form that needs none.  Two calls whose kernels can overlap
- *           on the GPU need scratch of their own.
+ *   scratch device memory, 16-byte aligned, contents undefined on entry and exit, or NULL.  Only an F32 x needs
+ *           it: tlaloc_b200_int8_gemm_scratch_bytes(m, k, n) bytes for its bf16 copy.
+ *
+ * The fast kernels read x and codes in 16-byte pieces; when either pointer is not 16-byte aligned (a view into a
+ * larger buffer at an odd offset), or N is not a multiple of 16 or K of 8, the call runs the order-faithful kernel
+ * below instead: slower, same contract.
  *
  * flags: TLALOC_B200_GEMM_EXACT runs the order-faithful kernel (f32 accumulate
  * in increasing k with separate multiply and add, bit-identical to the
@@ -261,7 +271,8 @@ int tlaloc_b200_peer_free(void* ptr);
  *   flag_offset  byte offset of 2 * world u32 flag words inside every buffer, zero before the first call
  *   state        4 u32 words of LOCAL device memory, zero before the first call: [0] all-reduces finished,
  *                [2] status (0, or 1 + 16 * phase + the rank that did not arrive within the time limit; once set,
- *                later calls do not wait).  The sums are added in rank order: every rank gets identical bits.
+ *                later calls do not wait), [3] the limit of each wait in microseconds (0 = 20 s; a caller may set
+ *                it before the first call).  The sums are added in rank order: every rank gets identical bits.
  * count must be a multiple of 4.  world == 1 is a no-op.
  */
 int tlaloc_b200_peer_allreduce_f32(void* const* bases, size_t data_offset, size_t flag_offset, uint32_t* state,

@@ -259,6 +259,13 @@ class DecoderShape:
     weight_dtype: str = "bf16"
     kv_dtype: str = "f32"  # "f32" | "bf16": values are snapped RNE on write when bf16
     head_quant: bool = False  # WeightQuant.kt:21-22: the head stays in weight dtype unless quantized
+    # The Granite family's four scalars (HfDecoderGraph.kt:546,915,1000,2129): h *= embed_scale after the embedding;
+    # the attention scale replaces 1/sqrt(head_dim); each sub-layer's output is multiplied by residual_multiplier
+    # before its residual add; the logits by logit_multiplier.  Every one a MUL by the f32 constant.
+    embed_scale: float | None = None
+    attention_scale: float | None = None
+    residual_multiplier: float = 1.0
+    logit_multiplier: float = 1.0
 
 
 @dataclass
@@ -306,26 +313,38 @@ def decode_step(shape: DecoderShape, w: DecoderWeights, key_pools, value_pools, 
     bf = shape.weight_dtype == "bf16"
     B = len(token_ids)
     H, Hkv, hd = shape.num_heads, shape.num_kv_heads, shape.head_dim
-    scale = float(np.float32(1.0) / np.sqrt(np.float32(hd)))  # HfDecoderGraph.kt:546 1f/sqrt(hd.toFloat()) widened
+    # HfDecoderGraph.kt:546: config.attentionScale?.toFloat() ?: 1f / sqrt(hd.toFloat()), widened
+    scale = float(np.float32(shape.attention_scale)) if shape.attention_scale is not None \
+        else float(np.float32(1.0) / np.sqrt(np.float32(hd)))
     cos, sin = rope_tables(shape.rope_theta, hd, int(np.max(positions)) + 1)
+
+    def proj(x, wt):
+        """HfDecoderGraph.proj (:625-655): an int8 weight is (codes, scales); an unquantized one [in, out] values."""
+        if isinstance(wt, tuple):
+            return proj_int8(x, *wt, round_x_bf16=bf, threads=threads)
+        return matmul_f32(snap_bf16(x) if bf else x, wt, threads=threads)
+
+    def times(x, c):  # :702-703: MUL by the constant narrowed to f32
+        return x if c == 1.0 else (x * np.float32(c)).astype(np.float32)
+
     h = embedding(w.embed, token_ids)
+    if shape.embed_scale is not None:
+        h = times(h, shape.embed_scale)
     for l, lw in enumerate(w.layers):
         hn = rmsnorm(h, lw["ln1"], shape.rms_eps)
-        q = proj_int8(hn, *lw["q"], round_x_bf16=bf, threads=threads).reshape(B, H, hd)
-        k = proj_int8(hn, *lw["k"], round_x_bf16=bf, threads=threads).reshape(B, Hkv, hd)
-        v = proj_int8(hn, *lw["v"], round_x_bf16=bf, threads=threads).reshape(B, Hkv, hd)
+        q = proj(hn, lw["q"]).reshape(B, H, hd)
+        k = proj(hn, lw["k"]).reshape(B, Hkv, hd)
+        v = proj(hn, lw["v"]).reshape(B, Hkv, hd)
         q, k = rope(q, positions, cos, sin), rope(k, positions, cos, sin)
         if shape.kv_dtype == "bf16":
             k, v = snap_bf16(k), snap_bf16(v)
         kv_cache_write_inplace(key_pools[l], k.reshape(B, -1), slot_mapping)
         kv_cache_write_inplace(value_pools[l], v.reshape(B, -1), slot_mapping)
         att = paged_attention(q, key_pools[l], value_pools[l], block_tables, seq_lens, scale, threads=threads)
-        h = h + proj_int8(att.reshape(B, H * hd), *lw["o"], round_x_bf16=bf, threads=threads)
+        h = h + times(proj(att.reshape(B, H * hd), lw["o"]), shape.residual_multiplier)
         hn2 = rmsnorm(h, lw["ln2"], shape.rms_eps)
-        g = proj_int8(hn2, *lw["gate"], round_x_bf16=bf, threads=threads)
-        u = proj_int8(hn2, *lw["up"], round_x_bf16=bf, threads=threads)
-        h = h + proj_int8(swiglu(g, u), *lw["down"], round_x_bf16=bf, threads=threads)
+        g = proj(hn2, lw["gate"])
+        u = proj(hn2, lw["up"])
+        h = h + times(proj(swiglu(g, u), lw["down"]), shape.residual_multiplier)
     hf = rmsnorm(h, w.final_norm, shape.rms_eps)
-    if shape.head_quant:
-        return proj_int8(hf, *w.head, round_x_bf16=bf, threads=threads)
-    return matmul_f32(snap_bf16(hf) if bf else hf, w.head, threads=threads)
+    return times(proj(hf, w.head), shape.logit_multiplier)

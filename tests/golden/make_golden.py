@@ -9,6 +9,14 @@ seam (triton/examples/reference/reference_decode.json, produced by its DXIR
 interpreter over maestro/.../ReferenceDecodeGraph.kt): five decode steps with
 their logits.  It is re-serialised unchanged (inputs and outputs only) so the
 tests can run where the reference is not mounted.
+
+tiny_granite.npz / tiny_granite.json: the reference's tiny Granite checkpoint
+(ir/src/jvmTest/resources/io/tlaloc/ir/inference/tiny_granite/: a 3-layer Llama-style decoder with the four
+Granite scalars), its tensors as f32 arrays, with the two known answers the reference holds for it: every logit
+at every position of two prompts from transformers' own GraniteForCausalLM (granite_modeling_logits.json, the
+oracle of HfGraniteParityTest.theReferenceIsTransformersGraniteCode) and the greedy continuations with their
+smallest top-1 margins (tiny_granite/greedy.json).  They pin the RMSNorm, RoPE, SwiGLU, grouped-query attention
+and layer structure of the CPU oracle's decode step, which reference_decode.json does not exercise.
 """
 import json
 import os
@@ -29,6 +37,28 @@ def main(ref_root: str) -> None:
     with open(os.path.join(here, "reference_decode.json"), "w") as f:
         json.dump(out, f, indent=1)
     print("wrote reference_decode.json with", len(out["steps"]), "steps")
+    granite(ref_root, here)
+
+
+def granite(ref_root: str, here: str) -> None:
+    import numpy as np
+    from safetensors import safe_open
+
+    res = os.path.join(ref_root, "ir/src/jvmTest/resources/io/tlaloc/ir/inference")
+    with safe_open(os.path.join(res, "tiny_granite/model.safetensors"), "np") as f:
+        tensors = {k: f.get_tensor(k).astype(np.float32) for k in f.keys()}
+    np.savez_compressed(os.path.join(here, "tiny_granite.npz"), **tensors)
+    with open(os.path.join(res, "tiny_granite/config.json")) as f:
+        config = json.load(f)
+    with open(os.path.join(res, "tiny_granite/greedy.json")) as f:
+        greedy = json.load(f)
+    with open(os.path.join(res, "granite_modeling_logits.json")) as f:
+        logits = json.load(f)
+    out = {"origin": "ir/src/jvmTest/resources/io/tlaloc/ir/inference/{tiny_granite/*, granite_modeling_logits.json}",
+           "config": config, "greedy": greedy, "modeling_logits": logits}
+    with open(os.path.join(here, "tiny_granite.json"), "w") as f:
+        json.dump(out, f)
+    print("wrote tiny_granite.npz with", len(tensors), "tensors and tiny_granite.json")
 
 
 if __name__ == "__main__":

@@ -87,3 +87,30 @@ def test_rope_and_kv_write(kv_dtype):
     ref_rows = oracle.snap_bf16(rows) if kv_dtype == torch.bfloat16 else rows
     want = oracle.kv_cache_write(kc0, ref_rows.reshape(4, -1), np.array([-1, 5, -1, 0], np.int32))
     assert np.array_equal(pool.float().cpu().numpy(), want)
+
+
+def test_parity_mode_rmsnorm_and_swiglu_are_bit_identical_to_the_oracle():
+    """tlaloc_b200_set_order_faithful: RMSNorm sums its squares sequentially in f32 and SiLU runs in double, as the
+    interpreter evaluates those nodes (the default kernels use a tree of fused multiply-adds and an f32 exponential)."""
+    o = ops()
+    rng = np.random.default_rng(21)
+    before = o.set_order_faithful(True)
+    try:
+        for rows, n in [(4, 256), (3, 688), (2, 8192), (5, 37)]:
+            x = (rng.standard_normal((rows, n)) * 3).astype(np.float32)
+            gain = rng.uniform(0.5, 1.5, size=n).astype(np.float32)
+            got = o.rmsnorm(dev(x), dev(gain), 1e-5)
+            torch.cuda.synchronize()
+            assert np.array_equal(got.cpu().numpy(), oracle.rmsnorm(x, gain, 1e-5))
+            got = o.rmsnorm(dev(x), None, 1e-6, out_dtype=torch.bfloat16)
+            assert np.array_equal(got.float().cpu().numpy(), oracle.snap_bf16(oracle.rmsnorm(x, None, 1e-6)))
+        gu = (rng.standard_normal((6, 2 * 688)) * 4).astype(np.float32)
+        t = dev(gu)
+        got = o.swiglu(t[:, :688], t[:, 688:])
+        torch.cuda.synchronize()
+        want = oracle.swiglu(gu[:, :688], gu[:, 688:])
+        # the exponential is the device library's double exp, the oracle's is the host's: equal except, at most, where
+        # the double quotient sits on an f32 rounding boundary
+        assert np.mean(got.cpu().numpy() == want) >= 0.9999 and np.abs(got.cpu().numpy() - want).max() <= 1e-6
+    finally:
+        o.set_order_faithful(before)

@@ -11,7 +11,7 @@ import oracle
 pytestmark = pytest.mark.gpu
 
 
-def _setup(kv_dtype, head_quant):
+def _setup(kv_dtype, head_quant, exact=False):
     from tlaloc_b200 import decoder as D
     from tlaloc_b200 import sharding
 
@@ -28,14 +28,20 @@ def _setup(kv_dtype, head_quant):
     perm = 1 + rng.permutation(B * max_blocks)
     tables = perm.reshape(B, max_blocks).astype(np.int32)
     prompts = [rng.integers(0, 1024, size=n).astype(np.int32) for n in ctx]
-    dec = D.Decoder(cfg, B, num_blocks, max_blocks)
+    dec = D.Decoder(cfg, B, num_blocks, max_blocks, exact=exact)
     dec.load_host_weights(w)
     return shape, w, cfg, dec, tables, prompts, ctx, num_blocks, sharding
 
 
-@pytest.mark.parametrize("kv_dtype,head_quant", [(torch.float32, False), (torch.bfloat16, True)])
-def test_tiny_decoder_64_greedy_steps_match_the_oracle(kv_dtype, head_quant):
-    shape, w, cfg, dec, tables, prompts, ctx, num_blocks, sharding = _setup(kv_dtype, head_quant)
+@pytest.mark.parametrize("kv_dtype,head_quant,exact", [(torch.float32, False, True), (torch.bfloat16, True, True),
+                                                       (torch.float32, False, False), (torch.bfloat16, True, False)])
+def test_tiny_decoder_64_greedy_steps_match_the_oracle(kv_dtype, head_quant, exact):
+    """`exact` runs the engine in the library's parity mode (the interpreter's own evaluation order in every
+    operator): there the greedy tokens must be IDENTICAL over the 64 steps and the logits equal to rounding.  The fast
+    kernels reorder f32 sums; a reordered sum can flip the bf16 rounding of one activation (every projection input is
+    rounded to bf16), which moves a logit by ~1e-3, so on a near-tie of the oracle's own top two logits a token may
+    differ: those are counted and bounded, and the parity-mode run shows that nothing else is behind them."""
+    shape, w, cfg, dec, tables, prompts, ctx, num_blocks, sharding = _setup(kv_dtype, head_quant, exact)
     B, bs = 4, 16
     kp = [np.zeros((num_blocks, bs, 2, 64), np.float32) for _ in range(2)]
     vp = [np.zeros((num_blocks, bs, 2, 64), np.float32) for _ in range(2)]
@@ -111,4 +117,8 @@ def test_tiny_decoder_64_greedy_steps_match_the_oracle(kv_dtype, head_quant):
     # Identical greedy tokens, except where the oracle's own logits put the two candidates closer together than the
     # two runs' logits are to each other (a tie within the comparison's resolution; triton/quant_checks.py:55-87
     # reports margins for the same reason).  Such swaps must stay rare.
-    assert mismatches == 0 and near_ties <= 2
+    if exact:
+        assert mismatches == 0 and near_ties == 0, "parity mode must reproduce the oracle's greedy tokens exactly"
+        assert worst <= 1e-5, worst
+    else:
+        assert mismatches == 0 and near_ties <= 2

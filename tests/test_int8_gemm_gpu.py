@@ -165,33 +165,144 @@ def test_quantized_weights_round_trip_like_the_reference_identity():
     assert np.abs(deq.T - w).max() <= np.abs(w).max() / 127.0 * 0.5 + 1e-9
 
 
-def test_evenly_spread_launch_is_exact_too():
-    """The stream-K form of the tensor-core kernel (off by default, $TLALOC_B200_GEMM_STREAMK=2 forces it): CTAs take
-    equal runs of (column tile, k block) units, partial tiles cross CTAs through the caller's scratch.  The switch is
-    read once per process, so the check runs in a child process."""
+def _exact_want_on_device(x, codes, scales, res):
+    """The exact integer dot products in float64 on the device (sums of integers below 2^53 are exact in any order),
+    column block by column block, narrowed to f32 and scaled like the kernel's epilogue."""
+    tx = torch.from_numpy(x).to(DEV).double()
+    out = torch.empty((x.shape[0], codes.shape[1]), dtype=torch.float32, device=DEV)
+    tc = torch.from_numpy(codes).to(DEV)
+    for c0 in range(0, codes.shape[1], 8192):
+        out[:, c0:c0 + 8192] = (tx @ tc[:, c0:c0 + 8192].double()).float()
+    out = out * torch.from_numpy(scales).to(DEV)[None, :]
+    if res is not None:
+        out = out + torch.from_numpy(res).to(DEV)
+    return out, tc
+
+
+# The projections of the 70B-shape decode step at batch 128 (K x N: q|k|v, o, gate|up, down), the shards one of eight
+# tensor-parallel ranks holds, and the vocabulary head.
+STEP_SHAPES = [(8192, 10240), (8192, 8192), (8192, 57344), (28672, 8192),
+               (8192, 1280), (1024, 8192), (8192, 7168), (3584, 8192)]
+
+
+@pytest.mark.parametrize("k,n", STEP_SHAPES)
+def test_decode_step_shapes_at_128_rows(k, n):
+    """Exact on integer activations over the whole output; against the oracle on a sample of rows for N(0,1) ones."""
+    from tlaloc_b200 import _native as N
+
+    m = 128
+    rng = np.random.default_rng(k + n)
+    codes = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    span = 4 if k > 16384 else 8  # keeps every partial sum an integer below 2^24
+    x = rng.integers(-span, span + 1, size=(m, k)).astype(np.float32)
+    scales = np.exp2(rng.integers(-8, -2, size=n)).astype(np.float32)
+    res = rng.integers(-50, 50, size=(m, n)).astype(np.float32)
+    want, tc = _exact_want_on_device(x, codes, scales, res)
+    got = ops().int8_gemm(dev(x, torch.bfloat16), tc, dev(scales), residual=dev(res), weights_const=True)
+    torch.cuda.synchronize()
+    assert N.lib().tlaloc_b200_device_status() == 0
+    assert torch.equal(got, want)
+    xn = oracle.snap_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    sc = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
+    got = ops().int8_gemm(dev(xn, torch.bfloat16), tc, dev(sc)).cpu().numpy()
+    rows = [0, 77, 127]
+    wantn = oracle.proj_int8(xn[rows], codes, sc, round_x_bf16=True, threads=oracle.host_threads())
+    worst = close(got[rows], wantn)
+    assert worst <= 1e-4 * max(1.0, np.abs(wantn).max())
+
+
+@pytest.mark.parametrize("m", [1, 32, 256])
+def test_vocabulary_head_shape_at_1_32_and_256_rows(m):
+    from tlaloc_b200 import _native as N
+
+    k, n = 4096, 128256
+    rng = np.random.default_rng(m)
+    codes = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    x = rng.integers(-8, 9, size=(m, k)).astype(np.float32)
+    scales = np.exp2(rng.integers(-8, -2, size=n)).astype(np.float32)
+    want, tc = _exact_want_on_device(x, codes, scales, None)
+    got = ops().int8_gemm(dev(x, torch.bfloat16), tc, dev(scales))
+    torch.cuda.synchronize()
+    assert N.lib().tlaloc_b200_device_status() == 0
+    assert torch.equal(got, want)
+    xn = oracle.snap_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    sc = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
+    got = ops().int8_gemm(dev(xn, torch.bfloat16), tc, dev(sc)).cpu().numpy()
+    rows = sorted({0, m // 2, m - 1})
+    wantn = oracle.proj_int8(xn[rows], codes, sc, round_x_bf16=True, threads=oracle.host_threads())
+    close(got[rows], wantn)
+
+
+def test_views_off_a_16_byte_boundary_take_the_order_faithful_kernel():
+    """x + 4 elements or a weight matrix that starts at an odd byte must not reach the 16-byte copies of the fast
+    kernels: the call falls back and still agrees with the oracle (bit for bit: it is the order-faithful kernel)."""
+    rng = np.random.default_rng(12)
+    m, k, n = 8, 512, 1024
+    x, codes, scales = make(rng, m, k, n)
+    want = oracle.proj_int8(x, codes, scales, round_x_bf16=True)
+    xbuf = torch.zeros((m * k + 4,), dtype=torch.bfloat16, device=DEV)
+    xv = xbuf[4:].view(m, k)  # starts 8 bytes into the allocation
+    xv.copy_(dev(x, torch.bfloat16))
+    assert xv.data_ptr() % 16 == 8
+    got = ops().int8_gemm(xv, dev(codes), dev(scales))
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), want)
+    cbuf = torch.zeros((k * n + 1,), dtype=torch.int8, device=DEV)
+    cv = cbuf[1:].view(k, n)  # starts one byte into the allocation
+    cv.copy_(dev(codes))
+    for rows in (m, 64):  # the row-vector kernel's range and the tensor-core kernel's
+        xr = oracle.snap_bf16(rng.standard_normal((rows, k)).astype(np.float32))
+        got = ops().int8_gemm(dev(xr, torch.bfloat16), cv, dev(scales))
+        torch.cuda.synchronize()
+        assert np.array_equal(got.cpu().numpy(), oracle.proj_int8(xr, codes, scales, round_x_bf16=True))
+    with pytest.raises(ValueError, match="INT8_PROJ out"):
+        ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), out=torch.empty((m, n + 16), device=DEV))
+
+
+def test_bf16_weight_tiles_are_exact_too():
+    """$TLALOC_B200_GEMM_W16=bf16 keeps the converted weights as bf16 instead of f16 in the tensor-core kernel (both
+    hold an int8 code exactly).  The switch is read once per process, so the check runs in a child process."""
     import os
     import subprocess
     import sys
 
-    code = r'''
+    code = r"""
 import numpy as np, torch, sys
 sys.path.insert(0, %r)
 from tlaloc_b200 import ops, _native as N
 rng = np.random.default_rng(5)
-for (m, k, n) in [(128, 4096, 4096), (100, 1024, 14336), (64, 688, 256), (128, 8192, 1280)]:
+for (m, k, n) in [(128, 4096, 4096), (100, 1024, 14336), (64, 688, 256), (256, 512, 768)]:
     x = rng.integers(-8, 9, size=(m, k)).astype(np.float32)
     codes = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    codes[0, :] = -127
+    codes[1, :] = 127
     scales = np.exp2(rng.integers(-8, -2, size=n)).astype(np.float32)
-    res = rng.integers(-50, 50, size=(m, n)).astype(np.float32)
-    want = (x.astype(np.float64) @ codes.astype(np.float64)).astype(np.float32) * scales[None, :] + res
+    want = (x.astype(np.float64) @ codes.astype(np.float64)).astype(np.float32) * scales[None, :]
     t = lambda a, dt=None: torch.from_numpy(a).cuda() if dt is None else torch.from_numpy(a).cuda().to(dt)
-    for rep in range(2):  # twice: the second launch meets the first one's flags in the recycled scratch
-        got = ops.int8_gemm(t(x, torch.bfloat16), t(codes), t(scales), residual=t(res))
-        torch.cuda.synchronize()
-        assert N.lib().tlaloc_b200_device_status() == 0
-        assert np.array_equal(got.cpu().numpy(), want), (m, k, n, rep)
-print("stream ok")
-''' % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, TLALOC_B200_GEMM_STREAMK="2")
+    got = ops.int8_gemm(t(x, torch.bfloat16), t(codes), t(scales))
+    torch.cuda.synchronize()
+    assert N.lib().tlaloc_b200_device_status() == 0
+    assert np.array_equal(got.cpu().numpy(), want), (m, k, n)
+print("bf16 tiles ok")
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TLALOC_B200_GEMM_W16="bf16", TLALOC_B200_GEMM_PREFETCH="0")
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=240)
-    assert out.returncode == 0 and "stream ok" in out.stdout, out.stdout[-1500:] + out.stderr[-1500:]
+    assert out.returncode == 0 and "bf16 tiles ok" in out.stdout, out.stdout[-1500:] + out.stderr[-1500:]
+
+
+@pytest.mark.parametrize("m", [8, 64])
+def test_every_code_value_converts_exactly(m):
+    """All 256 byte values as weights (the f16 expansion flips the top bit and subtracts 1152): one-hot activations
+    read each code back, on the row-vector kernel and on the tensor-core kernel."""
+    k, n = 256, 256
+    codes = np.zeros((k, n), np.int8)
+    for j in range(n):
+        codes[:, j] = np.roll(np.arange(-128, 128), j).astype(np.int8)
+    x = np.zeros((m, k), np.float32)
+    for i in range(m):
+        x[i, (5 * i) % k] = 1.0
+        x[i, (7 * i + 3) % k] += 2.0
+    want = x.astype(np.float64) @ codes.astype(np.float64)
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), None)
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), want.astype(np.float32))

@@ -289,6 +289,98 @@ def test_operator_config_full_size_against_the_oracle():
     assert err.max() <= tol_of(want)  # and in fact at the f32 kernels' own bar
 
 
+def test_one_kv_head_per_rank_shape_against_the_oracle_on_sampled_rows():
+    """What one of eight tensor-parallel ranks runs in the 70B-shape step: 8 query heads on 1 KV head, batch 128,
+    lengths uniform in [1024, 16384], nothing shared between sequences.  The oracle walks a sample of rows (their
+    pages gathered into a small pool of their own)."""
+    rng = np.random.default_rng(70)
+    B, Hq, Hk, Dh, bs = 128, 8, 1, 128, 16
+    lens = rng.integers(1024, 16385, size=B).astype(np.int32)
+    lens[:4] = [1024, 16384, 4097, 8191]
+    need = (lens + bs - 1) // bs
+    nb, width = int(need.sum()) + 1, 1024
+    perm = 1 + rng.permutation(nb - 1)
+    tab = np.zeros((B, width), np.int32)
+    o = 0
+    for i in range(B):
+        tab[i, :need[i]] = perm[o:o + need[i]]
+        o += int(need[i])
+    g = torch.Generator(device=DEV)
+    g.manual_seed(70)
+    tk = torch.randn((nb, bs, Hk, Dh), device=DEV, generator=g).to(torch.bfloat16)
+    tv = torch.randn((nb, bs, Hk, Dh), device=DEV, generator=g).to(torch.bfloat16)
+    tq = torch.randn((B, Hq, Dh), device=DEV, generator=g).to(torch.bfloat16)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(Dh)))
+    out = ops().paged_attention(tq, tk, tv, torch.from_numpy(tab).to(DEV), torch.from_numpy(lens).to(DEV), scale=scale,
+                                out=torch.empty((B, Hq, Dh), dtype=torch.float32, device=DEV))
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    rows = [0, 1, 2, 3, 64, 127]
+    for r in rows:
+        pages = torch.from_numpy(tab[r, :need[r]].astype(np.int64)).to(DEV)
+        k_r = tk[pages].float().cpu().numpy()
+        v_r = tv[pages].float().cpu().numpy()
+        want = oracle.paged_attention(tq[r:r + 1].float().cpu().numpy(), k_r, v_r,
+                                      np.arange(need[r], dtype=np.int32)[None, :], lens[r:r + 1], scale,
+                                      threads=oracle.host_threads())
+        err = np.abs(got[r:r + 1] - want)
+        assert err.max() <= tol_of(want), (r, float(err.max()))
+
+
+def test_pools_off_a_16_byte_boundary_take_the_generic_kernel():
+    """A pool that starts 2 bytes into an allocation must not reach the tensor-core kernel's 16-byte copies."""
+    rng = np.random.default_rng(13)
+    q, k, v, tab, lens = rand_case(rng, 4, 4, 8, 2, 64, 16, 8, 40, [100, 17, 128, 64])
+    q, k, v = as_bf16(q), as_bf16(k), as_bf16(v)
+    want = oracle.paged_attention(q, k, v, tab, lens, 0.125)
+    o = ops()
+    bufs = []
+    for a in (k, v):
+        buf = torch.zeros((a.size + 1,), dtype=torch.bfloat16, device=DEV)
+        view = buf[1:].view(*a.shape)
+        view.copy_(torch.from_numpy(a).to(DEV))
+        assert view.data_ptr() % 16 == 2
+        bufs.append(view)
+    out = o.paged_attention(torch.from_numpy(q).to(DEV).to(torch.bfloat16), bufs[0], bufs[1], torch.from_numpy(tab).to(DEV),
+                            torch.from_numpy(lens.astype(np.int32)).to(DEV), scale=0.125,
+                            out=torch.empty(q.shape, dtype=torch.float32, device=DEV))
+    torch.cuda.synchronize()
+    assert np.abs(out.cpu().numpy() - want).max() <= tol_of(want)
+    with pytest.raises(ValueError, match="PAGED_ATTENTION out"):
+        o.paged_attention(torch.from_numpy(q).to(DEV), bufs[0], bufs[1], torch.from_numpy(tab).to(DEV),
+                          torch.from_numpy(lens.astype(np.int32)).to(DEV), scale=0.125,
+                          out=torch.empty((4, 8, 32), dtype=torch.float32, device=DEV))
+
+
+def test_parity_mode_walks_like_the_interpreter():
+    """tlaloc_b200_set_order_faithful: double accumulators, ascending positions, one narrowing; equals the oracle to the
+    last bits on f32 and bf16 pools, windows, keep masks, shared tables and empty rows."""
+    o = ops()
+    rng = np.random.default_rng(14)
+    before = o.set_order_faithful(True)
+    try:
+        q, k, v = tiny(41, 43, 47)
+        table = np.array([5, 3, 1, 0, 4, 2], np.int32).reshape(R, M)
+        for w in (None, 1, 3):
+            for len0 in range(0, CTX + 1):
+                lens = np.array([len0, CTX - len0])
+                got, lse = run(q, k, v, table, lens, 0.5, sliding_window=w, return_lse=True)
+                want, wlse = oracle.paged_attention(q, k, v, table, lens, 0.5, sliding_window=w, return_lse=True)
+                assert np.abs(got - want).max() <= 1e-7 and np.array_equal(np.isneginf(lse), np.isneginf(wlse))
+        q, k, v, tab, lens = rand_case(rng, 6, 3, 8, 2, 64, 16, 20, 70, [300, 17, 1, 64, 0, 255])
+        keep = (rng.random((6, 10)) < 0.7).astype(np.int32)
+        for kw in ({}, {"sliding_window": 40}, {"keep": keep}):
+            got = run(q, k, v, tab, lens, 0.125, **kw)
+            want = oracle.paged_attention(q, k, v, tab, lens, 0.125, **kw)
+            assert np.abs(got - want).max() <= 2e-7 * max(1.0, float(np.abs(want).max())), kw
+        qb, kb, vb = as_bf16(q), as_bf16(k), as_bf16(v)
+        got = run(qb, kb, vb, tab, lens, 0.125, q_dtype=torch.bfloat16, kv_dtype=torch.bfloat16)
+        want = oracle.paged_attention(qb, kb, vb, tab, lens, 0.125)
+        assert np.abs(got - as_bf16(want)).max() <= 1e-7  # out takes the query's dtype: the same values, snapped once
+    finally:
+        o.set_order_faithful(before)
+
+
 def test_refusals_reach_the_caller():
     o = ops()
     from tlaloc_b200._native import KernelError

@@ -24,6 +24,7 @@ _SIGNATURES = {
     "tlaloc_b200_init": (ctypes.c_int, []),
     "tlaloc_b200_launch_count": (ctypes.c_longlong, []),
     "tlaloc_b200_device_status": (ctypes.c_int, []),
+    "tlaloc_b200_set_order_faithful": (ctypes.c_int, [ctypes.c_int]),
     "tlaloc_b200_paged_attention_splits": (ctypes.c_int, [_i32] * 5),
     "tlaloc_b200_paged_attention_scratch_bytes": (_sz, [_i32] * 4),
     "tlaloc_b200_paged_attention": (ctypes.c_int, [_vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,

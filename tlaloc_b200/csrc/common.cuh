@@ -8,6 +8,8 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
+#include <mutex>
 
 #include "../../include/tlaloc_b200.h"
 
@@ -50,6 +52,9 @@ template <>
 __device__ __forceinline__ float FromF32<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 FromF32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// tlaloc_b200_set_order_faithful: every operator evaluates in the reference interpreter's own order (parity runs).
+bool OrderFaithful();
 
 // Kernels launched by this library since it was loaded (tlaloc_b200_launch_count); a plain statistic.
 void CountLaunches(int n);
@@ -100,21 +105,40 @@ cudaError_t LaunchChained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
-// Once-per-process kernel attribute setup (dynamic shared memory opt-in) of each
-// translation unit; called from tlaloc_b200_init and from the typed-FFI
-// handlers' INITIALIZE stage, so that no launch inside a CUDA graph capture
-// has to change a function attribute.
+// Kernel attribute set-up (the dynamic shared memory opt-in) is per device: a process that drives several GPUs (a PJRT
+// client's usual layout) must repeat it on each.  Run(f) calls f(device) once per device, with that device current,
+// under a mutex; a failed set-up is retried by the next call.
+constexpr int kMaxDevices = 64;
+struct OncePerDevice {
+  std::mutex mu;
+  bool done[kMaxDevices] = {};
+  template <typename F>
+  cudaError_t Run(F f)
+  {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[device]) return cudaSuccess;
+    e = f(device);
+    if (e == cudaSuccess) done[device] = true;
+    return e;
+  }
+};
+
+// Per-device kernel attribute set-up of each translation unit; called from tlaloc_b200_init and from the typed-FFI
+// handlers' INITIALIZE stage, so that no launch inside a CUDA graph capture has to change a function attribute.
 cudaError_t PreparePagedAttentionKernels();
 cudaError_t PrepareInt8GemmKernels();
 cudaError_t PrepareInt8GemmTcKernels();
 
 // The tensor-core projection (int8_gemm_tc.cu): rows [0, m) of y = (x @ codes) * scales (+ residual), x bf16.
 cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const float* scales, const float* residual,
-                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches, bool weights_const,
-                             void* stream_scratch, size_t stream_scratch_bytes);
-// Caller scratch that lets the tensor-core projection spread its blocks evenly over the SMs (0 bytes = never used).
-size_t TcStreamScratchBytes();
+                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches, bool weights_const);
 // 1 if a bounded device-side wait has timed out since the last call (synchronous read), 0 if not, -1 on a CUDA error.
 int ReadTcStatus();
+
+inline bool Aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace tlaloc_b200

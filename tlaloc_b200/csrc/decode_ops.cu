@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(256) RmsNormKernel(const float* x, const float
   __shared__ float red[8];
   const float* xr = x + static_cast<size_t>(blockIdx.x) * n;
   OT* o = out + static_cast<size_t>(blockIdx.x) * n;
-  if ((n & 3) == 0 && n <= 8192 && (reinterpret_cast<uintptr_t>(xr) & 15) == 0) {
+  if ((n & 3) == 0 && n <= 8192 && (reinterpret_cast<uintptr_t>(xr) & 15) == 0 && (reinterpret_cast<uintptr_t>(gain) & 15) == 0) {
     const int n4 = n >> 2;
     float4 v[8];
     float ss = 0.f;
@@ -79,6 +79,30 @@ __global__ void __launch_bounds__(256) RmsNormKernel(const float* x, const float
   ss = BlockSum(ss, red);
   const float mean = ss / static_cast<float>(n);
   const float rsq = static_cast<float>(1.0 / sqrt(static_cast<double>(mean + eps)));
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    float v = __fmul_rn(xr[j], rsq);
+    if (gain != nullptr) v = __fmul_rn(v, gain[j]);
+    o[j] = FromF32<OT>(v);
+  }
+}
+
+// The interpreter's own evaluation of the same graph nodes (parity mode): sq = x * x, mean = (sum of sq in index
+// order, f32) / n, + eps, rsqrt in double, (x * rsq) * gain; one thread sums a row.
+template <typename OT>
+__global__ void __launch_bounds__(256) RmsNormOrderFaithfulKernel(const float* x, const float* gain, OT* out, int n, float eps)
+{
+  GridDependencySync();
+  __shared__ float s_rsq;
+  const float* xr = x + static_cast<size_t>(blockIdx.x) * n;
+  OT* o = out + static_cast<size_t>(blockIdx.x) * n;
+  if (threadIdx.x == 0) {
+    float acc = 0.f;
+    for (int j = 0; j < n; ++j) acc = __fadd_rn(acc, __fmul_rn(xr[j], xr[j]));
+    const float shifted = __fadd_rn(__fdiv_rn(acc, static_cast<float>(n)), eps);
+    s_rsq = static_cast<float>(1.0 / sqrt(static_cast<double>(shifted)));
+  }
+  __syncthreads();
+  const float rsq = s_rsq;
   for (int j = threadIdx.x; j < n; j += blockDim.x) {
     float v = __fmul_rn(xr[j], rsq);
     if (gain != nullptr) v = __fmul_rn(v, gain[j]);
@@ -139,6 +163,21 @@ RopeKvWriteKernel(const float* q, const float* k, const float* v, const int* pos
 }
 
 __device__ __forceinline__ float SiluMul(float g, float u) { return __fmul_rn(g / (1.f + expf(-g)), u); }
+// SILU as the interpreter evaluates it: in double, narrowed once (DxirInterpreter.kt:567-592).
+__device__ __forceinline__ float SiluMulOrderFaithful(float g, float u)
+{
+  const double gd = static_cast<double>(g);
+  return __fmul_rn(static_cast<float>(gd / (1.0 + exp(-gd))), u);
+}
+template <typename OT>
+__global__ void SwigluOrderFaithfulKernel(const float* gate, const float* up, int ld, OT* out, int rows, int n)
+{
+  GridDependencySync();
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<size_t>(rows) * n) return;
+  const int r = static_cast<int>(i / n), c = static_cast<int>(i - static_cast<size_t>(r) * n);
+  out[i] = FromF32<OT>(SiluMulOrderFaithful(gate[static_cast<size_t>(r) * ld + c], up[static_cast<size_t>(r) * ld + c]));
+}
 
 // Four columns per thread when the rows allow 16-byte accesses (VEC), else one.
 template <typename OT, bool VEC>
@@ -240,7 +279,11 @@ extern "C" int tlaloc_b200_rmsnorm(const float* x, const float* gain, void* out,
   if (rows == 0) return kOk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
-  if (out_dtype == TLALOC_B200_F32) {
+  if (OrderFaithful()) {
+    e = out_dtype == TLALOC_B200_F32
+            ? LaunchChained(RmsNormOrderFaithfulKernel<float>, rows, 256, 0, st, x, gain, static_cast<float*>(out), n, eps)
+            : LaunchChained(RmsNormOrderFaithfulKernel<__nv_bfloat16>, rows, 256, 0, st, x, gain, static_cast<__nv_bfloat16*>(out), n, eps);
+  } else if (out_dtype == TLALOC_B200_F32) {
     e = LaunchChained(RmsNormKernel<float>, rows, 256, 0, st, x, gain, static_cast<float*>(out), n, eps);
   } else {
     e = LaunchChained(RmsNormKernel<__nv_bfloat16>, rows, 256, 0, st, x, gain, static_cast<__nv_bfloat16*>(out), n, eps);
@@ -302,7 +345,12 @@ extern "C" int tlaloc_b200_swiglu(const float* gate, const float* up, int32_t ld
   const size_t total = static_cast<size_t>(rows) * (vec ? n / 4 : n);
   const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
   cudaError_t e;
-  if (out_dtype == TLALOC_B200_F32) {
+  if (OrderFaithful()) {
+    const unsigned fb = static_cast<unsigned>((static_cast<size_t>(rows) * n + 255) / 256);
+    e = out_dtype == TLALOC_B200_F32
+            ? LaunchChained(SwigluOrderFaithfulKernel<float>, fb, 256, 0, st, gate, up, ld, static_cast<float*>(out), rows, n)
+            : LaunchChained(SwigluOrderFaithfulKernel<__nv_bfloat16>, fb, 256, 0, st, gate, up, ld, static_cast<__nv_bfloat16*>(out), rows, n);
+  } else if (out_dtype == TLALOC_B200_F32) {
     e = vec ? LaunchChained(SwigluKernel<float, true>, blocks, 256, 0, st, gate, up, ld, static_cast<float*>(out), rows, n)
             : LaunchChained(SwigluKernel<float, false>, blocks, 256, 0, st, gate, up, ld, static_cast<float*>(out), rows, n);
   } else {

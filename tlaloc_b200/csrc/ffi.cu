@@ -25,9 +25,11 @@ char* ErrorBuffer()
 
 namespace {
 std::atomic<long long> g_launches{0};
+std::atomic<int> g_order_faithful{0};
 }  // namespace
 
 void CountLaunches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+bool OrderFaithful() { return g_order_faithful.load(std::memory_order_relaxed) != 0; }
 
 namespace {
 
@@ -291,6 +293,11 @@ extern "C" const char* tlaloc_b200_last_error(void) { return ErrorBuffer(); }
 extern "C" long long tlaloc_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int tlaloc_b200_device_status(void) { return ReadTcStatus(); }
+
+extern "C" int tlaloc_b200_set_order_faithful(int on)
+{
+  return g_order_faithful.exchange(on != 0 ? 1 : 0, std::memory_order_relaxed);
+}
 
 extern "C" int tlaloc_b200_init(void)
 {

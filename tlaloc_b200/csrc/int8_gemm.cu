@@ -18,8 +18,6 @@
 //                    multiply and add, zero activations skipped.  Bit-identical to the CPU oracle; slow.
 #include <cooperative_groups.h>
 
-#include <mutex>
-
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -356,18 +354,16 @@ int ChooseSlices(int k, int n)
 
 cudaError_t PrepareInt8GemmKernels()
 {
-  static std::mutex mu;
-  static bool done = false;
-  std::lock_guard<std::mutex> lock(mu);
-  if (done) return cudaSuccess;
-  cudaError_t e = PrepareGemv<1, float>();
-  if (e == cudaSuccess) e = PrepareGemv<1, __nv_bfloat16>();
-  if (e == cudaSuccess) e = PrepareGemv<2, float>();
-  if (e == cudaSuccess) e = PrepareGemv<2, __nv_bfloat16>();
-  if (e == cudaSuccess) e = PrepareGemv<4, float>();
-  if (e == cudaSuccess) e = PrepareGemv<4, __nv_bfloat16>();
-  if (e == cudaSuccess) done = true;
-  return e;
+  static OncePerDevice once;
+  return once.Run([](int) {
+    cudaError_t e = PrepareGemv<1, float>();
+    if (e == cudaSuccess) e = PrepareGemv<1, __nv_bfloat16>();
+    if (e == cudaSuccess) e = PrepareGemv<2, float>();
+    if (e == cudaSuccess) e = PrepareGemv<2, __nv_bfloat16>();
+    if (e == cudaSuccess) e = PrepareGemv<4, float>();
+    if (e == cudaSuccess) e = PrepareGemv<4, __nv_bfloat16>();
+    return e;
+  });
 }
 
 }  // namespace tlaloc_b200
@@ -401,15 +397,12 @@ cudaError_t LaunchGemvRows(const GemmParams& p, int rows, cudaStream_t st)
 
 }  // namespace
 
-// Scratch layout: [bf16 copy of an f32 x, rounded up to 256 bytes][partial tiles and flags of the evenly spread
-// tensor-core launch].  The second part is optional: a shorter buffer only rules that launch form out.
-static size_t CastBytes(int m, int k) { return (sizeof(__nv_bfloat16) * static_cast<size_t>(m) * k + 255) / 256 * 256; }
-
+// Scratch: the bf16 copy of an f32 x, nothing else.
 extern "C" size_t tlaloc_b200_int8_gemm_scratch_bytes(int32_t m, int32_t k, int32_t n)
 {
   (void)n;
   if (m <= 0 || k <= 0) return 0;
-  return CastBytes(m, k) + (m > 32 ? TcStreamScratchBytes() : 0);
+  return (sizeof(__nv_bfloat16) * static_cast<size_t>(m) * k + 255) / 256 * 256;
 }
 
 extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_t* codes, const float* scales,
@@ -423,7 +416,10 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
   if (m < 1 || k < 1 || n < 1) return Fail(kInvalid, "%s: needs positive [M, K] x [K, N], got M %d K %d N %d", op, m, k, n);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
-  if ((flags & TLALOC_B200_GEMM_EXACT) != 0 || !FastShape(k, n)) {
+  // The fast kernels move x and the codes in 16-byte pieces: a view that starts off a 16-byte boundary (x + 4 elements,
+  // a weight slice at an odd column) takes the order-faithful kernel instead, which has no alignment needs.
+  const bool aligned = Aligned16(codes) && (x_dtype == TLALOC_B200_F32 || Aligned16(x));
+  if ((flags & TLALOC_B200_GEMM_EXACT) != 0 || OrderFaithful() || !FastShape(k, n) || !aligned) {
     const int round_x = x_dtype == TLALOC_B200_F32 && (flags & TLALOC_B200_GEMM_X_F32_EXACT) == 0;
     e = x_dtype == TLALOC_B200_F32
             ? LaunchExact<float, int8_t>(x, codes, scales, residual, y, y_dtype, m, k, n, round_x, st)
@@ -440,6 +436,7 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
     if (scratch == nullptr || scratch_bytes < need) {
       return Fail(kInvalid, "%s: an f32 x needs %zu bytes of scratch for its bf16 copy, got %zu", op, need, scratch_bytes);
     }
+    if (!Aligned16(scratch)) return Fail(kInvalid, "%s: scratch must be 16-byte aligned", op);
     const size_t count = static_cast<size_t>(m) * k;
     e = LaunchChained(ToBf16Kernel<float>, static_cast<unsigned>((count + 255) / 256), 256, 0, st,
                       static_cast<const float*>(x), reinterpret_cast<__nv_bfloat16*>(scratch), count);
@@ -455,12 +452,8 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
     e = PrepareInt8GemmTcKernels();
     if (e != cudaSuccess) return CudaFail("INT8_PROJ set-up", e);
     int launches = 0;
-    const size_t cast_bytes = CastBytes(m, k);
-    const bool has_stream = scratch != nullptr && scratch_bytes >= cast_bytes + TcStreamScratchBytes();
     e = LaunchInt8GemmTc(xb, codes, scales, residual, y, y_dtype, m, k, n, st, &launches,
-                         (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0,
-                         has_stream ? reinterpret_cast<unsigned char*>(scratch) + cast_bytes : nullptr,
-                         has_stream ? scratch_bytes - cast_bytes : 0);
+                         (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0);
     if (e != cudaSuccess) return CudaFail("INT8_PROJ tensor-core launch", e);
     CountLaunches(launches);
     return kOk;

@@ -28,9 +28,8 @@
 // Every mbarrier wait is bounded: on a time-out the kernel records it in a status word, frees its TMEM and returns.
 #include <cooperative_groups.h>
 
-#include <atomic>
 #include <mutex>
-#include <random>
+#include <string>
 #include <type_traits>
 
 #include "common.cuh"
@@ -49,6 +48,7 @@ struct TcParams {
   int M, K, N;
   int Kc, ks;
   int weights_const;  // codes and scales are not written by the preceding kernel: fetch them before the dependency wait
+  int prefetch;       // blocks ahead of the tensor core at which a block's weights are asked into L2 (0 = never)
 };
 
 constexpr int kTcThreads = 512;                    // converter threads (16 warps)
@@ -58,7 +58,27 @@ constexpr int kTcBK = 64;                          // k rows per block
 constexpr int kTcWBytes = kTcBN * kTcBK * 2;       // one block's weights as bf16
 constexpr int kTcTileStride = kTcBN + 4;
 constexpr uint32_t kTcSpinLimit = 1u << 22;
-constexpr int kTcMaxCtas = 148;  // the evenly spread launch: at most one CTA per SM of a B200
+
+// $TLALOC_B200_GEMM_W16 = bf16 keeps the converted weights as bf16 (three logic ops and a packed fma per pair of codes)
+// instead of the default f16 (two logic ops and a packed subtract); both are exact for int8 codes.
+bool TcHalfWeights()
+{
+  static const bool v = [] {
+    const char* e = std::getenv("TLALOC_B200_GEMM_W16");
+    return e == nullptr || std::string(e) != "bf16";
+  }();
+  return v;
+}
+// $TLALOC_B200_GEMM_PREFETCH: how many blocks ahead of the tensor core the weights are asked into L2 (default 8).
+int TcPrefetchDistance()
+{
+  static const int v = [] {
+    const char* e = std::getenv("TLALOC_B200_GEMM_PREFETCH");
+    const int x = e != nullptr ? std::atoi(e) : 8;
+    return x < 0 ? 0 : x > 64 ? 64 : x;
+  }();
+  return v;
+}
 
 __device__ int g_tc_status = 0;  // nonzero after an mbarrier wait timed out (sticky until read)
 
@@ -133,13 +153,29 @@ __device__ __forceinline__ uint32_t LowBytesToBf16x2(uint32_t q)
   asm("fma.rn.bf16x2 %0, %1, %2, %3;\n" : "=r"(r) : "r"(t), "r"(0x3F803F80u), "r"(c));
   return r;
 }
+// The same two codes as an exact f16 pair: with u = code + 128 (the byte with its top bit flipped), 0x6400|u is the
+// f16 1024 + u, and 1024 + u - 1152 = code; one logic op ((q & 0x00FF00FF) ^ 0x64806480) and one packed subtract
+// (0x6480 is also the f16 1152).
+__device__ __forceinline__ uint32_t LowBytesToF16x2(uint32_t q)
+{
+  uint32_t t, r;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;\n" : "=r"(t) : "r"(q), "r"(0x00FF00FFu), "r"(0x64806480u));
+  asm("sub.rn.f16x2 %0, %1, %2;\n" : "=r"(r) : "r"(t), "r"(0x64806480u));
+  return r;
+}
 // The four codes c0..c3 of one word as the pairs (c0, c2) and (c1, c3): the even bytes already sit in the low byte of
 // each half, the odd ones after one shift, so no byte permute is needed.  The weight tile therefore holds its columns
 // in the order 0 2 1 3 within every group of four; the epilogue swaps them back on the way out of TMEM.
-__device__ __forceinline__ void WordToBf16(uint32_t w, uint32_t& even, uint32_t& odd)
+template <bool F16W>
+__device__ __forceinline__ void WordTo16(uint32_t w, uint32_t& even, uint32_t& odd)
 {
-  even = LowBytesToBf16x2(w);
-  odd = LowBytesToBf16x2(w >> 8);
+  if constexpr (F16W) {
+    even = LowBytesToF16x2(w);
+    odd = LowBytesToF16x2(w >> 8);
+  } else {
+    even = LowBytesToBf16x2(w);
+    odd = LowBytesToBf16x2(w >> 8);
+  }
 }
 
 __device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count)
@@ -179,10 +215,16 @@ __device__ __forceinline__ uint64_t SmemDesc(uint32_t addr, uint32_t lbo_bytes, 
   return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) | (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16) |
          (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
-// kind::f16 instruction descriptor: f32 accumulator, bf16 A and B, A K-major, B MN-major, M = 128, N = 256.
-__host__ __device__ constexpr uint32_t InstrDesc()
+// kind::f16 instruction descriptor: f32 accumulator, bf16 A, B bf16 or f16 (the format fields are separate), A K-major,
+// B MN-major, M = 128, N = 256.
+__host__ __device__ constexpr uint32_t InstrDesc(bool b_is_f16)
 {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(kTcBN >> 3) << 17) | (8u << 24);
+  return (1u << 4) | (1u << 7) | (b_is_f16 ? 0u : (1u << 10)) | (1u << 16) | (static_cast<uint32_t>(kTcBN >> 3) << 17) | (8u << 24);
+}
+// Asks the memory system to bring `bytes` (a multiple of 16, from a 16-byte aligned address) into L2; no data returns.
+__device__ __forceinline__ void PrefetchL2(const void* ptr, uint32_t bytes)
+{
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(ptr), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void TcMma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
 {
@@ -268,7 +310,7 @@ __device__ __forceinline__ void ClusterReduceRows(cg::cluster_group& cluster, fl
   }
 }
 
-template <int MPAD, typename YT>
+template <int MPAD, typename YT, bool F16W>
 __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams p)
 {
   using L = TcLayout<MPAD>;
@@ -339,8 +381,20 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
   // Everything above touched only shared memory and TMEM.  The weights and scales are the first global reads; when
   // the caller says no preceding kernel writes them they are requested BEFORE the dependency wait, so the coldest
   // loads of the launch travel while the predecessor drains.  The activations always come after it.
+  // Block bp of this CTA into L2, by the lanes of the seventeenth warp: rows lane and lane + 32, the tile's columns.
+  const uint32_t tile_bytes = static_cast<uint32_t>(min(kTcBN, p.N - col0));
+  auto prefetch_block = [&](int bp) {
+    if (bp >= nblocks) return;
+    const int row = kb0 + bp * kTcBK + lane;
+    const int8_t* src = p.w + static_cast<size_t>(row) * p.N + col0;
+    if (row < ke) PrefetchL2(src, tile_bytes);
+    if (row + 32 < ke) PrefetchL2(src + static_cast<size_t>(32) * p.N, tile_bytes);
+  };
   uint4 wreg[kChunks];
   if (!p.weights_const) GridDependencySync();
+  if (!conv && p.prefetch > 0) {  // the blocks the converters do not already hold in registers
+    for (int bp = kG; bp < p.prefetch; ++bp) prefetch_block(bp);
+  }
 #pragma unroll
   for (int i = 0; i < kChunks; ++i)
     wreg[i] = LdWeights16(wp + static_cast<size_t>(grp) * blk + i * pass, col_ok && kb0 + grp * kTcBK + row0 + kRP * i < ke);
@@ -383,10 +437,10 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
         for (int i = 0; i < kChunks; ++i) {
           const uint4 v = wreg[i];
           uint32_t o0, o1, o2, o3, o4, o5, o6, o7;
-          WordToBf16(v.x, o0, o1);
-          WordToBf16(v.y, o2, o3);
-          WordToBf16(v.z, o4, o5);
-          WordToBf16(v.w, o6, o7);
+          WordTo16<F16W>(v.x, o0, o1);
+          WordTo16<F16W>(v.y, o2, o3);
+          WordTo16<F16W>(v.z, o4, o5);
+          WordTo16<F16W>(v.w, o6, o7);
           StShared16(bt + i * (kRP * 128) + s0, o0, o1, o2, o3);
           StShared16(bt + i * (kRP * 128) + s1, o4, o5, o6, o7);
           // the group's next block, one group period ahead
@@ -404,30 +458,37 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(conv_done0 + buf * 8) : "memory");
       }
     }
-  } else if (lane == 0) {
-    // The MMA thread: for each block, wait for its converter group, then 4 K-steps of 128 x 256 x 16 per accumulator
-    // and a commit.  A = the activation strip (K-major), B = the converted weights (MN-major).  Descriptors differ
-    // from block to block only in the 14-bit start-address field, so they are built once and advanced by adds.
-    constexpr uint32_t idesc = InstrDesc();
+  } else {
+    // The seventeenth warp.  Lane 0 is the MMA thread: for each block, wait for its converter group, then 4 K-steps of
+    // 128 x 256 x 16 per accumulator and a commit.  A = the activation strip (K-major), B = the converted weights
+    // (MN-major).  Descriptors differ from block to block only in the 14-bit start-address field, so they are built
+    // once and advanced by adds.  After each block all 32 lanes ask the weights of the block `prefetch` ahead into
+    // L2 (two 256-byte rows per lane), so the converters' register loads, which run one group period ahead, find them
+    // there: the latency of HBM is then covered by L2's capacity and not by the registers a thread can spare.
+    constexpr uint32_t idesc = InstrDesc(F16W);
     const uint64_t a_desc0 = SmemDesc(smem_base, 16, 1024), b_desc0 = SmemDesc(smem_base + L::kWOffset, 8192, 1024);
     for (int b = 0; b < nblocks; ++b) {
       const int buf = b % L::kBufs;
-      ok = MbarWait(conv_done0 + buf * 8, (b / L::kBufs) & 1) && ok;
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((buf * L::kXBytes) >> 4);
-      const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((buf * kTcWBytes) >> 4);
+      ok = MbarWaitWarp(conv_done0 + buf * 8, (b / L::kBufs) & 1, lane) && ok;
+      if (lane == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((buf * L::kXBytes) >> 4);
+        const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((buf * kTcWBytes) >> 4);
 #pragma unroll
-      for (int ks = 0; ks < kTcBK / 16; ++ks) {
+        for (int ks = 0; ks < kTcBK / 16; ++ks) {
 #pragma unroll
-        for (int acc = 0; acc < L::kAccs; ++acc)
-          TcMma(tmem_base + acc * kTcBN, a_desc + static_cast<uint64_t>((acc * 16384 + ks * 32) >> 4),
-                b_desc + static_cast<uint64_t>((ks * 2048) >> 4), idesc, (b > 0 || ks > 0) ? 1u : 0u);
+          for (int acc = 0; acc < L::kAccs; ++acc)
+            TcMma(tmem_base + acc * kTcBN, a_desc + static_cast<uint64_t>((acc * 16384 + ks * 32) >> 4),
+                  b_desc + static_cast<uint64_t>((ks * 2048) >> 4), idesc, (b > 0 || ks > 0) ? 1u : 0u);
+        }
+        TcCommit(mma_done0 + buf * 8);
       }
-      TcCommit(mma_done0 + buf * 8);
+      if (p.prefetch > 0) prefetch_block(b + p.prefetch);
+      __syncwarp();
     }
     // The last commit covers every MMA before it.  Its phase is unambiguous here: the converters of the last block
     // had already waited for the same barrier's previous phase.
-    if (nblocks > 0) ok = MbarWait(mma_done0 + ((nblocks - 1) % L::kBufs) * 8, ((nblocks - 1) / L::kBufs) & 1) && ok;
+    if (nblocks > 0) ok = MbarWaitWarp(mma_done0 + ((nblocks - 1) % L::kBufs) * 8, ((nblocks - 1) / L::kBufs) & 1, lane) && ok;
   }
   if (!ok) atomicExch(&g_tc_status, 1);
   if (warp < kTcThreads / 32) CpAsyncWait<0>();
@@ -465,7 +526,7 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
 #pragma unroll
       for (int c = 0; c < 16; ++c)
         dst[c] = make_float4(__uint_as_float(rr[4 * c]), __uint_as_float(rr[4 * c + 2]), __uint_as_float(rr[4 * c + 1]),
-                             __uint_as_float(rr[4 * c + 3]));  // TMEM holds the columns as 0 2 1 3 (see WordToBf16)
+                             __uint_as_float(rr[4 * c + 3]));  // TMEM holds the columns as 0 2 1 3 (see WordTo16)
     }
     if (nranks == 1) {
       __syncthreads();
@@ -521,325 +582,12 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
   }
 }
 
-// ------------------------------------------------------------------------------------------------------------
-// The same pipeline with the work spread evenly ("stream-K"): the launch's units are (column tile, 64-row block)
-// pairs, numbered tile-major; CTA i of G takes the units [total * i / G, total * (i + 1) / G), whatever tiles they
-// fall in.  A CTA's range is a run of SEGMENTS, each one contiguous run of blocks of one tile:
-//   * a whole tile: finished and stored by this CTA as in the kernel above;
-//   * the tail of a tile (does not start at block 0), which can only be the CTA's FIRST segment: the partial
-//     accumulator goes to the CTA's slot in the caller's scratch, then the slot's flag takes the launch's epoch;
-//   * the head of a tile (starts at block 0, ends early), which can only be the CTA's LAST segment: this CTA finishes
-//     the tile.  It adds to its own partial the slots of the CTAs i + 1, ... whose ranges start inside the tile, in
-//     that order (ascending k: the result does not depend on timing), after each slot's flag shows the epoch.
-// Contributors write their slot first thing and finishers wait last thing, and a finisher only ever waits for
-// higher-numbered CTAs, so no wait can be circular; all G <= 148 CTAs (one per SM) are resident together.  The wait is
-// bounded like every other one.  No wave is ever partly empty, and no cluster is needed.
-struct TcStreamParams {
-  const __nv_bfloat16* x;
-  const int8_t* w;
-  const float* scales;
-  const float* residual;
-  void* y;
-  float* slots;               // [G][128][256] f32 partial tiles
-  unsigned long long* flags;  // [G]
-  unsigned long long epoch;
-  int M, K, N;
-  int nb;     // 64-row blocks per tile
-  int total;  // tiles * nb
-  int weights_const;
-};
-
-constexpr size_t kTcSlotFloats = static_cast<size_t>(128) * kTcBN;
-
-template <int MPAD, typename YT>
-__global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcStreamKernel(TcStreamParams p)
-{
-  using L = TcLayout<MPAD>;
-  static_assert(MPAD <= 128, "one accumulator");
-  extern __shared__ unsigned char smem_raw[];
-  const uint32_t smem_base = (SmemAddr(smem_raw) + 1023u) & ~1023u;
-  unsigned char* smem = smem_raw + (smem_base - SmemAddr(smem_raw));
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int G = gridDim.x, cta = blockIdx.x;
-  const int L0 = static_cast<int>(static_cast<long long>(p.total) * cta / G);
-  const int L1 = static_cast<int>(static_cast<long long>(p.total) * (cta + 1) / G);
-  const int nblocks = L1 - L0;
-  // mma_done / conv_done as above; seg_done: the MMAs of a segment have completed (the accumulator may be read);
-  // epi_done: the sixteen converter warps have finished a segment's epilogue (the accumulator and the shared-memory
-  // tile, which overlays the pipeline buffers, may be reused).
-  const uint32_t mma_done0 = smem_base + L::kBarOffset, conv_done0 = mma_done0 + 8 * L::kBufs;
-  const uint32_t seg_done = conv_done0 + 8 * L::kBufs, epi_done = seg_done + 8;
-  const uint32_t tmem_slot_addr = smem_base + L::kBarOffset + 96;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + 96);
-  static_assert(8 * (2 * L::kBufs + 2) <= 96, "barriers fit before the TMEM slot");
-
-  if (tid == 0) {
-    for (int i = 0; i < L::kBufs; ++i) {
-      MbarInit(mma_done0 + 8 * i, 1);
-      MbarInit(conv_done0 + 8 * i, L::kGroupWarps);
-    }
-    MbarInit(seg_done, 1);
-    MbarInit(epi_done, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tmem_slot_addr),
-                 "r"(static_cast<uint32_t>(L::kTmemCols))
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-  const uint32_t tmem_base = *tmem_slot;
-
-  constexpr int kG = L::kGroups, kChunks = L::kChunks, kRP = L::kRowsPerPass, kXR = L::kXRowsPerPass;
-  const bool conv = warp < kTcThreads / 32;
-  const int grp = warp / L::kGroupWarps, wg = warp % L::kGroupWarps, gtid = tid % L::kGroupThreads;
-  const int j = lane & 3, r = (lane >> 2) & 1, atom = lane >> 3;
-  const int row0 = 2 * wg + r, k_in = row0 & 7;
-  const int ccol = atom * 64 + j * 16;
-  const size_t pass = static_cast<size_t>(kRP) * p.N;
-  const uint32_t dst_off = atom * 8192 + (row0 >> 3) * 1024 + k_in * 128;
-  const uint32_t s0 = static_cast<uint32_t>((2 * j) ^ k_in) << 4, s1 = static_cast<uint32_t>((2 * j + 1) ^ k_in) << 4;
-  const int xm0 = gtid >> 3, xch = gtid & 7;
-  const uint32_t xdst0 = (xm0 >> 3) * 1024 + (xm0 & 7) * 128 + ((xch ^ (xm0 & 7)) << 4);
-  const size_t xstep = static_cast<size_t>(kXR) * p.K;
-  const int x_rows = p.M > xm0 ? (p.M - xm0 + kXR - 1) / kXR : 0;
-
-  // Block b of this CTA (0 <= b < nblocks) is unit L0 + b: tile (L0 + b) / nb, k rows from ((L0 + b) % nb) * 64.
-  auto load_first = [&](int b, uint4(&v)[kChunks]) {
-    const int unit = L0 + b, tile = unit / p.nb, k0 = (unit - tile * p.nb) * kTcBK;
-    const bool ok_col = conv && b < nblocks && tile * kTcBN + ccol < p.N;
-    const int8_t* q = p.w + static_cast<size_t>(k0 + row0) * p.N + tile * kTcBN + ccol;
-#pragma unroll
-    for (int i = 0; i < kChunks; ++i) v[i] = LdWeights16(q + i * pass, ok_col && k0 + row0 + kRP * i < p.K);
-  };
-
-  uint4 wreg[kChunks];
-  if (!p.weights_const) GridDependencySync();
-  load_first(grp, wreg);
-  if (p.weights_const) GridDependencySync();
-
-  float* tile_s = reinterpret_cast<float*>(smem);
-  YT* y = static_cast<YT*>(p.y);
-  const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0 &&
-                      (reinterpret_cast<uintptr_t>(p.scales) & 15) == 0;
-  const int lg = warp & 3, wq = warp >> 2;
-  bool ok = true;
-
-  int seg_begin = 0, seg_no = 0;
-  while (seg_begin < nblocks) {
-    const int unit0 = L0 + seg_begin, tile = unit0 / p.nb, kb_first = unit0 - tile * p.nb;
-    const int seg_len = min(nblocks - seg_begin, p.nb - kb_first);
-    const int seg_end = seg_begin + seg_len;
-    const int col0 = tile * kTcBN;
-    if (conv) {
-      // this group's blocks of the segment: b = grp (mod kG) in the CTA's own numbering, which runs across segments
-      int b = seg_begin + ((grp - seg_begin) % kG + kG) % kG;
-      for (; b < seg_end; b += kG) {
-        const int buf = b % L::kBufs;
-        if (b >= L::kBufs) ok = MbarWaitWarp(mma_done0 + buf * 8, ((b / L::kBufs) - 1) & 1, lane) && ok;
-        const int k0 = (kb_first + (b - seg_begin)) * kTcBK;
-        {
-          const uint32_t st = smem_base + buf * L::kXBytes + xdst0;
-          const __nv_bfloat16* src = p.x + static_cast<size_t>(xm0) * p.K + k0 + xch * 8;
-          if (k0 + kTcBK <= p.K) {
-#pragma unroll
-            for (int i = 0; i < MPAD / kXR; ++i)
-              if (i < x_rows) CpAsync16(st + i * (kXR * 128), src + i * xstep, 16);
-          } else {
-            const bool k_ok = k0 + xch * 8 < p.K;
-#pragma unroll
-            for (int i = 0; i < MPAD / kXR; ++i) {
-              const bool valid = k_ok && i < x_rows;
-              CpAsync16(st + i * (kXR * 128), valid ? src + i * xstep : p.x, valid ? 16 : 0);
-            }
-          }
-          CpAsyncCommit();
-        }
-        const uint32_t bt = smem_base + L::kWOffset + buf * kTcWBytes + dst_off;
-        // the group's next block, one group period ahead: kG units on, which may be in the next tile (the next segment)
-        int nkb = kb_first + (b - seg_begin) + kG, ntile = tile;
-        while (nkb >= p.nb) {
-          nkb -= p.nb;
-          ++ntile;
-        }
-        const int nk0 = nkb * kTcBK;
-        const bool nok = b + kG < nblocks && ntile * kTcBN + ccol < p.N;
-        const int8_t* nq = p.w + static_cast<size_t>(nk0 + row0) * p.N + ntile * kTcBN + ccol;
-#pragma unroll
-        for (int i = 0; i < kChunks; ++i) {
-          const uint4 v = wreg[i];
-          uint32_t o0, o1, o2, o3, o4, o5, o6, o7;
-          WordToBf16(v.x, o0, o1);
-          WordToBf16(v.y, o2, o3);
-          WordToBf16(v.z, o4, o5);
-          WordToBf16(v.w, o6, o7);
-          StShared16(bt + i * (kRP * 128) + s0, o0, o1, o2, o3);
-          StShared16(bt + i * (kRP * 128) + s1, o4, o5, o6, o7);
-          wreg[i] = LdWeights16(nq + i * pass, nok && nk0 + row0 + kRP * i < p.K);
-        }
-        CpAsyncWait<0>();
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        __syncwarp();
-        if (lane == 0) {
-          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(conv_done0 + buf * 8) : "memory");
-        }
-      }
-      // ---- the segment's epilogue -------------------------------------------------------------------------------
-      ok = MbarWaitWarp(seg_done, seg_no & 1, lane) && ok;
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      if (lg * 32 < L::kTileRows) {
-        const int m = lg * 32 + lane;
-        uint32_t rr[64];
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + wq * 64;
-        TcLd32(taddr, rr);
-        TcLd32(taddr + 32, rr + 32);
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        float4* dst = reinterpret_cast<float4*>(tile_s + m * kTcTileStride + wq * 64);
-#pragma unroll
-        for (int c = 0; c < 16; ++c)
-          dst[c] = make_float4(__uint_as_float(rr[4 * c]), __uint_as_float(rr[4 * c + 2]), __uint_as_float(rr[4 * c + 1]),
-                               __uint_as_float(rr[4 * c + 3]));  // TMEM holds the columns as 0 2 1 3 (see WordToBf16)
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-      asm volatile("bar.sync 1, %0;\n" ::"n"(kTcThreads) : "memory");  // the converter warps only
-      const bool head = kb_first == 0, whole = head && seg_len == p.nb;
-      const int c4 = (tid & 63) * 4;
-      const bool col_in = col0 + c4 < p.N;
-      if (!head) {
-        // the tail of a tile: park the partial sums in this CTA's slot
-        float* slot = p.slots + static_cast<size_t>(cta) * kTcSlotFloats;
-        for (int m = tid >> 6; m < p.M; m += 8)
-          *reinterpret_cast<float4*>(slot + m * kTcBN + c4) = *reinterpret_cast<const float4*>(tile_s + m * kTcTileStride + c4);
-        __threadfence();
-        asm volatile("bar.sync 1, %0;\n" ::"n"(kTcThreads) : "memory");
-        if (tid == 0) asm volatile("st.release.gpu.global.u64 [%0], %1;\n" ::"l"(p.flags + cta), "l"(p.epoch) : "memory");
-      } else {
-        // a whole tile, or the head of one: then this CTA finishes it with the slots of the CTAs whose ranges start
-        // inside it (cta + 1 .. cta + nc), each read only after its flag shows this launch's epoch
-        int nc = 0;
-        if (!whole) {
-          const int tile_end = (tile + 1) * p.nb;
-          for (int jc = cta + 1; jc < G; ++jc) {
-            if (static_cast<int>(static_cast<long long>(p.total) * jc / G) >= tile_end) break;
-            int seen = 1;
-            if (lane == 0) {
-              seen = 0;
-              for (uint32_t spin = 0; spin < kTcSpinLimit; ++spin) {
-                unsigned long long f;
-                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];\n" : "=l"(f) : "l"(p.flags + jc) : "memory");
-                if (f == p.epoch) {
-                  seen = 1;
-                  break;
-                }
-                __nanosleep(100);
-              }
-            }
-            seen = __shfl_sync(0xffffffffu, seen, 0);
-            ok = ok && seen != 0;
-            ++nc;
-          }
-          __threadfence();  // the other lanes' slot reads come after lane 0's acquire
-        }
-        if (col_in) {
-          float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
-          if (p.scales != nullptr) {
-            if (vec_ok) sc = __ldg(reinterpret_cast<const float4*>(p.scales + col0 + c4));
-            else sc = make_float4(__ldg(p.scales + col0 + c4), __ldg(p.scales + col0 + c4 + 1), __ldg(p.scales + col0 + c4 + 2),
-                                  __ldg(p.scales + col0 + c4 + 3));
-          }
-#pragma unroll 2
-          for (int row = tid >> 6; row < p.M; row += 8) {
-            float4 v = *reinterpret_cast<const float4*>(tile_s + row * kTcTileStride + c4);
-            for (int q = 1; q <= nc; ++q) {  // ascending k: the sum does not depend on who finished first
-              const float4 u = __ldcg(reinterpret_cast<const float4*>(p.slots + static_cast<size_t>(cta + q) * kTcSlotFloats + row * kTcBN + c4));
-              v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
-            }
-            const size_t at = static_cast<size_t>(row) * p.N + col0 + c4;
-            v.x *= sc.x; v.y *= sc.y; v.z *= sc.z; v.w *= sc.w;
-            if (p.residual != nullptr) {
-              if (vec_ok) {
-                const float4 rs = __ldg(reinterpret_cast<const float4*>(p.residual + at));
-                v.x += rs.x; v.y += rs.y; v.z += rs.z; v.w += rs.w;
-              } else {
-                v.x += __ldg(p.residual + at); v.y += __ldg(p.residual + at + 1);
-                v.z += __ldg(p.residual + at + 2); v.w += __ldg(p.residual + at + 3);
-              }
-            }
-            StoreRow4(y + at, v, vec_ok);
-          }
-        }
-      }
-      asm volatile("bar.sync 1, %0;\n" ::"n"(kTcThreads) : "memory");  // the tile (= the pipeline buffers) is free again
-      if (tid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(epi_done) : "memory");
-    } else if (lane == 0) {
-      // The MMA thread: the segment's blocks, the first one overwriting the accumulator.
-      constexpr uint32_t idesc = InstrDesc();
-      const uint64_t a_desc0 = SmemDesc(smem_base, 16, 1024), b_desc0 = SmemDesc(smem_base + L::kWOffset, 8192, 1024);
-      if (seg_no > 0) {  // the previous segment has left the accumulator
-        ok = MbarWait(epi_done, (seg_no - 1) & 1) && ok;
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      }
-      for (int b = seg_begin; b < seg_end; ++b) {
-        const int buf = b % L::kBufs;
-        ok = MbarWait(conv_done0 + buf * 8, (b / L::kBufs) & 1) && ok;
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((buf * L::kXBytes) >> 4);
-        const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((buf * kTcWBytes) >> 4);
-#pragma unroll
-        for (int ks = 0; ks < kTcBK / 16; ++ks)
-          TcMma(tmem_base, a_desc + static_cast<uint64_t>((ks * 32) >> 4), b_desc + static_cast<uint64_t>((ks * 2048) >> 4), idesc,
-                (b > seg_begin || ks > 0) ? 1u : 0u);
-        TcCommit(mma_done0 + buf * 8);
-      }
-      TcCommit(seg_done);
-    }
-    seg_begin = seg_end;
-    ++seg_no;
-  }
-  if (!ok) atomicExch(&g_tc_status, 1);
-  if (conv) CpAsyncWait<0>();
-  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  __syncthreads();
-  if (warp == 0) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(static_cast<uint32_t>(L::kTmemCols)) : "memory");
-  }
-}
-
 template <int MPAD, typename YT>
 cudaError_t PrepareTc()
 {
-  cudaError_t e = cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD>::kBytes);
-  if constexpr (MPAD <= 128) {
-    if (e == cudaSuccess) {
-      e = cudaFuncSetAttribute(Int8GemmTcStreamKernel<MPAD, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD>::kBytes);
-    }
-  }
+  cudaError_t e = cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD>::kBytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD>::kBytes);
   return e;
-}
-
-template <int MPAD, typename YT>
-cudaError_t LaunchTcStream(const TcStreamParams& p, int ctas, cudaStream_t stream)
-{
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(ctas, 1, 1);
-  cfg.blockDim = dim3(kTcLaunchThreads, 1, 1);
-  cfg.dynamicSmemBytes = TcLayout<MPAD>::kBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  cfg.numAttrs = ChainAttributes(attr);
-  cfg.attrs = attr;
-  return cudaLaunchKernelEx(&cfg, Int8GemmTcStreamKernel<MPAD, YT>, p);
-}
-
-template <typename YT>
-cudaError_t LaunchTcStreamRows(const TcStreamParams& p, int rows, int ctas, cudaStream_t st)
-{
-  if (rows <= 32) return LaunchTcStream<32, YT>(p, ctas, st);
-  if (rows <= 64) return LaunchTcStream<64, YT>(p, ctas, st);
-  return LaunchTcStream<128, YT>(p, ctas, st);
 }
 
 template <int MPAD, typename YT>
@@ -853,16 +601,17 @@ cudaError_t LaunchTc(const TcParams& p, cudaStream_t stream)
   cudaLaunchAttribute attr[2];
   cfg.numAttrs = ChainAttributes(attr, p.ks);
   cfg.attrs = attr;
-  return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT>, p);
+  if (TcHalfWeights()) return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT, true>, p);
+  return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT, false>, p);
 }
 
-// CTAs of the kernel that can be resident at once when launched as clusters of ks (index [MPAD class][ks]); filled by
-// PrepareInt8GemmTcKernels from the occupancy calculator, because clusters must fit inside a GPC and so do not always
-// reach all 148 SMs (clusters of 8 reach 120).
-int g_tc_slots[3][9];
+// CTAs of the kernel that can be resident at once when launched as clusters of ks (index [device][MPAD class][ks]);
+// filled per device by PrepareInt8GemmTcKernels from the occupancy calculator, because clusters must fit inside a GPC
+// and so do not always reach all 148 SMs (clusters of 8 reach 120).
+int g_tc_slots[kMaxDevices][3][9];
 
 template <int MPAD>
-void FillTcSlots(int cls)
+void FillTcSlots(int device, int cls)
 {
   for (int ks = 1; ks <= 8; ++ks) {
     cudaLaunchConfig_t cfg = {};
@@ -877,11 +626,11 @@ void FillTcSlots(int cls)
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, Int8GemmTcKernel<MPAD, float>, &cfg) != cudaSuccess || clusters <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, Int8GemmTcKernel<MPAD, float, true>, &cfg) != cudaSuccess || clusters <= 0) {
       cudaGetLastError();
       clusters = (ks <= 2 ? 148 : ks <= 4 ? 128 : 112) / ks;  // a cautious guess when the query is not available
     }
-    g_tc_slots[cls][ks] = clusters * ks;
+    g_tc_slots[device][cls][ks] = clusters * ks;
   }
 }
 
@@ -903,11 +652,13 @@ int ChooseTcSlices(int k, int n, int mpad, double* cost_out = nullptr)
   }
   if (forced >= 1 && forced <= 8) return forced;
   const int cls = mpad <= 32 ? 0 : mpad <= 64 ? 1 : 2;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) device = 0;
   int best = 1;
   double best_cost = 1e30;
   for (int ks = 1; ks <= 8; ++ks) {
     if (ks > 1 && nb / ks < 4) break;
-    const int slots = g_tc_slots[cls][ks] > 0 ? g_tc_slots[cls][ks] : 148 / ks * ks;
+    const int slots = g_tc_slots[device][cls][ks] > 0 ? g_tc_slots[device][cls][ks] : 148 / ks * ks;
     const int waves = (tiles * ks + slots - 1) / slots;
     const double per_cta = (nb + ks - 1) / ks + 10.0 + (ks > 1 ? 8.0 + 1.5 * ks : 0.0);
     const double cost = waves * per_cta;
@@ -933,105 +684,56 @@ cudaError_t LaunchTcRows(const TcParams& p, int rows, cudaStream_t st)
 
 cudaError_t PrepareInt8GemmTcKernels()
 {
-  static std::mutex mu;
-  static bool done = false;
-  std::lock_guard<std::mutex> lock(mu);
-  if (done) return cudaSuccess;
-  cudaError_t e = PrepareTc<32, float>();
-  if (e == cudaSuccess) e = PrepareTc<32, __nv_bfloat16>();
-  if (e == cudaSuccess) e = PrepareTc<64, float>();
-  if (e == cudaSuccess) e = PrepareTc<64, __nv_bfloat16>();
-  if (e == cudaSuccess) e = PrepareTc<128, float>();
-  if (e == cudaSuccess) e = PrepareTc<128, __nv_bfloat16>();
-  if (e == cudaSuccess) e = PrepareTc<256, float>();
-  if (e == cudaSuccess) e = PrepareTc<256, __nv_bfloat16>();
-  if (e == cudaSuccess) {
-    FillTcSlots<32>(0);
-    FillTcSlots<64>(1);
-    FillTcSlots<128>(2);
-    done = true;
-  }
-  return e;
+  static OncePerDevice once;
+  return once.Run([](int device) {
+    cudaError_t e = PrepareTc<32, float>();
+    if (e == cudaSuccess) e = PrepareTc<32, __nv_bfloat16>();
+    if (e == cudaSuccess) e = PrepareTc<64, float>();
+    if (e == cudaSuccess) e = PrepareTc<64, __nv_bfloat16>();
+    if (e == cudaSuccess) e = PrepareTc<128, float>();
+    if (e == cudaSuccess) e = PrepareTc<128, __nv_bfloat16>();
+    if (e == cudaSuccess) e = PrepareTc<256, float>();
+    if (e == cudaSuccess) e = PrepareTc<256, __nv_bfloat16>();
+    if (e == cudaSuccess) {
+      FillTcSlots<32>(device, 0);
+      FillTcSlots<64>(device, 1);
+      FillTcSlots<128>(device, 2);
+    }
+    return e;
+  });
 }
 
 // Rows [0, m) of the projection on the tensor-core kernel, at most 256 rows per launch.  x is bf16.
-// Bytes of caller scratch the evenly spread ("stream-K") launch needs: one partial tile and one flag per CTA.
-size_t TcStreamScratchBytes() { return kTcMaxCtas * (kTcSlotFloats * sizeof(float) + sizeof(unsigned long long)); }
-
 cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const float* scales, const float* residual,
-                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches, bool weights_const,
-                             void* stream_scratch, size_t stream_scratch_bytes)
+                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches, bool weights_const)
 {
-  // $TLALOC_B200_GEMM_STREAMK: 2 = the evenly spread launch whenever the scratch allows, 1 = when the model prices it
-  // lower, otherwise (the default) never: as measured it is exact but slower than the cluster split (57344 x 8192 at 128
-  // rows: 156 vs 149 us; 8192 x 8192: 51 vs 30 us), its segment hand-overs and a hot loop at the register cap costing
-  // more than the partly empty waves it removes.
-  static const int stream_mode = [] {
-    const char* e = std::getenv("TLALOC_B200_GEMM_STREAMK");
-    return e != nullptr ? std::atoi(e) : 0;
-  }();
-  // Unique per launch and unlikely to equal anything a recycled scratch buffer holds: a flag left by another launch
-  // (or another process) must never read as this launch's.
-  static std::atomic<unsigned long long> epoch{[] {
-    std::random_device rd;
-    return (static_cast<unsigned long long>(rd()) << 32) ^ rd() ^ 0x9E3779B97F4A7C15ull;
-  }()};
   TcParams p;
   p.weights_const = weights_const ? 1 : 0;
+  p.prefetch = TcPrefetchDistance();
   p.w = codes;
   p.scales = scales;
   p.K = k;
   p.N = n;
   const size_t ybytes = DtypeBytes(y_dtype);
-  const int tiles = (n + kTcBN - 1) / kTcBN, nb = (k + kTcBK - 1) / kTcBK;
-  const bool stream_fits = stream_scratch != nullptr && stream_scratch_bytes >= TcStreamScratchBytes() &&
-                           (reinterpret_cast<uintptr_t>(stream_scratch) & 15) == 0;
+  const int nb = (k + kTcBK - 1) / kTcBK;
   for (int m0 = 0; m0 < m;) {
     int rows = std::min(256, m - m0);
-    double c256 = 0.0, c128 = 0.0;
-    ChooseTcSlices(k, n, 128, &c128);
     if (rows > 128) {
       // Two accumulators share one pass over the weights but cannot split K; with few column tiles two passes of 128
       // rows, each split over K, keep more SMs busy.
+      double c256 = 0.0, c128 = 0.0;
+      ChooseTcSlices(k, n, 128, &c128);
       ChooseTcSlices(k, n, 256, &c256);
       if (2.0 * c128 < c256) rows = 128;
     }
-    // The evenly spread launch: every CTA gets total / ctas blocks; about ten blocks of fixed cost as above plus about
-    // ten for the extra epilogue and the hand-over of partial tiles.
-    const long long total = static_cast<long long>(tiles) * nb;
-    const int ctas = static_cast<int>(std::min<long long>(kTcMaxCtas, std::max<long long>(1, total / 4)));
-    const double c_stream = static_cast<double>((total + ctas - 1) / ctas) + 20.0;
-    const bool use_stream = stream_fits && stream_mode != 0 && total < (1ll << 30) &&
-                            (stream_mode == 2 || c_stream < 0.95 * (rows > 128 ? c256 / 2.0 : c128));
-    if (use_stream && rows > 128) rows = 128;
     const int mpad = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
-    cudaError_t e;
-    if (use_stream) {
-      TcStreamParams sp;
-      sp.x = x + static_cast<size_t>(m0) * k;
-      sp.w = codes;
-      sp.scales = scales;
-      sp.residual = residual ? residual + static_cast<size_t>(m0) * n : nullptr;
-      sp.y = static_cast<unsigned char*>(y) + static_cast<size_t>(m0) * n * ybytes;
-      sp.slots = static_cast<float*>(stream_scratch);
-      sp.flags = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(stream_scratch) + kTcMaxCtas * kTcSlotFloats * sizeof(float));
-      sp.epoch = epoch.fetch_add(1, std::memory_order_relaxed);
-      sp.M = rows;
-      sp.K = k;
-      sp.N = n;
-      sp.nb = nb;
-      sp.total = static_cast<int>(total);
-      sp.weights_const = p.weights_const;
-      e = y_dtype == TLALOC_B200_F32 ? LaunchTcStreamRows<float>(sp, rows, ctas, st) : LaunchTcStreamRows<__nv_bfloat16>(sp, rows, ctas, st);
-    } else {
-      p.ks = ChooseTcSlices(k, n, mpad);
-      p.Kc = (nb + p.ks - 1) / p.ks * kTcBK;  // whole blocks per slice; trailing slices may be empty
-      p.M = rows;
-      p.x = x + static_cast<size_t>(m0) * k;
-      p.residual = residual ? residual + static_cast<size_t>(m0) * n : nullptr;
-      p.y = static_cast<unsigned char*>(y) + static_cast<size_t>(m0) * n * ybytes;
-      e = y_dtype == TLALOC_B200_F32 ? LaunchTcRows<float>(p, rows, st) : LaunchTcRows<__nv_bfloat16>(p, rows, st);
-    }
+    p.ks = ChooseTcSlices(k, n, mpad);
+    p.Kc = (nb + p.ks - 1) / p.ks * kTcBK;  // whole blocks per slice; trailing slices may be empty
+    p.M = rows;
+    p.x = x + static_cast<size_t>(m0) * k;
+    p.residual = residual ? residual + static_cast<size_t>(m0) * n : nullptr;
+    p.y = static_cast<unsigned char*>(y) + static_cast<size_t>(m0) * n * ybytes;
+    const cudaError_t e = y_dtype == TLALOC_B200_F32 ? LaunchTcRows<float>(p, rows, st) : LaunchTcRows<__nv_bfloat16>(p, rows, st);
     if (e != cudaSuccess) return e;
     ++*launches;
     m0 += rows;

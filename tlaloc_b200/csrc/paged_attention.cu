@@ -703,6 +703,97 @@ __global__ void __launch_bounds__(kCombineThreads) PaCombine(PaParams p)
 }
 
 // ------------------------------------------------------------------------------------------
+// Parity mode: the interpreter's own walk (DxirInterpreter.kt:2049-2140).  One CTA per (row, head): every score is a
+// double dot over the head dimension in ascending order times the scale; the denominator is summed in position order
+// by one thread; channel j accumulates (e / denom) * v in double over the positions in ascending order, multiply and
+// add rounded separately; one narrowing to f32 at the end.  The scores of the whole row sit in shared memory.
+
+constexpr int kFaithfulThreads = 256;
+constexpr int kFaithfulMaxCtx = 5632;  // doubles that fit the default 48 KB of dynamic shared memory, less the rest
+
+template <typename QT, typename KVT, typename OT>
+__global__ void __launch_bounds__(kFaithfulThreads) PaOrderFaithful(PaParams p)
+{
+  GridDependencySync();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  double* scores = reinterpret_cast<double*>(smem_raw);
+  __shared__ double red[kFaithfulThreads / 32];
+  __shared__ double s_mx, s_denom;
+  const int rh = blockIdx.x, row = rh / p.H, head = rh - row * p.H;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int D = p.D, ctx = p.M * p.bs, kv = head / p.group, tb = row / p.rpt;
+  const int len = ClampI(__ldg(p.lens + row), 0, ctx);
+  const int first = p.window > 0 ? max(0, len - p.window) : 0;
+  const QT* q = static_cast<const QT*>(p.q) + static_cast<size_t>(rh) * D;
+  const KVT* kc = static_cast<const KVT*>(p.kc);
+  const KVT* vc = static_cast<const KVT*>(p.vc);
+  OT* out = static_cast<OT*>(p.out) + static_cast<size_t>(rh) * D;
+  const double scale = static_cast<double>(p.scale);
+  auto offset = [&](int t) {
+    const int blk = ClampI(__ldg(p.tables + static_cast<size_t>(tb) * p.M + t / p.bs), 0, p.P - 1);
+    return ((static_cast<size_t>(blk) * p.bs + t % p.bs) * p.Hkv + kv) * D;
+  };
+  double mx = -INFINITY;
+  for (int t = first + tid; t < len; t += kFaithfulThreads) {
+    double sc = -INFINITY;
+    if (Kept(p, row, t)) {
+      const KVT* kr = kc + offset(t);
+      double dot = 0.0;
+      for (int j = 0; j < D; ++j) dot = __dadd_rn(dot, __dmul_rn(static_cast<double>(ToF32(q[j])), static_cast<double>(ToF32(kr[j]))));
+      sc = __dmul_rn(dot, scale);
+      mx = fmax(mx, sc);
+    }
+    scores[t - first] = sc;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    double m = red[0];
+    for (int w = 1; w < kFaithfulThreads / 32; ++w) m = fmax(m, red[w]);
+    s_mx = m;
+  }
+  __syncthreads();
+  mx = s_mx;
+  for (int t = first + tid; t < len; t += kFaithfulThreads) {
+    const double sc = scores[t - first];
+    scores[t - first] = sc == -INFINITY ? 0.0 : exp(sc - mx);  // a masked position weighs nothing
+  }
+  __syncthreads();
+  if (tid == 0) {
+    double denom = 0.0;
+    for (int t = first; t < len; ++t)
+      if (Kept(p, row, t)) denom = __dadd_rn(denom, scores[t - first]);
+    s_denom = denom;
+  }
+  __syncthreads();
+  const double denom = s_denom;
+  const bool empty = len <= first || mx == -INFINITY || denom == 0.0;
+  for (int j = tid; j < D; j += kFaithfulThreads) {
+    double acc = 0.0;
+    if (!empty) {
+      for (int t = first; t < len; ++t) {
+        if (!Kept(p, row, t)) continue;
+        const double w = scores[t - first] / denom;
+        acc = __dadd_rn(acc, __dmul_rn(w, static_cast<double>(ToF32(vc[offset(t) + j]))));
+      }
+    }
+    out[j] = FromF32<OT>(static_cast<float>(acc));
+  }
+  if (tid == 0 && p.lse != nullptr) p.lse[rh] = empty ? -INFINITY : static_cast<float>(mx + log(denom));
+}
+
+template <typename QT, typename KVT>
+cudaError_t LaunchFaithful(const PaParams& p, int out_dtype, int span, cudaStream_t st)
+{
+  const size_t smem = sizeof(double) * static_cast<size_t>(span > 0 ? span : 1);
+  const unsigned grid = static_cast<unsigned>(p.R * p.H);
+  if (out_dtype == TLALOC_B200_F32) return LaunchChained(PaOrderFaithful<QT, KVT, float>, grid, kFaithfulThreads, smem, st, p);
+  return LaunchChained(PaOrderFaithful<QT, KVT, __nv_bfloat16>, grid, kFaithfulThreads, smem, st, p);
+}
+
+// ------------------------------------------------------------------------------------------
 // KV_CACHE_WRITE: one CTA per token row.
 
 template <typename PT, typename NT>
@@ -806,16 +897,14 @@ int PreferredSlice(int ctx, long long pairs)
 
 cudaError_t PreparePagedAttentionKernels()
 {
-  static std::mutex mu;
-  static bool done = false;
-  std::lock_guard<std::mutex> lock(mu);
-  if (done) return cudaSuccess;
-  cudaError_t e = PrepareMma<__nv_bfloat16, 64>();
-  if (e == cudaSuccess) e = PrepareMma<__nv_bfloat16, 128>();
-  if (e == cudaSuccess) e = PrepareMma<float, 64>();
-  if (e == cudaSuccess) e = PrepareMma<float, 128>();
-  if (e == cudaSuccess) done = true;
-  return e;
+  static OncePerDevice once;
+  return once.Run([](int) {
+    cudaError_t e = PrepareMma<__nv_bfloat16, 64>();
+    if (e == cudaSuccess) e = PrepareMma<__nv_bfloat16, 128>();
+    if (e == cudaSuccess) e = PrepareMma<float, 64>();
+    if (e == cudaSuccess) e = PrepareMma<float, 128>();
+    return e;
+  });
 }
 
 }  // namespace tlaloc_b200
@@ -914,8 +1003,26 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
   p.scale = scale;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (OrderFaithful()) {  // parity mode: the interpreter's walk, straight into out (no slices, no scratch use)
+    const int span = sliding_window > 0 ? std::min(sliding_window, ctx) : ctx;
+    if (span > kFaithfulMaxCtx) {
+      return Fail(kUnsupported, "%s: parity mode holds a row's scores on chip, at most %d positions (got %d)", op, kFaithfulMaxCtx, span);
+    }
+    p.slice = ctx;
+    p.S = 1;
+    cudaError_t fe;
+    if (q_dtype == TLALOC_B200_F32 && kv_dtype == TLALOC_B200_F32) fe = LaunchFaithful<float, float>(p, out_dtype, span, st);
+    else if (q_dtype == TLALOC_B200_F32) fe = LaunchFaithful<float, __nv_bfloat16>(p, out_dtype, span, st);
+    else if (kv_dtype == TLALOC_B200_F32) fe = LaunchFaithful<__nv_bfloat16, float>(p, out_dtype, span, st);
+    else fe = LaunchFaithful<__nv_bfloat16, __nv_bfloat16>(p, out_dtype, span, st);
+    if (fe != cudaSuccess) return CudaFail("PAGED_ATTENTION parity-mode launch", fe);
+    CountLaunches(1);
+    return kOk;
+  }
+  // The tensor-core kernel copies K/V rows in 16-byte pieces: pools that start off a 16-byte boundary (a slice of a
+  // larger allocation at an odd element) take the generic kernel, which has no alignment needs.
   const bool mma = kv_dtype == TLALOC_B200_BF16 && (head_dim == 64 || head_dim == 128) && p.NQ <= kMmaQ &&
-                   keep == nullptr && block_size >= 8;
+                   keep == nullptr && block_size >= 8 && Aligned16(key_cache) && Aligned16(value_cache);
   // Slice length: the preferred one (tensor-core kernel) or 256, stretched until `splits` slices cover the context.
   int slice = mma ? PreferredSlice(ctx, static_cast<long long>(num_tables) * num_kv_heads) : 256;
   if (static_cast<int64_t>(slice) * splits < ctx) slice = (ctx + splits - 1) / splits;
@@ -1004,7 +1111,6 @@ namespace {
 constexpr size_t kStaticScratchBytes = size_t(16) << 20;  // 16 MiB on every GPU that loads the library, until exit
 static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
 
-constexpr int kMaxDevices = 64;
 std::mutex g_static_mu;
 float* g_static_ptr[kMaxDevices] = {nullptr};
 

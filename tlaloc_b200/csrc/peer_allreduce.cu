@@ -30,7 +30,7 @@ namespace {
 
 constexpr int kMaxRanks = TLALOC_B200_MAX_PEERS;
 constexpr int kThreads = 512;
-constexpr unsigned long long kWaitNs = 20ull * 1000ull * 1000ull * 1000ull;  // 20 s: a rank may still be loading weights
+constexpr unsigned long long kDefaultWaitNs = 20ull * 1000ull * 1000ull * 1000ull;  // 20 s: a rank may still be loading weights
 
 struct PeerTable
 {
@@ -65,20 +65,26 @@ __device__ __forceinline__ unsigned long long NowNs()
 }
 
 // Thread `q` (< world) waits until rank q's flag of this phase reaches `epoch`.  Returns false when time ran out.
-__device__ __forceinline__ bool WaitFlag(const uint32_t* flag, uint32_t epoch)
+__device__ __forceinline__ bool WaitFlag(const uint32_t* flag, uint32_t epoch, unsigned long long limit_ns)
 {
   if (static_cast<int32_t>(LoadFlag(flag) - epoch) >= 0) return true;
   const unsigned long long t0 = NowNs();
   for (;;) {
     for (int i = 0; i < 64; ++i)
       if (static_cast<int32_t>(LoadFlag(flag) - epoch) >= 0) return true;
-    if (NowNs() - t0 > kWaitNs) return false;
+    if (NowNs() - t0 > limit_ns) return false;
     __nanosleep(200);
   }
 }
+// The wait limit: state[3] microseconds when the caller set it, else 20 s.
+__device__ __forceinline__ unsigned long long WaitLimitNs(const uint32_t* state)
+{
+  const uint32_t us = reinterpret_cast<const volatile uint32_t*>(state)[3];
+  return us != 0 ? 1000ull * us : kDefaultWaitNs;
+}
 
 // state[0] = epoch of the last finished all-reduce, state[1] = CTAs finished in this launch, state[2] = status
-// (0 ok, else 1 + 16 * phase + the rank that never arrived).
+// (0 ok, else 1 + 16 * phase + the rank that never arrived), state[3] = wait limit in microseconds (0 = 20 s).
 template <int W>
 __global__ void __launch_bounds__(kThreads, 1) PeerAllReduceKernel(PeerTable t, uint32_t* state, int rank, int world_rt, size_t n4)
 {
@@ -94,12 +100,13 @@ __global__ void __launch_bounds__(kThreads, 1) PeerAllReduceKernel(PeerTable t, 
   __syncthreads();
   const uint32_t epoch = s_epoch;
   const bool dead = s_dead != 0;
+  const unsigned long long limit_ns = WaitLimitNs(state);
 
   // 1. arrive.  The producing kernel has completed (stream order), so its writes are already in this GPU's L2, which
   // is where a peer's loads are served from: the flag needs no fence of its own.
   if (blockIdx.x == 0 && tid < world) StoreFlag(t.flags[tid] + rank, epoch);
   if (!dead && tid < world) {
-    if (!WaitFlag(t.flags[rank] + tid, epoch)) atomicCAS(state + 2, 0u, 1u + tid);
+    if (!WaitFlag(t.flags[rank] + tid, epoch, limit_ns)) atomicCAS(state + 2, 0u, 1u + tid);
   }
   __syncthreads();
 
@@ -132,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1) PeerAllReduceKernel(PeerTable t, 
   if (tid < world) {
     __threadfence_system();
     StoreFlag(t.flags[tid] + world + rank, epoch);
-    if (!dead && !WaitFlag(t.flags[rank] + world + tid, epoch)) atomicCAS(state + 2, 0u, 17u + tid);
+    if (!dead && !WaitFlag(t.flags[rank] + world + tid, epoch, limit_ns)) atomicCAS(state + 2, 0u, 17u + tid);
   }
   __syncthreads();
   if (tid == 0) {
@@ -192,9 +199,10 @@ PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, flo
   __syncthreads();
   const uint32_t epoch = s_epoch;
   const bool dead = s_dead != 0;
+  const unsigned long long limit_ns = WaitLimitNs(state);
   if (blockIdx.x == 0 && blockIdx.y == 0 && tid < world) StoreFlag(t.flags[tid] + rank, epoch);
   if (!dead && tid < world) {
-    if (!WaitFlag(t.flags[rank] + tid, epoch)) atomicCAS(state + 2, 0u, 1u + tid);
+    if (!WaitFlag(t.flags[rank] + tid, epoch, limit_ns)) atomicCAS(state + 2, 0u, 1u + tid);
   }
   __syncthreads();
 
@@ -268,7 +276,7 @@ PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, flo
   if (tid < world) {
     __threadfence_system();
     StoreFlag(t.flags[tid] + world + rank, epoch);
-    if (!dead && !WaitFlag(t.flags[rank] + world + tid, epoch)) atomicCAS(state + 2, 0u, 17u + tid);
+    if (!dead && !WaitFlag(t.flags[rank] + world + tid, epoch, limit_ns)) atomicCAS(state + 2, 0u, 17u + tid);
   }
   __syncthreads();
   if (tid == 0) {

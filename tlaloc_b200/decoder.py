@@ -66,11 +66,15 @@ class Decoder:
     """Weights, KV pools and step buffers of one rank; `step()` runs one decode step for `batch` sequences."""
 
     def __init__(self, cfg: DecoderConfig, batch: int, num_blocks: int, max_blocks_per_seq: int, *, device="cuda:0",
-                 rank: int = 0, world: int = 1, group=None):
+                 rank: int = 0, world: int = 1, group=None, exact: bool = False):
+        """`exact`: every operator runs in the library's parity mode (the reference interpreter's own evaluation
+        order: order-faithful projections, double-precision attention walk, sequential RMSNorm sums, SiLU in
+        double).  Slow; its logits equal the CPU oracle's to the last bits and its greedy tokens are the oracle's."""
         if not torch.cuda.is_available():
             raise RuntimeError("tlaloc_b200.Decoder needs a CUDA device: there is no CPU path")
         sharding.check_world(cfg.num_heads, cfg.num_kv_heads, cfg.ffn, cfg.vocab, world)
         self.cfg, self.batch, self.device, self.rank, self.world, self.group = cfg, batch, torch.device(device), rank, world, group
+        self.exact = bool(exact)
         self.hq, self.hk, self.f = cfg.num_heads // world, cfg.num_kv_heads // world, cfg.ffn // world
         self.num_blocks, self.max_blocks = num_blocks, max_blocks_per_seq
         dev, B, d, hd = self.device, batch, cfg.d_model, cfg.head_dim
@@ -112,9 +116,6 @@ class Decoder:
         self.gu = torch.empty((B, 2 * self.f), **f32)
         self.act = torch.empty((B, self.f), **bf)
         self.logits = torch.empty((B, cfg.vocab // world), **f32)
-        # scratch of the projections (partial tiles of the evenly spread tensor-core launch); one buffer serves them all
-        kmax = max(d, self.hq * hd, self.f)
-        self.gemm_scratch = torch.empty((ops.int8_gemm_scratch_bytes(B, kmax, d) + 3) // 4, **f32)
         self.next_ids = torch.zeros((B,), **i32)
         self.best = torch.empty((B,), **f32)
         shape = ops.parse_paged_attention(self.q_rot, self.key_pools[0], self.value_pools[0], self.block_tables,
@@ -193,6 +194,15 @@ class Decoder:
             torch.distributed.all_reduce(x, group=self.group)
 
     def _run_step(self) -> None:
+        if not self.exact:
+            return self._launch_step()
+        before = ops.set_order_faithful(True)
+        try:
+            self._launch_step()
+        finally:
+            ops.set_order_faithful(before)
+
+    def _launch_step(self) -> None:
         cfg, B = self.cfg, self.batch
         hd, hq, hk = cfg.head_dim, self.hq, self.hk
         ops.embedding(self.embed, self.token_ids, out=self.h)
@@ -205,20 +215,20 @@ class Decoder:
         for l, lw in enumerate(self.layers):
             if l == 0 or not fused:
                 ops.rmsnorm(h, lw["ln1"], cfg.rms_eps, out=self.hn)
-            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True, scratch=self.gemm_scratch)
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True)
             ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
                               self.value_pools[l], q_out=self.q_rot)
             ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
                                 scale=cfg.scale, out=self.att, scratch=self.att_scratch)
-            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, weights_const=True, scratch=self.gemm_scratch)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, weights_const=True)
             if fused:
                 self.peer.all_reduce_norm_(1, lw["ln2"], cfg.rms_eps)
             else:
                 self._all_reduce(h2)
                 ops.rmsnorm(h2, lw["ln2"], cfg.rms_eps, out=self.hn)
-            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True, scratch=self.gemm_scratch)
+            self.gate_up_proj(lw)
             ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
-            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True, scratch=self.gemm_scratch)
+            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True)
             if fused:
                 nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
                 self.peer.all_reduce_norm_(0, nxt, cfg.rms_eps)
@@ -227,12 +237,16 @@ class Decoder:
         if not fused:
             ops.rmsnorm(h, self.final_norm, cfg.rms_eps, out=self.hn)
         if isinstance(self.head, tuple):
-            ops.int8_gemm(self.hn, *self.head, out=self.logits, weights_const=True, scratch=self.gemm_scratch)
+            ops.int8_gemm(self.hn, *self.head, out=self.logits, weights_const=True)
         else:
             self.logits.copy_(ops.dense_gemm_exact(self.hn, self.head))
         ops.argmax(self.logits, out=self.next_ids)
         if self.world > 1:
             self._merge_greedy()
+
+    def gate_up_proj(self, lw) -> None:
+        """The fused gate|up projection of one layer: normalised rows `hn` -> `gu` = [gate | up]."""
+        ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True)
 
     def _merge_greedy(self) -> None:
         """Each rank's best (logit, local id) -> the global greedy token on every rank (sharding.merge_greedy)."""

@@ -27,16 +27,37 @@ def _dev(*ts) -> None:
             raise ValueError("operands must be contiguous CUDA tensors (there is no CPU path)")
 
 
+def _out(name: str, t, shape, dtypes, like: torch.Tensor) -> None:
+    """A caller-supplied result or scratch tensor is written through its raw pointer: refuse one that is not exactly
+    the contiguous CUDA tensor of that shape the kernel will write."""
+    if t is None:
+        return
+    if not isinstance(dtypes, (tuple, list)):
+        dtypes = (dtypes,)
+    if (not t.is_cuda or not t.is_contiguous() or t.device != like.device or t.dtype not in dtypes
+            or (shape is not None and tuple(t.shape) != tuple(shape))):
+        want = "x".join(str(d) for d in shape) if shape is not None else "any shape"
+        raise ValueError(f"{name} must be a contiguous {'/'.join(str(d) for d in dtypes)} tensor [{want}] on {like.device}, "
+                         f"got {t.dtype} {tuple(t.shape)} on {t.device}")
+
+
 def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
-def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+def _stream(t: torch.Tensor) -> int:
+    """The current stream of the tensor's own device (not of whichever device happens to be current)."""
+    return torch.cuda.current_stream(t.device).cuda_stream
 
 
 def init() -> None:
+    """Kernel set-up for the current CUDA device (call once per device, before any graph capture)."""
     N.check(N.lib().tlaloc_b200_init())
+
+
+def set_order_faithful(on: bool) -> bool:
+    """Parity mode of the whole library (tlaloc_b200_set_order_faithful); returns the previous setting."""
+    return bool(N.lib().tlaloc_b200_set_order_faithful(1 if on else 0))
 
 
 def paged_attention_scratch(shape: PagedAttentionShape, device, splits: int | None = None) -> torch.Tensor:
@@ -60,12 +81,16 @@ def paged_attention(query, key_cache, value_cache, block_tables, seq_lens, *, sc
         out = torch.empty_like(query)
     if scratch is None:
         scratch = paged_attention_scratch(p, query.device)
+    _out("PAGED_ATTENTION out", out, (p.num_seqs, p.num_heads, p.head_dim), (torch.float32, torch.bfloat16), query)
+    if scratch.dim() != 4 or scratch.shape[0] < 1:
+        raise ValueError("PAGED_ATTENTION scratch must be f32 [S, R, H, D + 2] with S >= 1")
+    _out("PAGED_ATTENTION scratch", scratch, (scratch.shape[0], p.num_seqs, p.num_heads, p.head_dim + 2), torch.float32, query)
     lse = torch.empty((p.num_seqs, p.num_heads), dtype=torch.float32, device=query.device) if return_lse else None
     N.check(N.lib().tlaloc_b200_paged_attention(
         _ptr(query), _dt(query), _ptr(key_cache), _ptr(value_cache), _dt(key_cache), _ptr(block_tables),
         _ptr(seq_lens), _ptr(keep), 0 if keep is None else keep.shape[1], _ptr(out), _dt(out), _ptr(lse),
         _ptr(scratch), scratch.shape[0], p.num_seqs, p.num_heads, p.head_dim, p.num_blocks, p.block_size,
-        p.num_kv_heads, p.max_blocks_per_seq, p.num_tables, float(scale), int(sliding_window or 0), _stream()))
+        p.num_kv_heads, p.max_blocks_per_seq, p.num_tables, float(scale), int(sliding_window or 0), _stream(query)))
     return (out, lse) if return_lse else out
 
 
@@ -77,7 +102,7 @@ def kv_cache_write(pool, new_kv, slot_mapping):
     if new_kv.numel() != T * Hkv * D:
         raise ValueError(f"KV_CACHE_WRITE: newKv must be [T, {Hkv}, {D}] for the pool, got {tuple(new_kv.shape)}")
     N.check(N.lib().tlaloc_b200_kv_cache_write(_ptr(pool), _dt(pool), _ptr(new_kv), _dt(new_kv), _ptr(slot_mapping), T,
-                                               Hkv * D, P * bs, _stream()))
+                                               Hkv * D, P * bs, _stream(pool)))
     return pool
 
 
@@ -92,15 +117,17 @@ def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.floa
         raise ValueError(f"INT8_PROJ: x [M, K] x codes int8 [K, N] with scales [N]; got {tuple(x.shape)}, {tuple(codes.shape)}")
     if out is None:
         out = torch.empty((M, Nn), dtype=out_dtype, device=x.device)
-    if scratch is None and not exact and (x.dtype == torch.float32 or M > 32):
-        # an f32 x is cast to bf16 there; batches of rows also use it to spread their blocks evenly over the SMs
+    _out("INT8_PROJ out", out, (M, Nn), (torch.float32, torch.bfloat16), x)
+    _out("INT8_PROJ residual", residual, (M, Nn), torch.float32, x)
+    if scratch is None and not exact and x.dtype == torch.float32:  # an f32 x is cast to bf16 there
         scratch = torch.empty((N.lib().tlaloc_b200_int8_gemm_scratch_bytes(M, K, Nn) + 3) // 4, dtype=torch.float32,
                               device=x.device)
+    _out("INT8_PROJ scratch", scratch, None, torch.float32, x)
     flags = ((N.GEMM_EXACT if exact else 0) | (N.GEMM_X_F32_EXACT if x_f32_exact else 0)
              | (N.GEMM_WEIGHTS_CONST if weights_const else 0))
     N.check(N.lib().tlaloc_b200_int8_gemm(_ptr(x), _dt(x), _ptr(codes), _ptr(scales), _ptr(residual), _ptr(out), _dt(out),
                                           _ptr(scratch), 0 if scratch is None else scratch.numel() * 4, M, K, Nn, flags,
-                                          _stream()))
+                                          _stream(x)))
     return out
 
 
@@ -114,7 +141,7 @@ def dense_gemm_exact(x, w, *, x_f32_exact=False):
     M, K = x.shape
     out = torch.empty((M, w.shape[1]), dtype=torch.float32, device=x.device)
     N.check(N.lib().tlaloc_b200_dense_gemm_exact(_ptr(x), _dt(x), _ptr(w), _dt(w), _ptr(out), M, K, w.shape[1],
-                                                 N.GEMM_X_F32_EXACT if x_f32_exact else 0, _stream()))
+                                                 N.GEMM_X_F32_EXACT if x_f32_exact else 0, _stream(x)))
     return out
 
 
@@ -123,8 +150,9 @@ def embedding(table, ids, *, out=None):
     ids = ids.reshape(-1)
     if out is None:
         out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+    _out("EMBEDDING out", out, (ids.shape[0], table.shape[1]), torch.float32, table)
     N.check(N.lib().tlaloc_b200_embedding(_ptr(table), _dt(table), _ptr(ids), _ptr(out), ids.shape[0], table.shape[0],
-                                          table.shape[1], _stream()))
+                                          table.shape[1], _stream(table)))
     return out
 
 
@@ -133,7 +161,8 @@ def rmsnorm(x, gain, eps, *, out=None, out_dtype=torch.float32):
     rows, n = x.shape
     if out is None:
         out = torch.empty((rows, n), dtype=out_dtype, device=x.device)
-    N.check(N.lib().tlaloc_b200_rmsnorm(_ptr(x), _ptr(gain), _ptr(out), _dt(out), rows, n, float(eps), _stream()))
+    _out("RMSNORM out", out, (rows, n), (torch.float32, torch.bfloat16), x)
+    N.check(N.lib().tlaloc_b200_rmsnorm(_ptr(x), _ptr(gain), _ptr(out), _dt(out), rows, n, float(eps), _stream(x)))
     return out
 
 
@@ -149,10 +178,11 @@ def rope_kv_write(q, k, v, positions, cos_table, sin_table, slot_mapping, key_ca
     P, bs = key_cache.shape[0], key_cache.shape[1]
     if q_out is None:
         q_out = torch.empty((T, H, hd), dtype=q_dtype, device=q.device)
+    _out("ROPE_KV_WRITE q_out", q_out, (T, H, hd), (torch.float32, torch.bfloat16), q)
     N.check(N.lib().tlaloc_b200_rope_kv_write(_ptr(q), _ptr(k), _ptr(v), _ptr(positions), _ptr(cos_table), _ptr(sin_table),
                                               _ptr(slot_mapping), _ptr(q_out), _dt(q_out), _ptr(key_cache),
                                               _ptr(value_cache), _dt(key_cache), T, H, Hkv, hd, P * bs,
-                                              cos_table.shape[0], q.stride(0), k.stride(0), v.stride(0), _stream()))
+                                              cos_table.shape[0], q.stride(0), k.stride(0), v.stride(0), _stream(q)))
     return q_out
 
 
@@ -163,7 +193,8 @@ def swiglu(gate, up, *, out=None, out_dtype=torch.float32):
     rows, n = gate.shape
     if out is None:
         out = torch.empty((rows, n), dtype=out_dtype, device=gate.device)
-    N.check(N.lib().tlaloc_b200_swiglu(_ptr(gate), _ptr(up), gate.stride(0), _ptr(out), _dt(out), rows, n, _stream()))
+    _out("SWIGLU out", out, (rows, n), (torch.float32, torch.bfloat16), gate)
+    N.check(N.lib().tlaloc_b200_swiglu(_ptr(gate), _ptr(up), gate.stride(0), _ptr(out), _dt(out), rows, n, _stream(gate)))
     return out
 
 
@@ -172,5 +203,6 @@ def argmax(logits, out=None):
     rows, n = logits.shape
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    N.check(N.lib().tlaloc_b200_argmax(_ptr(logits), _ptr(out), rows, n, _stream()))
+    _out("ARGMAX out", out, (rows,), torch.int32, logits)
+    N.check(N.lib().tlaloc_b200_argmax(_ptr(logits), _ptr(out), rows, n, _stream(logits)))
     return out

@@ -133,12 +133,16 @@ def make_tables(rng, batch, lens, block_size, num_blocks, max_blocks, steps_ahea
 
 
 def fill_normal_bf16(torch, pool, gen):
-    """N(0, 1) into a (possibly huge) bf16 tensor, piece by piece to bound the f32 temporaries."""
+    """N(0, 1) into a (possibly huge) bf16 or e4m3fn tensor, piece by piece to bound the f32 temporaries."""
     flat = pool.view(-1)
     step = 1 << 28
     for o in range(0, flat.numel(), step):
         n = min(step, flat.numel() - o)
-        flat[o:o + n] = torch.randn((n,), device=pool.device, generator=gen, dtype=torch.float32).to(torch.bfloat16)
+        flat[o:o + n].copy_(torch.randn((n,), device=pool.device, generator=gen, dtype=torch.float32).to(pool.dtype))
+
+
+def kv_torch_dtype(torch, kv: str):
+    return {"bf16": torch.bfloat16, "e4m3": torch.float8_e4m3fn}[kv]
 
 
 def workload_config(wl_name, batch, layers, world, extra=None) -> dict:
@@ -151,7 +155,7 @@ def workload_config(wl_name, batch, layers, world, extra=None) -> dict:
 class StepBench:
     """One decoder of a named workload on this rank with synthetic weights, pools and inputs, and its timings."""
 
-    def __init__(self, torch, workload, K, W, *, dev, rank=0, world=1, group=None, layers=0):
+    def __init__(self, torch, workload, K, W, *, dev, rank=0, world=1, group=None, layers=0, kv="bf16"):
         from tlaloc_b200 import _native
         from tlaloc_b200 import decoder as D
         from tlaloc_b200 import sharding
@@ -165,11 +169,12 @@ class StepBench:
         self.lens0 = rng.integers(lo, hi + 1, size=batch).astype(np.int64)
         steps_ahead = 2 * (K + W) + 8
         self.max_blocks = (hi + steps_ahead + BS - 1) // BS + 1
-        cfg = self.cfg = D.DecoderConfig(**cfg_kw, kv_dtype=torch.bfloat16, head_quant=True, max_positions=self.max_blocks * BS)
+        self.kv, self.kv_bytes = kv, (2 if kv == "bf16" else 1)
+        cfg = self.cfg = D.DecoderConfig(**cfg_kw, kv_dtype=kv_torch_dtype(torch, kv), head_quant=True, max_positions=self.max_blocks * BS)
         # Size the KV pool: all logical blocks when they fit beside the weights, else what the memory budget allows
         # (then block tables alias physical blocks across sequences; logical bytes are what the step reads).
         self.hk = cfg.num_kv_heads // world
-        block_bytes = 2 * BS * self.hk * cfg.head_dim * 2 * cfg.num_layers  # K and V, all layers
+        block_bytes = 2 * BS * self.hk * cfg.head_dim * self.kv_bytes * cfg.num_layers  # K and V, all layers
         self.logical_blocks = int(np.sum((self.lens0 + BS - 1) // BS)) + batch * 4 + 64
         free, total = torch.cuda.mem_get_info(dev)
         per_layer_w = cfg.d_model * (cfg.num_heads + 2 * cfg.num_kv_heads) * cfg.head_dim + cfg.num_heads * cfg.head_dim * cfg.d_model \
@@ -267,7 +272,7 @@ class StepBench:
 
         torch, dec, cfg, dev, batch, hk = self.torch, self.dec, self.cfg, self.dev, self.batch, self.hk
         lens_now = (self.lens0 + 1).astype(np.int64)
-        att_bytes = 2 * int(lens_now.sum()) * hk * cfg.head_dim * 2 + 2 * batch * (cfg.num_heads // self.world) * cfg.head_dim * 3
+        att_bytes = 2 * int(lens_now.sum()) * hk * cfg.head_dim * self.kv_bytes + 2 * batch * (cfg.num_heads // self.world) * cfg.head_dim * 3
         reps = 20
         dec.set_inputs(*self.stage(0))
         torch.cuda.synchronize(dev)
@@ -296,7 +301,7 @@ class StepBench:
         for i in range(batch):
             own_tables[i, :need[i]] = perm[o:o + need[i]]
             o += int(need[i])
-        roof_k = torch.empty((own_blocks, BS, hk, cfg.head_dim), dtype=torch.bfloat16, device=dev)
+        roof_k = torch.empty((own_blocks, BS, hk, cfg.head_dim), dtype=cfg.kv_dtype, device=dev)
         roof_v = torch.empty_like(roof_k)
         fill_normal_bf16(torch, roof_k, self.gen)
         fill_normal_bf16(torch, roof_v, self.gen)
@@ -307,11 +312,11 @@ class StepBench:
         try:
             with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
                 per_pos = json.load(f).get("paged_attention_dram_bytes_per_position_per_kv_head")
-                if per_pos:
+                if per_pos and self.kv == "bf16":
                     traffic = float(per_pos) * int(lens_now.sum()) * hk
         except Exception:
             pass
-        return {"kernel": "PaSliceMma+PaCombine", "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+        return {"kernel": ("PaSliceMma" if self.kv == "bf16" else "PaSliceMmaF8") + "+PaCombine", "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / pk["hbm_gbs"], "traffic": traffic, "peak_kind": pk["kind"], "bytes_per_launch": att_bytes,
                 "ms_per_launch": att_ms, "pool": "one block per (sequence, 16 positions): nothing shared",
                 "in_step_pools": {"ms_per_launch": in_step_ms, "logical_gbs": att_bytes / (in_step_ms / 1e3) / 1e9,
@@ -496,7 +501,8 @@ def run_ours(args) -> dict:
             os._exit(3)
 
     pk = peaks()
-    sb = StepBench(torch, args.workload, args.steps, args.warmup, dev=dev, rank=rank, world=world, group=group, layers=args.layers)
+    sb = StepBench(torch, args.workload, args.steps, args.warmup, dev=dev, rank=rank, world=world, group=group, layers=args.layers,
+                   kv=args.kv)
     cfg, batch, dec = sb.cfg, sb.batch, sb.dec
     if args.timeline:
         return {"timeline": sb.timeline(), "config": workload_config(sb.wl_name, batch, cfg.num_layers, world)}
@@ -509,11 +515,11 @@ def run_ours(args) -> dict:
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "int8 weights x bf16, f32 accumulate; bf16 KV", "data": "synthetic",
+        "dtype": f"int8 weights x bf16, f32 accumulate; {'bf16' if args.kv == 'bf16' else 'f8e4m3fn'} KV", "data": "synthetic",
         "config": workload_config(sb.wl_name, batch, cfg.num_layers, world, {
             "mean_context": float(lens_now.mean()), "kv_blocks_per_layer": sb.num_blocks,
             "kv_blocks_logical": sb.logical_blocks, "kv_aliased": bool(sb.aliased),
-            "l2": "inputs larger than L2 (weights and KV pools are tens of GB)", "head": "int8 (headQuant)"}),
+            "l2": "inputs larger than L2 (weights and KV pools are tens of GB)", "head": "int8 (headQuant)", "kv": args.kv}),
         "e2e": e2e, "gpu_launches": int(sb.launches_per_step * args.steps), "launches_per_step": int(sb.launches_per_step),
         "clocks": clocks, "roofline": roofline,
         "step_hbm": {"weights_bytes": stb["weights"], "kv_bytes": stb["kv"], "achieved_gbs": step_gbs, "frac": step_gbs / pk["hbm_gbs"]},
@@ -537,6 +543,7 @@ def run_ours(args) -> dict:
     del sb, dec
     if not args.lean and args.workload == "llama70b":
         line["operators"] = {"paged_attention": operator_paged_attention(torch, dev, pk, reps=20),
+                             "paged_attention_e4m3_kv": operator_paged_attention(torch, dev, pk, reps=20, kv="e4m3"),
                              "int8_projection": operator_int8_projection(torch, dev, pk, only="")}
         line["llama8b"] = llama8b_block(torch, dev, local, pk)
     if rank == 0 and not args.no_cpu:
@@ -583,7 +590,7 @@ def _time_graph(torch, fn, reps, warm=3):
     return ts[0], ts[len(ts) // 2]
 
 
-def operator_paged_attention(torch, dev, pk, reps=20) -> dict:
+def operator_paged_attention(torch, dev, pk, reps=20, kv="bf16") -> dict:
     """The paged-attention decode operator alone: bf16 Q [32, 32, 128], 8 KV heads, block 16, 4096 physical blocks,
     permuted tables, lengths U[512, 8192], seed 1; as configured (tables alias blocks: 8704 logical > 4096 physical)
     and with a block of its own for every (sequence, 16 positions).  HBM GB/s on algorithmic bytes."""
@@ -593,7 +600,8 @@ def operator_paged_attention(torch, dev, pk, reps=20) -> dict:
     rng = np.random.default_rng(1)
     B, H, Hkv, D, nb, width = 32, 32, 8, 128, 4096, 512
     lens = rng.integers(512, 8193, size=B).astype(np.int32)
-    logical = 2 * int(lens.sum()) * Hkv * D * 2 + 2 * B * H * D * 2
+    kvb = 2 if kv == "bf16" else 1
+    logical = 2 * int(lens.sum()) * Hkv * D * kvb + 2 * B * H * D * 2
     g = torch.Generator(device=dev)
     g.manual_seed(1)
     out = {}
@@ -610,8 +618,8 @@ def operator_paged_attention(torch, dev, pk, reps=20) -> dict:
             for i in range(B):
                 tab[i, :need[i]] = perm[o:o + need[i]]
                 o += int(need[i])
-        k = torch.randn((P, BS, Hkv, D), device=dev, generator=g).to(torch.bfloat16)
-        v = torch.randn((P, BS, Hkv, D), device=dev, generator=g).to(torch.bfloat16)
+        k = torch.randn((P, BS, Hkv, D), device=dev, generator=g).to(kv_torch_dtype(torch, kv))
+        v = torch.randn((P, BS, Hkv, D), device=dev, generator=g).to(kv_torch_dtype(torch, kv))
         q = torch.randn((B, H, D), device=dev, generator=g).to(torch.bfloat16)
         tt, tl = torch.from_numpy(tab).to(dev), torch.from_numpy(lens).to(dev)
         o_t = torch.empty((B, H, D), dtype=torch.bfloat16, device=dev)
@@ -621,6 +629,7 @@ def operator_paged_attention(torch, dev, pk, reps=20) -> dict:
                      "frac": logical / med / 1e6 / pk["hbm_gbs"]}
         del k, v
     out["algorithmic_bytes"] = logical
+    out["kv"] = kv
     return out
 
 
@@ -664,7 +673,7 @@ def run_operator(args) -> dict:
     dev = torch.device("cuda", 0)
     pk = peaks()
     if args.workload == "paged_attn":
-        out = operator_paged_attention(torch, dev, pk, reps=max(args.steps, 20))
+        out = operator_paged_attention(torch, dev, pk, reps=max(args.steps, 20), kv=args.kv)
         head = out["no_shared_blocks"]
         return {"metric": "paged_attention_hbm_gbs", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": max(args.steps, 20),
                 "warmup": 3, "higher_is_better": True, "data": "synthetic", "dtype": "bf16 KV and Q, f32 accumulate",
@@ -850,6 +859,8 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--lean", action="store_true", help="skip the projection roofline, the operator sweeps and the 8B-shape block")
     ap.add_argument("--timeline", action="store_true", help="per-kernel durations inside one graph replay of the step")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "e4m3"],
+                    help="KV pool dtype: bf16 (the benchmark configuration) or e4m3 (f8e4m3fn pools, half the bytes; reported beside it)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -40,6 +40,7 @@ extern "C" {
 #define TLALOC_B200_S32 4
 #define TLALOC_B200_F32 11
 #define TLALOC_B200_BF16 16
+#define TLALOC_B200_F8E4M3FN 20 /* KV pools only: values stored clamped to +-448 and rounded to nearest even */
 
 int tlaloc_b200_abi_version(void);
 
@@ -99,7 +100,8 @@ size_t tlaloc_b200_paged_attention_scratch_bytes(int32_t num_rows, int32_t num_h
  * three-stage PTX chain kptx_paged_scores/softmax/out (kptx/.../KptxKernels.kt:970-1356).
  *
  *   query        device [R, H, D]            q_dtype  F32 | BF16
- *   key_cache    device [P, bs, Hkv, D]      kv_dtype F32 | BF16
+ *   key_cache    device [P, bs, Hkv, D]      kv_dtype F32 | BF16 | F8E4M3FN (the reference's three pool dtypes,
+ *                                            triton/kernels/paged_attention.cu:1429-1441; e4m3fn values widen exactly)
  *   value_cache  device, same shape/dtype
  *   block_tables device i32 [Tb, M]          row r reads table r / (R / Tb)
  *   seq_lens     device i32 [R]              row r attends positions [first, seq_lens[r])
@@ -159,7 +161,9 @@ int tlaloc_b200_paged_attention_static(const void* query, int32_t q_dtype, const
  * DxirInterpreter.kt:2233-2272; XLA scatter form stablehlo/.../StablehloEmitter.kt:4634):
  * row i of new_kv [T, Hkv*D] goes to pool slot slot_mapping[i]; a negative slot
  * is padding and is skipped; slots >= P*bs are skipped too (the interpreter
- * refuses them; the scatter drops them).  In place on the pool.
+ * refuses them; the scatter drops them).  In place on the pool.  pool_dtype F32 | BF16 |
+ * F8E4M3FN: a bf16 pool stores each value rounded to nearest even, an e4m3fn pool clamped
+ * to +-448 and rounded (core/.../Fp8.kt:89-90 saturateToF8e4m3fn); new_dtype F32 | BF16.
  */
 int tlaloc_b200_kv_cache_write(void* pool, int32_t pool_dtype, const void* new_kv, int32_t new_dtype,
                                const int32_t* slot_mapping, int32_t num_tokens, int32_t row_elems,
@@ -228,7 +232,8 @@ int tlaloc_b200_rmsnorm(const float* x, const float* gain, void* out, int32_t ou
  * RoPE (HfDecoderGraph.kt:792-818, HF rotate_half with the duplicated cos/sin tables of
  * ropeTables :436-462) applied to q [T, H, hd] and k [T, Hkv, hd] (f32), followed by the two
  * KV_CACHE_WRITEs of attention() (:1230-1231): rotated k and v [T, Hkv, hd] go to the pools at
- * slot_mapping.  q_out [T, H, hd] is F32 | BF16.  cos/sin are f32 [max_pos, hd].  ld_q/ld_k/ld_v are the row
+ * slot_mapping (kv_dtype F32 | BF16 | F8E4M3FN, narrowed as KV_CACHE_WRITE narrows).  q_out [T, H, hd] is F32 | BF16.
+ * cos/sin are f32 [max_pos, hd].  ld_q/ld_k/ld_v are the row
  * strides of q, k and v in elements, so the three may be column blocks of one fused q|k|v projection result.
  */
 int tlaloc_b200_rope_kv_write(const float* q, const float* k, const float* v, const int32_t* positions,

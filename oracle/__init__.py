@@ -81,6 +81,26 @@ def bf16_widen(bits) -> np.ndarray:
     return out
 
 
+def e4m3_bits(x) -> np.ndarray:
+    """f32 -> e4m3fn bytes as an f8e4m3fn KV pool stores them: clamped to +-448, rounded to nearest even."""
+    x = _f32(x)
+    out = np.empty(x.shape, dtype=np.uint8)
+    lib().orc_f32_to_e4m3_bits(_p(x), _p(out), ctypes.c_int64(x.size))
+    return out
+
+
+def e4m3_widen(bits) -> np.ndarray:
+    bits = np.ascontiguousarray(bits, dtype=np.uint8)
+    out = np.empty(bits.shape, dtype=np.float32)
+    lib().orc_e4m3_bits_to_f32(_p(bits), _p(out), ctypes.c_int64(bits.size))
+    return out
+
+
+def snap_e4m3(x) -> np.ndarray:
+    """saturateToF8e4m3fn elementwise: the f32 values an e4m3fn pool holds after a write of x."""
+    return e4m3_widen(e4m3_bits(x))
+
+
 class OracleRefusal(ValueError):
     """The interpreter would have refused these operands by name."""
 
@@ -257,7 +277,7 @@ class DecoderShape:
     # HfDecoderConfig.weightDType: BF16 rounds activations to bf16 before each projection and keeps the
     # embedding table / head / norm gains as bf16 values; F32 leaves everything f32.
     weight_dtype: str = "bf16"
-    kv_dtype: str = "f32"  # "f32" | "bf16": values are snapped RNE on write when bf16
+    kv_dtype: str = "f32"  # "f32" | "bf16" | "e4m3": values are snapped on write (bf16 RNE; e4m3fn clamped to 448, RNE)
     head_quant: bool = False  # WeightQuant.kt:21-22: the head stays in weight dtype unless quantized
     # The Granite family's four scalars (HfDecoderGraph.kt:546,915,1000,2129): h *= embed_scale after the embedding;
     # the attention scale replaces 1/sqrt(head_dim); each sub-layer's output is multiplied by residual_multiplier
@@ -338,6 +358,8 @@ def decode_step(shape: DecoderShape, w: DecoderWeights, key_pools, value_pools, 
         q, k = rope(q, positions, cos, sin), rope(k, positions, cos, sin)
         if shape.kv_dtype == "bf16":
             k, v = snap_bf16(k), snap_bf16(v)
+        elif shape.kv_dtype == "e4m3":  # DxirInterpreter.kt:2241-2246: an f8e4m3fn cache stores each value clamped and rounded
+            k, v = snap_e4m3(k), snap_e4m3(v)
         kv_cache_write_inplace(key_pools[l], k.reshape(B, -1), slot_mapping)
         kv_cache_write_inplace(value_pools[l], v.reshape(B, -1), slot_mapping)
         att = paged_attention(q, key_pools[l], value_pools[l], block_tables, seq_lens, scale, threads=threads)

@@ -69,6 +69,61 @@ ORC_API void orc_bf16_bits_to_f32(const uint16_t* in, float* out, int64_t n)
   for (int64_t i = 0; i < n; ++i) out[i] = bf16_widen(in[i]);
 }
 
+/*
+ * core/.../Fp8.kt:8-16,30-59,89-90: an f8e4m3fn KV pool stores saturateToF8e4m3fn(v) = the value clamped to +-448 and
+ * rounded to the nearest e4m3fn (ties to even; subnormals are multiples of 2^-9; NaN encodes as 0x7F and reads back NaN).
+ */
+static inline uint8_t e4m3_bits(float v)
+{
+  if (v != v) return 0x7F;
+  if (v > 448.f) v = 448.f;
+  if (v < -448.f) v = -448.f;
+  uint32_t bits;
+  memcpy(&bits, &v, 4);
+  const uint32_t sign = (bits >> 24) & 0x80u;
+  bits &= 0x7FFFFFFFu;
+  float a;
+  memcpy(&a, &bits, 4);
+  uint32_t code;
+  if (a < 0.015625f) {
+    const double scaled = (double)a * 512.0;
+    const double lower = floor(scaled);
+    const double frac = scaled - lower;
+    int lo = (int)lower;
+    code = (uint32_t)(frac > 0.5 ? lo + 1 : frac < 0.5 ? lo : (lo % 2 == 0 ? lo : lo + 1));
+  } else {
+    int e = (int)(bits >> 23) - 127;
+    uint32_t m = bits & 0x7FFFFFu;
+    const uint32_t lsb = (m >> 20) & 1u;
+    m += 0x7FFFFu + lsb;
+    if (m >= 0x800000u) {
+      m -= 0x800000u;
+      e += 1;
+    }
+    code = ((uint32_t)(e + 7) << 3) | (m >> 20);
+  }
+  return (uint8_t)(sign | code);
+}
+
+static inline float e4m3_widen(uint8_t b)
+{
+  const float sign = (b & 0x80) ? -1.f : 1.f;
+  const int e = (b >> 3) & 0xF, m = b & 7;
+  if (e == 0xF && m == 7) return NAN;
+  const float v = e == 0 ? (float)m / 8.f * 0.015625f : (1.f + (float)m / 8.f) * ldexpf(1.f, e - 7);
+  return sign * v;
+}
+
+ORC_API void orc_f32_to_e4m3_bits(const float* in, uint8_t* out, int64_t n)
+{
+  for (int64_t i = 0; i < n; ++i) out[i] = e4m3_bits(in[i]);
+}
+
+ORC_API void orc_e4m3_bits_to_f32(const uint8_t* in, float* out, int64_t n)
+{
+  for (int64_t i = 0; i < n; ++i) out[i] = e4m3_widen(in[i]);
+}
+
 ORC_API int orc_num_threads(void)
 {
 #ifdef _OPENMP

@@ -259,40 +259,9 @@ def test_views_off_a_16_byte_boundary_take_the_order_faithful_kernel():
         ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), out=torch.empty((m, n + 16), device=DEV))
 
 
-def test_bf16_weight_tiles_are_exact_too():
-    """$TLALOC_B200_GEMM_W16=bf16 keeps the converted weights as bf16 instead of f16 in the tensor-core kernel (both
-    hold an int8 code exactly).  The switch is read once per process, so the check runs in a child process."""
-    import os
-    import subprocess
-    import sys
-
-    code = r"""
-import numpy as np, torch, sys
-sys.path.insert(0, %r)
-from tlaloc_b200 import ops, _native as N
-rng = np.random.default_rng(5)
-for (m, k, n) in [(128, 4096, 4096), (100, 1024, 14336), (64, 688, 256), (256, 512, 768)]:
-    x = rng.integers(-8, 9, size=(m, k)).astype(np.float32)
-    codes = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
-    codes[0, :] = -127
-    codes[1, :] = 127
-    scales = np.exp2(rng.integers(-8, -2, size=n)).astype(np.float32)
-    want = (x.astype(np.float64) @ codes.astype(np.float64)).astype(np.float32) * scales[None, :]
-    t = lambda a, dt=None: torch.from_numpy(a).cuda() if dt is None else torch.from_numpy(a).cuda().to(dt)
-    got = ops.int8_gemm(t(x, torch.bfloat16), t(codes), t(scales))
-    torch.cuda.synchronize()
-    assert N.lib().tlaloc_b200_device_status() == 0
-    assert np.array_equal(got.cpu().numpy(), want), (m, k, n)
-print("bf16 tiles ok")
-""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, TLALOC_B200_GEMM_W16="bf16", TLALOC_B200_GEMM_PREFETCH="0")
-    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=240)
-    assert out.returncode == 0 and "bf16 tiles ok" in out.stdout, out.stdout[-1500:] + out.stderr[-1500:]
-
-
 @pytest.mark.parametrize("m", [8, 64])
 def test_every_code_value_converts_exactly(m):
-    """All 256 byte values as weights (the f16 expansion flips the top bit and subtracts 1152): one-hot activations
+    """All 256 byte values as weights (-128, which the quantizer never emits, included): one-hot activations
     read each code back, on the row-vector kernel and on the tensor-core kernel."""
     k, n = 256, 256
     codes = np.zeros((k, n), np.int8)

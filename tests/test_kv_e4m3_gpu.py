@@ -1,0 +1,177 @@
+"""f8e4m3fn KV pools (the format the reference serves long contexts with: kvDtype F8E4M3FN,
+ir/.../inference/DecodeGraphSpec.kt:762-767; its CUDA kernel's first pool type, triton/kernels/paged_attention.cu:74-102,
+1429-1441): the write side narrows exactly as the interpreter does (clamp to +-448, round to nearest even,
+DxirInterpreter.kt:2241-2246), the read side widens exactly.  Against the CPU oracle (needs a B200)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+F8 = torch.float8_e4m3fn
+
+
+def ops():
+    from tlaloc_b200 import ops as o
+
+    return o
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    return t if dtype is None else t.to(dtype)
+
+
+def f8_pool(values_f32):
+    """A device pool holding exactly oracle.snap_e4m3(values)."""
+    bits = oracle.e4m3_bits(values_f32)
+    return torch.from_numpy(bits).to(DEV).view(F8)
+
+
+def test_kv_write_narrows_as_the_interpreter_does():
+    rng = np.random.default_rng(0)
+    P, bs, Hkv, D = 6, 16, 2, 64
+    pool0 = oracle.snap_e4m3(rng.standard_normal((P, bs, Hkv, D)).astype(np.float32))
+    rows = (rng.standard_normal((5, Hkv, D)) * 100).astype(np.float32)
+    rows[0, 0, :6] = [448.0, 449.0, 464.0, 1e9, -1e9, 2.0 ** -10]
+    slots = np.array([5, -1, 95, 0, 17], np.int32)
+    pool = f8_pool(pool0)
+    ops().kv_cache_write(pool, dev(rows), dev(slots))
+    want = oracle.kv_cache_write(pool0, oracle.snap_e4m3(rows).reshape(5, -1), slots)
+    assert np.array_equal(pool.float().cpu().numpy(), want)
+    # bf16 rows narrow the same way
+    pool = f8_pool(pool0)
+    rb = oracle.snap_bf16(rows)
+    ops().kv_cache_write(pool, dev(rb, torch.bfloat16), dev(slots))
+    assert np.array_equal(pool.float().cpu().numpy(), oracle.kv_cache_write(pool0, oracle.snap_e4m3(rb).reshape(5, -1), slots))
+
+
+def test_rope_then_write_into_e4m3_pools():
+    rng = np.random.default_rng(1)
+    T, H, Hkv, hd, P, bs = 6, 8, 2, 64, 4, 16
+    qkv = (rng.standard_normal((T, (H + 2 * Hkv) * hd)) * 3).astype(np.float32)
+    pos = np.array([0, 5, 17, 63, 1, 40], np.int32)
+    slots = np.array([3, -1, 20, 63, 0, 41], np.int32)
+    cos, sin = oracle.rope_tables(10000.0, hd, 64)
+    q = qkv[:, :H * hd].reshape(T, H, hd)
+    k = qkv[:, H * hd:(H + Hkv) * hd].reshape(T, Hkv, hd)
+    v = qkv[:, (H + Hkv) * hd:].reshape(T, Hkv, hd)
+    want_q, want_k = oracle.rope(q, pos, cos, sin), oracle.snap_e4m3(oracle.rope(k, pos, cos, sin))
+    kc0 = oracle.snap_e4m3(rng.standard_normal((P, bs, Hkv, hd)).astype(np.float32))
+    vc0 = oracle.snap_e4m3(rng.standard_normal((P, bs, Hkv, hd)).astype(np.float32))
+    want_kc = oracle.kv_cache_write(kc0, want_k.reshape(T, -1), slots)
+    want_vc = oracle.kv_cache_write(vc0, oracle.snap_e4m3(v).reshape(T, -1), slots)
+    dq = dev(qkv)
+    kc, vc = f8_pool(kc0), f8_pool(vc0)
+    got_q = ops().rope_kv_write(dq[:, :H * hd].view(T, H, hd), dq[:, H * hd:(H + Hkv) * hd].view(T, Hkv, hd),
+                                dq[:, (H + Hkv) * hd:].view(T, Hkv, hd), dev(pos), dev(cos), dev(sin), dev(slots), kc, vc)
+    torch.cuda.synchronize()
+    assert np.array_equal(got_q.cpu().numpy(), want_q)
+    assert np.array_equal(kc.float().cpu().numpy(), want_kc) and np.array_equal(vc.float().cpu().numpy(), want_vc)
+
+
+def rand_case(rng, rows, tables, heads, kv_heads, dim, bs, width, nb, lens, spread=1.0):
+    q = rng.standard_normal((rows, heads, dim)).astype(np.float32)
+    k = oracle.snap_e4m3((rng.standard_normal((nb, bs, kv_heads, dim)) * spread).astype(np.float32))
+    v = oracle.snap_e4m3((rng.standard_normal((nb, bs, kv_heads, dim)) * spread).astype(np.float32))
+    tab = np.stack([rng.permutation(nb)[:width] for _ in range(tables)]).astype(np.int32)
+    return q, k, v, tab, np.asarray(lens, np.int32)
+
+
+CASES = [
+    # the reference kernel test's fixture shape (KptxPagedAttentionKernelTest.kt:59-76)
+    dict(rows=8, tables=8, heads=8, kv_heads=2, dim=64, bs=16, width=8, nb=64, lens=[128, 1, 17, 64, 33, 127, 5, 100]),
+    # Llama shapes: 8B heads (32/8, D 128) and one KV head per rank of the 70B shape, across slice boundaries
+    dict(rows=6, tables=6, heads=32, kv_heads=8, dim=128, bs=16, width=80, nb=500, lens=[1000, 17, 512, 513, 1024, 1280]),
+    dict(rows=5, tables=5, heads=8, kv_heads=1, dim=128, bs=16, width=300, nb=1400, lens=[4096, 4097, 1, 2500, 4800]),
+    # rows sharing a table, a generic head size, a small block
+    dict(rows=6, tables=2, heads=6, kv_heads=2, dim=48, bs=8, width=40, nb=90, lens=[300, 301, 302, 15, 16, 17]),
+]
+
+
+@pytest.mark.parametrize("case", range(len(CASES)))
+@pytest.mark.parametrize("q_dtype", [torch.float32, torch.bfloat16])
+def test_attention_over_e4m3_pools_matches_the_oracle(case, q_dtype):
+    c = CASES[case]
+    rng = np.random.default_rng(100 + case)
+    q, k, v, tab, lens = rand_case(rng, spread=3.0, **c)
+    if q_dtype == torch.bfloat16:
+        q = oracle.snap_bf16(q)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(c["dim"])))
+    want, want_lse = oracle.paged_attention(q, k, v, tab, lens, scale, return_lse=True, threads=oracle.host_threads())
+    out, lse = ops().paged_attention(dev(q, q_dtype), f8_pool(k), f8_pool(v), dev(tab), dev(lens), scale=scale, return_lse=True,
+                                     out=torch.empty(q.shape, dtype=torch.float32, device=DEV))
+    torch.cuda.synchronize()
+    tol = max(1e-4, 1e-5 * float(np.abs(want).max()))
+    assert np.abs(out.cpu().numpy() - want).max() <= tol
+    assert np.abs(lse.cpu().numpy() - want_lse).max() <= 1e-4
+    # a window, and (generic kernel) a keep mask
+    w_want = oracle.paged_attention(q, k, v, tab, lens, scale, sliding_window=33)
+    w_got = ops().paged_attention(dev(q, q_dtype), f8_pool(k), f8_pool(v), dev(tab), dev(lens), scale=scale, sliding_window=33,
+                                  out=torch.empty(q.shape, dtype=torch.float32, device=DEV))
+    assert np.abs(w_got.cpu().numpy() - w_want).max() <= tol
+
+
+def test_operator_configuration_shape_with_e4m3_pools():
+    """bf16 Q [32, 32, 128], 8 KV heads, block 16, 4096 blocks, permuted tables, lengths U[512, 8192]: the operator
+    configuration with the pools in e4m3fn (half the bytes)."""
+    rng = np.random.default_rng(1)
+    B, Hq, Hk, Dh, bs, nb, width = 32, 32, 8, 128, 16, 4096, 512
+    lens = rng.integers(512, 8193, size=B).astype(np.int32)
+    q = oracle.snap_bf16(rng.standard_normal((B, Hq, Dh)).astype(np.float32))
+    k = oracle.snap_e4m3(rng.standard_normal((nb, bs, Hk, Dh)).astype(np.float32))
+    v = oracle.snap_e4m3(rng.standard_normal((nb, bs, Hk, Dh)).astype(np.float32))
+    tab = np.stack([rng.permutation(nb)[:width] for _ in range(B)]).astype(np.int32)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(Dh)))
+    want = oracle.paged_attention(q, k, v, tab, lens, scale, threads=oracle.host_threads())
+    out = ops().paged_attention(dev(q, torch.bfloat16), f8_pool(k), f8_pool(v), dev(tab), dev(lens), scale=scale,
+                                out=torch.empty((B, Hq, Dh), dtype=torch.float32, device=DEV))
+    torch.cuda.synchronize()
+    err = np.abs(out.cpu().numpy() - want)
+    assert err.max() <= 2e-3 and np.all(err <= 2e-3 + 1e-2 * np.abs(want))
+    assert err.max() <= max(1e-4, 1e-5 * float(np.abs(want).max()))
+
+
+@pytest.mark.parametrize("exact", [True, False])
+def test_tiny_decoder_with_e4m3_kv_matches_the_oracle(exact):
+    from tlaloc_b200 import decoder as D
+    from tlaloc_b200 import sharding
+
+    shape = oracle.DecoderShape(num_layers=2, d_model=256, num_heads=4, num_kv_heads=2, head_dim=64, ffn=688, vocab=1024,
+                                kv_dtype="e4m3", head_quant=True)
+    w = oracle.make_weights(shape, seed=0)
+    cfg = D.DecoderConfig(**D.TINY, kv_dtype=F8, head_quant=True, max_positions=128)
+    B, bs, M = 4, 16, 6
+    rng = np.random.default_rng(2)
+    tables = (1 + rng.permutation(B * M)).reshape(B, M).astype(np.int32)
+    dec = D.Decoder(cfg, B, 1 + B * M, M, exact=exact)
+    dec.load_host_weights(w)
+    kp = [np.zeros((1 + B * M, bs, 2, 64), np.float32) for _ in range(2)]
+    vp = [np.zeros_like(a) for a in kp]
+    ids = rng.integers(0, 1024, size=B).astype(np.int32)
+    worst, swaps = 0.0, 0
+    for step in range(48):
+        pos = np.full(B, step, np.int32)
+        slots = sharding.slot_mapping(tables, pos, bs)
+        dec.set_inputs(ids, pos, tables, pos + 1, slots)
+        if step == 4:
+            dec.capture()
+        nxt = dec.step().cpu().numpy()
+        want = oracle.decode_step(shape, w, kp, vp, ids, pos, tables, pos + 1, slots)
+        err = np.abs(dec.logits.cpu().numpy() - want)
+        # Parity mode holds the build-wide bar (rel 1e-2 / abs 2e-3).  The fast kernels reorder f32 sums, and here a
+        # last-bit difference in a key or value BEFORE it is stored can land on the other side of an e4m3fn rounding
+        # boundary: the stored element then differs by one e4m3fn step (up to 1/8 of its value), and stays in the
+        # pool.  The two runs keep their own pools, so their logits drift apart by a few 1e-2 over the steps.
+        rel = 1e-2 if exact else 5e-2
+        assert np.all(err <= 2e-3 + rel * np.abs(want).max(axis=1, keepdims=True)), (step, float(err.max()))
+        worst = max(worst, float(err.max()))
+        ids = oracle.argmax(want).astype(np.int32)
+        swaps += int((nxt != ids).sum())
+    for l in range(2):
+        got = dec.key_pools[l].float().cpu().numpy()[1:]
+        assert np.mean(got == kp[l][1:]) >= (1.0 if exact else 0.995)
+    print(f"e4m3 KV, exact={exact}: worst logit |d| {worst:.2e}, token differences {swaps} of {48 * B}")
+    assert swaps == 0 if exact else swaps <= 6

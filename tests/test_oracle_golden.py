@@ -295,3 +295,26 @@ def test_decode_step_small_shapes_run_and_threads_agree():
     a = oracle.decode_step(shape, w, kp, vp, ids, pos, tables, lens, slots, threads=1)
     b = oracle.decode_step(shape, w, kp2, vp2, ids, pos, tables, lens, slots, threads=4)
     assert a.shape == (2, 64) and np.all(np.isfinite(a)) and np.array_equal(a, b)
+
+
+def test_e4m3fn_pool_narrowing_is_xlas_convert():
+    """An f8e4m3fn KV pool stores saturateToF8e4m3fn(v) (core/.../Fp8.kt:89-90): clamp to +-448, then the f32 ->
+    f8e4m3fn convert (ties to even, subnormals in steps of 2^-9, NaN -> 0x7F).  The restatement is held to an
+    independent implementation of the same convert (PyTorch's float8_e4m3fn cast) on every boundary and 200,000 draws,
+    and the widening to all 256 codes."""
+    import torch
+
+    rng = np.random.default_rng(0)
+    x = np.concatenate([
+        (rng.standard_normal(200000) * 30).astype(np.float32), (rng.standard_normal(50000) * 0.02).astype(np.float32),
+        np.array([0, -0.0, 448, 449, 463.9, 464, 465, 1e9, -1e9, 2 ** -9, 2 ** -10, 1.5 * 2 ** -9, 2.5 * 2 ** -9, 0.0146,
+                  0.015625, np.inf, -np.inf, 17.0, 18.0, 19.0, 0.40625, 0.4375], np.float32)])
+    mine = oracle.e4m3_bits(x)
+    theirs = torch.from_numpy(np.clip(x, -448, 448)).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(mine, theirs)
+    assert oracle.e4m3_bits(np.array([np.nan], np.float32))[0] == 0x7F
+    codes = np.arange(256, dtype=np.uint8)
+    want = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn).float().numpy()
+    got = oracle.e4m3_widen(codes)
+    assert np.array_equal(np.isnan(got), np.isnan(want)) and np.array_equal(got[~np.isnan(got)], want[~np.isnan(want)])
+    assert np.array_equal(oracle.snap_e4m3(np.array([17.0, 19.0, 500.0, -1e9], np.float32)), np.array([16.0, 20.0, 448.0, -448.0], np.float32))

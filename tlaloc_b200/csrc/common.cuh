@@ -3,6 +3,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -40,11 +41,14 @@ inline int CudaFail(const char* what, cudaError_t e)
 }
 
 inline bool IsFloatType(int dt) { return dt == TLALOC_B200_F32 || dt == TLALOC_B200_BF16; }
+// What a KV pool may hold: the float types plus e4m3fn.
+inline bool IsPoolType(int dt) { return IsFloatType(dt) || dt == TLALOC_B200_F8E4M3FN; }
 inline size_t DtypeBytes(int dt) { return dt == TLALOC_B200_F32 || dt == TLALOC_B200_S32 ? 4 : dt == TLALOC_B200_BF16 ? 2 : 1; }
 
 __device__ __forceinline__ float ToF32(float x) { return x; }
 __device__ __forceinline__ float ToF32(__nv_bfloat16 x) { return __bfloat162float(x); }
 __device__ __forceinline__ float ToF32(int8_t x) { return static_cast<float>(x); }
+__device__ __forceinline__ float ToF32(__nv_fp8_e4m3 x) { return static_cast<float>(x); }
 
 template <typename T>
 __device__ __forceinline__ T FromF32(float x);
@@ -52,6 +56,14 @@ template <>
 __device__ __forceinline__ float FromF32<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 FromF32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+// e4m3fn as a KV pool stores it: clamped to +-448, rounded to nearest even; NaN stays NaN (0x7F).
+template <>
+__device__ __forceinline__ __nv_fp8_e4m3 FromF32<__nv_fp8_e4m3>(float x)
+{
+  __nv_fp8_e4m3 r;
+  r.__x = __nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+  return r;
+}
 
 // tlaloc_b200_set_order_faithful: every operator evaluates in the reference interpreter's own order (parity runs).
 bool OrderFaithful();

@@ -304,7 +304,7 @@ extern "C" int tlaloc_b200_rope_kv_write(const float* q, const float* k, const f
   if (!q || !k || !v || !positions || !cos_table || !sin_table || !slot_mapping || !q_out || !key_cache || !value_cache) {
     return Fail(kInvalid, "%s: a required device pointer is null", op);
   }
-  if (!IsFloatType(q_out_dtype) || !IsFloatType(kv_dtype)) return Fail(kInvalid, "%s: q_out and the pools must be f32 or bf16", op);
+  if (!IsFloatType(q_out_dtype) || !IsPoolType(kv_dtype)) return Fail(kInvalid, "%s: q_out must be f32 or bf16, the pools f32, bf16 or f8e4m3fn", op);
   if (head_dim < 2 || head_dim % 2 != 0) {
     return Fail(kInvalid, "%s: head_dim %d is odd; RoPE rotates pairs of channels (rotate_half)", op, head_dim);
   }
@@ -323,9 +323,11 @@ extern "C" int tlaloc_b200_rope_kv_write(const float* q, const float* k, const f
                     static_cast<KVT*>(value_cache), num_heads, num_kv_heads, head_dim, num_slots, max_pos, ld_q,   \
                     ld_k, ld_v)
   if (q_out_dtype == TLALOC_B200_F32 && kv_dtype == TLALOC_B200_F32) TLALOC_LAUNCH(float, float);
-  else if (q_out_dtype == TLALOC_B200_F32) TLALOC_LAUNCH(float, __nv_bfloat16);
+  else if (q_out_dtype == TLALOC_B200_F32 && kv_dtype == TLALOC_B200_BF16) TLALOC_LAUNCH(float, __nv_bfloat16);
+  else if (q_out_dtype == TLALOC_B200_F32) TLALOC_LAUNCH(float, __nv_fp8_e4m3);
   else if (kv_dtype == TLALOC_B200_F32) TLALOC_LAUNCH(__nv_bfloat16, float);
-  else TLALOC_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else if (kv_dtype == TLALOC_B200_BF16) TLALOC_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else TLALOC_LAUNCH(__nv_bfloat16, __nv_fp8_e4m3);
 #undef TLALOC_LAUNCH
   if (e != cudaSuccess) return CudaFail("ROPE_KV_WRITE launch", e);
   CountLaunches(1);

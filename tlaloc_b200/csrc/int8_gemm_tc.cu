@@ -49,26 +49,17 @@ struct TcParams {
   int Kc, ks;
   int weights_const;  // codes and scales are not written by the preceding kernel: fetch them before the dependency wait
   int prefetch;       // blocks ahead of the tensor core at which a block's weights are asked into L2 (0 = never)
+  int prefetch_bulk;  // 1: through the bulk-copy unit (one request per 256-byte row), 0: one request per line
 };
 
 constexpr int kTcThreads = 512;                    // converter threads (16 warps)
-constexpr int kTcLaunchThreads = kTcThreads + 32;  // plus one warp whose elected lane issues the MMAs
+constexpr int kTcLaunchThreads = kTcThreads + 64;  // plus the warp whose first lane issues the MMAs and the L2 prefetch warp
 constexpr int kTcBN = 256;                         // output columns per CTA: the N of one MMA
 constexpr int kTcBK = 64;                          // k rows per block
 constexpr int kTcWBytes = kTcBN * kTcBK * 2;       // one block's weights as bf16
 constexpr int kTcTileStride = kTcBN + 4;
 constexpr uint32_t kTcSpinLimit = 1u << 22;
 
-// $TLALOC_B200_GEMM_W16 = bf16 keeps the converted weights as bf16 (three logic ops and a packed fma per pair of codes)
-// instead of the default f16 (two logic ops and a packed subtract); both are exact for int8 codes.
-bool TcHalfWeights()
-{
-  static const bool v = [] {
-    const char* e = std::getenv("TLALOC_B200_GEMM_W16");
-    return e == nullptr || std::string(e) != "bf16";
-  }();
-  return v;
-}
 // $TLALOC_B200_GEMM_PREFETCH: how many blocks ahead of the tensor core the weights are asked into L2 (default 8).
 int TcPrefetchDistance()
 {
@@ -153,29 +144,13 @@ __device__ __forceinline__ uint32_t LowBytesToBf16x2(uint32_t q)
   asm("fma.rn.bf16x2 %0, %1, %2, %3;\n" : "=r"(r) : "r"(t), "r"(0x3F803F80u), "r"(c));
   return r;
 }
-// The same two codes as an exact f16 pair: with u = code + 128 (the byte with its top bit flipped), 0x6400|u is the
-// f16 1024 + u, and 1024 + u - 1152 = code; one logic op ((q & 0x00FF00FF) ^ 0x64806480) and one packed subtract
-// (0x6480 is also the f16 1152).
-__device__ __forceinline__ uint32_t LowBytesToF16x2(uint32_t q)
-{
-  uint32_t t, r;
-  asm("lop3.b32 %0, %1, %2, %3, 0x6A;\n" : "=r"(t) : "r"(q), "r"(0x00FF00FFu), "r"(0x64806480u));
-  asm("sub.rn.f16x2 %0, %1, %2;\n" : "=r"(r) : "r"(t), "r"(0x64806480u));
-  return r;
-}
 // The four codes c0..c3 of one word as the pairs (c0, c2) and (c1, c3): the even bytes already sit in the low byte of
 // each half, the odd ones after one shift, so no byte permute is needed.  The weight tile therefore holds its columns
 // in the order 0 2 1 3 within every group of four; the epilogue swaps them back on the way out of TMEM.
-template <bool F16W>
-__device__ __forceinline__ void WordTo16(uint32_t w, uint32_t& even, uint32_t& odd)
+__device__ __forceinline__ void WordToBf16(uint32_t w, uint32_t& even, uint32_t& odd)
 {
-  if constexpr (F16W) {
-    even = LowBytesToF16x2(w);
-    odd = LowBytesToF16x2(w >> 8);
-  } else {
-    even = LowBytesToBf16x2(w);
-    odd = LowBytesToBf16x2(w >> 8);
-  }
+  even = LowBytesToBf16x2(w);
+  odd = LowBytesToBf16x2(w >> 8);
 }
 
 __device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count)
@@ -215,16 +190,21 @@ __device__ __forceinline__ uint64_t SmemDesc(uint32_t addr, uint32_t lbo_bytes, 
   return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) | (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16) |
          (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
-// kind::f16 instruction descriptor: f32 accumulator, bf16 A, B bf16 or f16 (the format fields are separate), A K-major,
-// B MN-major, M = 128, N = 256.
-__host__ __device__ constexpr uint32_t InstrDesc(bool b_is_f16)
+// kind::f16 instruction descriptor: f32 accumulator, bf16 A and B (the two operand formats must agree: a bf16 A with an
+// f16 B raises an illegal-instruction error), A K-major, B MN-major, M = 128, N = 256.
+__host__ __device__ constexpr uint32_t InstrDesc()
 {
-  return (1u << 4) | (1u << 7) | (b_is_f16 ? 0u : (1u << 10)) | (1u << 16) | (static_cast<uint32_t>(kTcBN >> 3) << 17) | (8u << 24);
+  return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(kTcBN >> 3) << 17) | (8u << 24);
 }
 // Asks the memory system to bring `bytes` (a multiple of 16, from a 16-byte aligned address) into L2; no data returns.
-__device__ __forceinline__ void PrefetchL2(const void* ptr, uint32_t bytes)
+// bulk: one request for the whole run through the bulk-copy unit; otherwise one request per 128-byte line.
+__device__ __forceinline__ void PrefetchL2(const int8_t* ptr, uint32_t bytes, bool bulk)
 {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(ptr), "r"(bytes) : "memory");
+  if (bulk) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(ptr), "r"(bytes) : "memory");
+  } else {
+    for (uint32_t o = 0; o < bytes; o += 128) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(ptr + o) : "memory");
+  }
 }
 __device__ __forceinline__ void TcMma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
 {
@@ -310,7 +290,7 @@ __device__ __forceinline__ void ClusterReduceRows(cg::cluster_group& cluster, fl
   }
 }
 
-template <int MPAD, typename YT, bool F16W>
+template <int MPAD, typename YT>
 __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams p)
 {
   using L = TcLayout<MPAD>;
@@ -381,18 +361,18 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
   // Everything above touched only shared memory and TMEM.  The weights and scales are the first global reads; when
   // the caller says no preceding kernel writes them they are requested BEFORE the dependency wait, so the coldest
   // loads of the launch travel while the predecessor drains.  The activations always come after it.
-  // Block bp of this CTA into L2, by the lanes of the seventeenth warp: rows lane and lane + 32, the tile's columns.
+  // Block bp of this CTA into L2, by the lanes of the prefetch warp: rows lane and lane + 32, the tile's columns.
   const uint32_t tile_bytes = static_cast<uint32_t>(min(kTcBN, p.N - col0));
   auto prefetch_block = [&](int bp) {
     if (bp >= nblocks) return;
     const int row = kb0 + bp * kTcBK + lane;
     const int8_t* src = p.w + static_cast<size_t>(row) * p.N + col0;
-    if (row < ke) PrefetchL2(src, tile_bytes);
-    if (row + 32 < ke) PrefetchL2(src + static_cast<size_t>(32) * p.N, tile_bytes);
+    if (row < ke) PrefetchL2(src, tile_bytes, p.prefetch_bulk != 0);
+    if (row + 32 < ke) PrefetchL2(src + static_cast<size_t>(32) * p.N, tile_bytes, p.prefetch_bulk != 0);
   };
   uint4 wreg[kChunks];
   if (!p.weights_const) GridDependencySync();
-  if (!conv && p.prefetch > 0) {  // the blocks the converters do not already hold in registers
+  if (warp == kTcThreads / 32 + 1 && p.prefetch > 0) {  // the blocks the converters do not already hold in registers
     for (int bp = kG; bp < p.prefetch; ++bp) prefetch_block(bp);
   }
 #pragma unroll
@@ -437,10 +417,10 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
         for (int i = 0; i < kChunks; ++i) {
           const uint4 v = wreg[i];
           uint32_t o0, o1, o2, o3, o4, o5, o6, o7;
-          WordTo16<F16W>(v.x, o0, o1);
-          WordTo16<F16W>(v.y, o2, o3);
-          WordTo16<F16W>(v.z, o4, o5);
-          WordTo16<F16W>(v.w, o6, o7);
+          WordToBf16(v.x, o0, o1);
+          WordToBf16(v.y, o2, o3);
+          WordToBf16(v.z, o4, o5);
+          WordToBf16(v.w, o6, o7);
           StShared16(bt + i * (kRP * 128) + s0, o0, o1, o2, o3);
           StShared16(bt + i * (kRP * 128) + s1, o4, o5, o6, o7);
           // the group's next block, one group period ahead
@@ -458,19 +438,17 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(conv_done0 + buf * 8) : "memory");
       }
     }
-  } else {
-    // The seventeenth warp.  Lane 0 is the MMA thread: for each block, wait for its converter group, then 4 K-steps of
-    // 128 x 256 x 16 per accumulator and a commit.  A = the activation strip (K-major), B = the converted weights
-    // (MN-major).  Descriptors differ from block to block only in the 14-bit start-address field, so they are built
-    // once and advanced by adds.  After each block all 32 lanes ask the weights of the block `prefetch` ahead into
-    // L2 (two 256-byte rows per lane), so the converters' register loads, which run one group period ahead, find them
-    // there: the latency of HBM is then covered by L2's capacity and not by the registers a thread can spare.
-    constexpr uint32_t idesc = InstrDesc(F16W);
-    const uint64_t a_desc0 = SmemDesc(smem_base, 16, 1024), b_desc0 = SmemDesc(smem_base + L::kWOffset, 8192, 1024);
-    for (int b = 0; b < nblocks; ++b) {
-      const int buf = b % L::kBufs;
-      ok = MbarWaitWarp(conv_done0 + buf * 8, (b / L::kBufs) & 1, lane) && ok;
-      if (lane == 0) {
+  } else if (warp == kTcThreads / 32) {
+    // The MMA thread (one lane; nothing else may sit between a block's arrival and its MMAs): for each block, wait for
+    // its converter group, then 4 K-steps of 128 x 256 x 16 per accumulator and a commit.  A = the activation strip
+    // (K-major), B = the converted weights (MN-major).  Descriptors differ from block to block only in the 14-bit
+    // start-address field, so they are built once and advanced by adds.
+    if (lane == 0) {
+      constexpr uint32_t idesc = InstrDesc();
+      const uint64_t a_desc0 = SmemDesc(smem_base, 16, 1024), b_desc0 = SmemDesc(smem_base + L::kWOffset, 8192, 1024);
+      for (int b = 0; b < nblocks; ++b) {
+        const int buf = b % L::kBufs;
+        ok = MbarWait(conv_done0 + buf * 8, (b / L::kBufs) & 1) && ok;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((buf * L::kXBytes) >> 4);
         const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((buf * kTcWBytes) >> 4);
@@ -483,12 +461,19 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
         }
         TcCommit(mma_done0 + buf * 8);
       }
-      if (p.prefetch > 0) prefetch_block(b + p.prefetch);
-      __syncwarp();
+      // The last commit covers every MMA before it.  Its phase is unambiguous here: the converters of the last block
+      // had already waited for the same barrier's previous phase.
+      if (nblocks > 0) ok = MbarWait(mma_done0 + ((nblocks - 1) % L::kBufs) * 8, ((nblocks - 1) / L::kBufs) & 1) && ok;
     }
-    // The last commit covers every MMA before it.  Its phase is unambiguous here: the converters of the last block
-    // had already waited for the same barrier's previous phase.
-    if (nblocks > 0) ok = MbarWaitWarp(mma_done0 + ((nblocks - 1) % L::kBufs) * 8, ((nblocks - 1) / L::kBufs) & 1, lane) && ok;
+  } else if (p.prefetch > 0) {
+    // The prefetch warp: keeps the weights `prefetch` blocks ahead of the tensor core on their way into L2, so that the
+    // converters' register loads (which run one group period ahead and are limited by the registers a thread can
+    // spare) meet L2's latency, not HBM's.  It paces itself on the MMA completions, as an onlooker of those barriers;
+    // a wait that runs out only ends the prefetching.
+    for (int b = 0; b + p.prefetch < nblocks; ++b) {
+      if (!MbarWaitWarp(mma_done0 + (b % L::kBufs) * 8, (b / L::kBufs) & 1, lane)) break;
+      prefetch_block(b + p.prefetch);
+    }
   }
   if (!ok) atomicExch(&g_tc_status, 1);
   if (warp < kTcThreads / 32) CpAsyncWait<0>();
@@ -526,7 +511,7 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
 #pragma unroll
       for (int c = 0; c < 16; ++c)
         dst[c] = make_float4(__uint_as_float(rr[4 * c]), __uint_as_float(rr[4 * c + 2]), __uint_as_float(rr[4 * c + 1]),
-                             __uint_as_float(rr[4 * c + 3]));  // TMEM holds the columns as 0 2 1 3 (see WordTo16)
+                             __uint_as_float(rr[4 * c + 3]));  // TMEM holds the columns as 0 2 1 3 (see WordToBf16)
     }
     if (nranks == 1) {
       __syncthreads();
@@ -585,9 +570,7 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
 template <int MPAD, typename YT>
 cudaError_t PrepareTc()
 {
-  cudaError_t e = cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD>::kBytes);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD>::kBytes);
-  return e;
+  return cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD>::kBytes);
 }
 
 template <int MPAD, typename YT>
@@ -601,8 +584,7 @@ cudaError_t LaunchTc(const TcParams& p, cudaStream_t stream)
   cudaLaunchAttribute attr[2];
   cfg.numAttrs = ChainAttributes(attr, p.ks);
   cfg.attrs = attr;
-  if (TcHalfWeights()) return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT, true>, p);
-  return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT, false>, p);
+  return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT>, p);
 }
 
 // CTAs of the kernel that can be resident at once when launched as clusters of ks (index [device][MPAD class][ks]);
@@ -626,7 +608,7 @@ void FillTcSlots(int device, int cls)
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, Int8GemmTcKernel<MPAD, float, true>, &cfg) != cudaSuccess || clusters <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, Int8GemmTcKernel<MPAD, float>, &cfg) != cudaSuccess || clusters <= 0) {
       cudaGetLastError();
       clusters = (ks <= 2 ? 148 : ks <= 4 ? 128 : 112) / ks;  // a cautious guess when the query is not available
     }
@@ -710,6 +692,11 @@ cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const 
   TcParams p;
   p.weights_const = weights_const ? 1 : 0;
   p.prefetch = TcPrefetchDistance();
+  static const int bulk = [] {
+    const char* e = std::getenv("TLALOC_B200_GEMM_PREFETCH_BULK");
+    return e != nullptr ? std::atoi(e) : 0;
+  }();
+  p.prefetch_bulk = bulk;
   p.w = codes;
   p.scales = scales;
   p.K = k;

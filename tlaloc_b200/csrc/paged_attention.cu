@@ -581,6 +581,339 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
 }
 
 // ------------------------------------------------------------------------------------------
+// The tensor-core slice kernel for f8e4m3fn pools: the same decomposition as PaSliceMma with half the bytes per
+// position.  An e4m3fn value is exact in f16 (4 significant bits, exponents 2^-9 .. 2^8), so the MMAs run on f16
+// operands: the raw bytes are copied to shared memory as they lie (a position's head row is D bytes), ldmatrix
+// moves them as if they were 16-bit elements (one "element" = two neighbouring channels) and cvt.f16x2.e4m3x2
+// widens each pair in registers.  That fixes which channels a lane holds, which differs from the 16-bit layout:
+//   K as A (positions x channels): a lane's register of chunk c holds channels 16c + 4tig .. + 3 of position gid,
+//     so MMA k-slots 2tig, 2tig+1 / 2tig+8, 2tig+9 stand for channels 16c + 4tig, +1 / +2, +3, and the query's B
+//     fragments are loaded with the same assignment (a dot product does not care in which order it is summed);
+//   V^T as A (channels x positions, ldmatrix.trans): a lane's register holds channels 2gid, 2gid+1 of positions
+//     2tig, 2tig+1; a byte permute pairs the two positions of each channel, so accumulator rows gid / gid+8 of
+//     m-tile c stand for channels 16c + 2gid / 16c + 2gid + 1 (undone when the record is written).
+// The query and the probabilities are carried as hi + lo f16 parts (22 bits); a query beyond f16's range (|q| > 65504)
+// is clamped to it.
+
+__device__ __forceinline__ void MmaF16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Two e4m3fn bytes (the low and the high byte of `pair`) as an f16 pair, exactly.
+__device__ __forceinline__ uint32_t E4m3x2ToF16x2(uint32_t pair)
+{
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(pair & 0xFFFFu), __NV_E4M3);
+  return static_cast<uint32_t>(h.x) | (static_cast<uint32_t>(h.y) << 16);
+}
+// Two floats as f16 hi parts (lower index in the low half) and the f16 of what is left.
+__device__ __forceinline__ void SplitPackF16(float x, float y, uint32_t& hi, uint32_t& lo)
+{
+  x = fminf(fmaxf(x, -65504.f), 65504.f);
+  y = fminf(fmaxf(y, -65504.f), 65504.f);
+  const __half xh = __float2half_rn(x), yh = __float2half_rn(y);
+  const __half xl = __float2half_rn(x - __half2float(xh)), yl = __float2half_rn(y - __half2float(yh));
+  hi = static_cast<uint32_t>(__half_as_ushort(xh)) | (static_cast<uint32_t>(__half_as_ushort(yh)) << 16);
+  lo = static_cast<uint32_t>(__half_as_ushort(xl)) | (static_cast<uint32_t>(__half_as_ushort(yl)) << 16);
+}
+
+template <int D, int NS>
+struct MmaLayoutF8 {
+  static constexpr int kRowBytes = D;
+  static constexpr int kTileBytes = 16 * kRowBytes;
+  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kWarpBytes = NS * kStageBytes;
+  static constexpr int kTabOffset = kMmaWarps * kWarpBytes;
+  static_assert(kWarpBytes >= static_cast<int>(sizeof(float)) * kMmaQ * (D + 2), "a warp's stages hold its partial record");
+  static size_t Bytes(int tab_entries) { return kTabOffset + sizeof(int) * static_cast<size_t>(tab_entries); }
+};
+
+template <typename QT, int D, int NS, int NT>
+__global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
+{
+  GridDependencySync();
+  constexpr bool QLO = sizeof(QT) == 4;  // a bf16 query is exact in f16 (within its range): no low part to carry
+  using L = MmaLayoutF8<D, NS>;
+  constexpr int CPR = L::kRowBytes / 16;  // 16-byte chunks per row: 8 (D = 128) or 4 (D = 64)
+  constexpr int KS = D / 16;              // k-steps of K Q^T, m-tiles of V^T P^T: one per chunk
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* stages = smem;
+  int* tab = reinterpret_cast<int*>(smem + L::kTabOffset);
+
+  const int s = blockIdx.x, kv = blockIdx.y, tb = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int ctx = p.M * p.bs;
+  const int c0 = s * p.slice;
+
+  const int c_end = min(c0 + p.slice, ctx);
+  const int b0 = p.bs_shift >= 0 ? (c0 >> p.bs_shift) : c0 / p.bs;
+  const int b_last = c_end > c0 ? (p.bs_shift >= 0 ? ((c_end - 1) >> p.bs_shift) : (c_end - 1) / p.bs) : b0 - 1;
+  for (int j = tid; j <= b_last - b0; j += kMmaThreads) {
+    tab[j] = ClampI(__ldg(p.tables + static_cast<size_t>(tb) * p.M + b0 + j), 0, p.P - 1);
+  }
+  int maxlen = 0, minfirst = ctx;
+  for (int r = 0; r < p.rpt; ++r) {
+    const int len = ClampI(__ldg(p.lens + tb * p.rpt + r), 0, ctx);
+    maxlen = max(maxlen, len);
+    minfirst = min(minfirst, p.window > 0 ? max(0, len - p.window) : 0);
+  }
+  const int c1 = min(min(c0 + p.slice, ctx), maxlen);
+  const int t_begin = max(c0, minfirst) & ~15;
+  if (t_begin >= c1) return;
+  const int ngroups = (c1 - t_begin + 15) >> 4;
+
+  int qlen[NT][2], qfirst[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int i = nt * 8 + 2 * tig + e;
+      int len = 0, first = 0;
+      if (i < p.NQ) {
+        const int full = ClampI(__ldg(p.lens + tb * p.rpt + i / p.group), 0, ctx);
+        first = p.window > 0 ? max(0, full - p.window) : 0;
+        len = min(full, c1);
+      }
+      qlen[nt][e] = len;
+      qfirst[nt][e] = first;
+    }
+  }
+  // Q^T as B fragments under the byte layout's channel assignment: for k-step kk, b0b1 = Q[query gid][16kk + 4tig, +1],
+  // b2b3 = Q[query gid][16kk + 4tig + 2, +3]; hi and lo f16 parts.
+  uint32_t qh[NT][KS][2], ql[QLO ? NT : 1][QLO ? KS : 1][2];
+  {
+    const QT* q = static_cast<const QT*>(p.q);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int i = nt * 8 + gid;
+      const bool have = i < p.NQ;
+      const QT* src = q + (static_cast<size_t>(tb * p.rpt + (have ? i / p.group : 0)) * p.H + kv * p.group + (have ? i % p.group : 0)) * D;
+#pragma unroll
+      for (int kk = 0; kk < KS; ++kk) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int d = 16 * kk + 4 * tig + 2 * h;
+          const float x = have ? ToF32(src[d]) : 0.f, y = have ? ToF32(src[d + 1]) : 0.f;
+          uint32_t hi, lo;
+          SplitPackF16(x, y, hi, lo);
+          qh[nt][kk][h] = hi;
+          if (QLO) ql[nt][kk][h] = lo;
+        }
+      }
+    }
+  }
+  __syncthreads();  // tab is staged
+
+  const unsigned char* kc = static_cast<const unsigned char*>(p.kc);
+  const unsigned char* vc = static_cast<const unsigned char*>(p.vc);
+  unsigned char* my_stages = stages + warp * L::kWarpBytes;
+  const uint32_t my_stages_addr = SmemAddr(my_stages);
+  const int my_n = warp < ngroups ? (ngroups - warp + kMmaWarps - 1) / kMmaWarps : 0;
+  const size_t row_elems = static_cast<size_t>(p.Hkv) * D;  // bytes between consecutive positions of a block
+  const bool one_block_per_group = p.bs_shift >= 4;
+
+  // A row's 16-byte chunk c lands at chunk c ^ swz(row): with 128-byte rows swz = row & 7, with 64-byte rows (two rows
+  // per 128 bytes) swz = (row >> 1) & 3; either way the eight rows an ldmatrix touches fall in eight different 16-byte
+  // bank groups.
+  auto swz = [](int r) { return CPR == 8 ? (r & 7) : ((r >> 1) & 3); };
+  auto issue = [&](int it) {
+    const int t_base = t_begin + ((warp + kMmaWarps * it) << 4);
+    const uint32_t dst_base = my_stages_addr + (it % NS) * L::kStageBytes;
+    size_t group_off = 0;
+    if (one_block_per_group) {
+      const int blk = tab[(t_base >> p.bs_shift) - b0];
+      group_off = ((static_cast<size_t>(blk) << p.bs_shift) + (t_base & (p.bs - 1))) * row_elems + static_cast<size_t>(kv) * D;
+    }
+#pragma unroll
+    for (int i = 0; i < 16 * CPR / 32; ++i) {
+      const int c = lane + 32 * i;
+      const int r = c / CPR, col = c % CPR;
+      const int t = t_base + r;
+      const bool valid = t < c1;
+      size_t off = 0;
+      if (valid) {
+        if (one_block_per_group) {
+          off = group_off + r * row_elems + col * 16;
+        } else {
+          const int blk_i = p.bs_shift >= 0 ? (t >> p.bs_shift) : t / p.bs;
+          const int slot = t - blk_i * p.bs;
+          off = ((static_cast<size_t>(tab[blk_i - b0]) * p.bs + slot) * p.Hkv + kv) * D + col * 16;
+        }
+      }
+      const uint32_t dst = dst_base + r * L::kRowBytes + ((col ^ swz(r)) << 4);
+      CpAsync16(dst, kc + off, valid ? 16 : 0);
+      CpAsync16(dst + L::kTileBytes, vc + off, valid ? 16 : 0);
+    }
+  };
+
+  for (int it = 0; it < NS - 1; ++it) {
+    if (it < my_n) issue(it);
+    CpAsyncCommit();
+  }
+
+  float o[NT][KS][4];
+  float m_run[NT][2], l_run[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    m_run[nt][0] = m_run[nt][1] = -INFINITY;
+    l_run[nt][0] = l_run[nt][1] = 0.f;
+#pragma unroll
+    for (int mt = 0; mt < KS; ++mt) o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.f;
+  }
+  const float sl2 = p.scale * kLog2e;
+  // ldmatrix addressing, the same for K and V: matrices 0, 1 = positions 0-7, 8-15 of chunk 2j; 2, 3 = of chunk 2j + 1.
+  const int row_a = (lane & 7) + ((lane >> 3) & 1) * 8;
+  const uint32_t row_off = row_a * L::kRowBytes;
+  const int row_swz = swz(row_a), hi_chunk = lane >> 4;
+
+  for (int it = 0; it < my_n; ++it) {
+    if (it + NS - 1 < my_n) issue(it + NS - 1);
+    CpAsyncCommit();
+    CpAsyncWait<NS - 1>();
+    __syncwarp();
+    const int t_base = t_begin + ((warp + kMmaWarps * it) << 4);
+    const uint32_t k_addr = my_stages_addr + (it % NS) * L::kStageBytes;
+    const uint32_t v_addr = k_addr + L::kTileBytes;
+
+    float sacc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+    for (int j = 0; j < KS / 2; ++j) {
+      uint32_t r[4];
+      LdMatrixX4(r, k_addr + row_off + (((2 * j + hi_chunk) ^ row_swz) << 4));
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int kk = 2 * j + half;
+        const uint32_t lo_rows = r[2 * half], hi_rows = r[2 * half + 1];
+        const uint32_t a[4] = {E4m3x2ToF16x2(lo_rows), E4m3x2ToF16x2(hi_rows), E4m3x2ToF16x2(lo_rows >> 16), E4m3x2ToF16x2(hi_rows >> 16)};
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          MmaF16(sacc[nt], a, qh[nt][kk][0], qh[nt][kk][1]);
+          if (QLO) MmaF16(sacc[nt], a, ql[nt][kk][0], ql[nt][kk][1]);
+        }
+      }
+    }
+    uint32_t pb_hi[NT][2], pb_lo[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const int e = x & 1;
+        const int tok = t_base + gid + (x >> 1) * 8;
+        const bool live = tok < qlen[nt][e] && tok >= qfirst[nt][e];
+        const float v = live ? sacc[nt][x] * sl2 : -INFINITY;
+        sacc[nt][x] = v;
+        tmax[e] = fmaxf(tmax[e], v);
+      }
+      float alpha[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float t = tmax[e];
+        t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 4));
+        t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 8));
+        t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 16));
+        const float mn = fmaxf(m_run[nt][e], t);
+        alpha[e] = mn == -INFINITY ? 1.f : Exp2(m_run[nt][e] - mn);
+        const float base = mn == -INFINITY ? 0.f : mn;
+        m_run[nt][e] = mn;
+        const float p0 = Exp2(sacc[nt][e] - base), p1 = Exp2(sacc[nt][2 + e] - base);
+        sacc[nt][e] = p0;
+        sacc[nt][2 + e] = p1;
+        l_run[nt][e] = l_run[nt][e] * alpha[e] + p0 + p1;
+      }
+#pragma unroll
+      for (int mt = 0; mt < KS; ++mt) {
+        o[nt][mt][0] *= alpha[0];
+        o[nt][mt][1] *= alpha[1];
+        o[nt][mt][2] *= alpha[0];
+        o[nt][mt][3] *= alpha[1];
+      }
+      uint32_t h0, l0, h1, l1;
+      SplitPackF16(sacc[nt][0], sacc[nt][1], h0, l0);
+      SplitPackF16(sacc[nt][2], sacc[nt][3], h1, l1);
+      pb_hi[nt][0] = MovMatrixTrans(h0);
+      pb_hi[nt][1] = MovMatrixTrans(h1);
+      pb_lo[nt][0] = MovMatrixTrans(l0);
+      pb_lo[nt][1] = MovMatrixTrans(l1);
+    }
+#pragma unroll
+    for (int j = 0; j < KS / 2; ++j) {
+      uint32_t r[4];
+      LdMatrixX4Trans(r, v_addr + row_off + (((2 * j + hi_chunk) ^ row_swz) << 4));
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int mt = 2 * j + half;
+        // bytes {p0 c0, p0 c1, p1 c0, p1 c1} -> {p0 c0, p1 c0 | p0 c1, p1 c1}: the two positions of each channel side by side
+        const uint32_t lo_pos = __byte_perm(r[2 * half], 0u, 0x3120), hi_pos = __byte_perm(r[2 * half + 1], 0u, 0x3120);
+        const uint32_t a[4] = {E4m3x2ToF16x2(lo_pos), E4m3x2ToF16x2(lo_pos >> 16), E4m3x2ToF16x2(hi_pos), E4m3x2ToF16x2(hi_pos >> 16)};
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          MmaF16(o[nt][mt], a, pb_hi[nt][0], pb_hi[nt][1]);
+          MmaF16(o[nt][mt], a, pb_lo[nt][0], pb_lo[nt][1]);
+        }
+      }
+    }
+    __syncwarp();
+  }
+  CpAsyncWait<0>();
+  __syncwarp();
+
+  {
+    float* wm = reinterpret_cast<float*>(my_stages);
+    float* wl = wm + kMmaQ;
+    float* wo = wl + kMmaQ;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float l = l_run[nt][e];
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        const int i = nt * 8 + 2 * tig + e;
+        if (gid == 0) {
+          wm[i] = m_run[nt][e];
+          wl[i] = l;
+        }
+#pragma unroll
+        for (int mt = 0; mt < KS; ++mt) {
+          wo[i * D + 16 * mt + 2 * gid] = o[nt][mt][e];          // accumulator row gid: channel 16 mt + 2 gid
+          wo[i * D + 16 * mt + 2 * gid + 1] = o[nt][mt][2 + e];  // accumulator row gid + 8: channel 16 mt + 2 gid + 1
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < p.NQ * D; idx += kMmaThreads) {
+    const int i = idx / D, d = idx - i * D;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) mx = fmaxf(mx, reinterpret_cast<const float*>(stages + w * L::kWarpBytes)[i]);
+    float acc = 0.f, l = 0.f;
+    if (mx != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kMmaWarps; ++w) {
+        const float* wm = reinterpret_cast<const float*>(stages + w * L::kWarpBytes);
+        const float f = Exp2(wm[i] - mx);
+        acc += f * wm[2 * kMmaQ + i * D + d];
+        l += f * wm[kMmaQ + i];
+      }
+    }
+    float* rec = Record(p, s, tb * p.rpt + i / p.group, kv * p.group + i % p.group);
+    rec[2 + d] = acc;
+    if (d == 0) {
+      rec[0] = mx * kLn2;
+      rec[1] = l;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // Combine: grid R*H.  Row r's live slices are [first / slice, ceil(len / slice)); their records merge as
 // out = sum_s exp(m_s - max) acc_s / sum_s exp(m_s - max) l_s, in slice order (deterministic).
 
@@ -865,6 +1198,29 @@ cudaError_t LaunchMma(const PaParams& p, cudaStream_t stream)
   }
 }
 
+constexpr int kF8Stages = 4;  // half the bytes per group: twice the groups in flight for the same shared memory
+
+template <typename QT, int D>
+cudaError_t PrepareMmaF8()
+{
+  cudaError_t e = cudaFuncSetAttribute(PaSliceMmaF8<QT, D, kF8Stages, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(MmaLayoutF8<D, kF8Stages>::Bytes(kMaxTabEntries)));
+  if (e == cudaSuccess) {
+    e = cudaFuncSetAttribute(PaSliceMmaF8<QT, D, kF8Stages, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(MmaLayoutF8<D, kF8Stages>::Bytes(kMaxTabEntries)));
+  }
+  return e;
+}
+
+template <typename QT, int D>
+cudaError_t LaunchMmaF8(const PaParams& p, cudaStream_t stream)
+{
+  const size_t smem = MmaLayoutF8<D, kF8Stages>::Bytes(p.slice / p.bs + 2);
+  const dim3 grid(p.S, p.Hkv, p.Tb);
+  if (p.NQ <= 8) return LaunchChained(PaSliceMmaF8<QT, D, kF8Stages, 1>, grid, kMmaThreads, smem, stream, p);
+  return LaunchChained(PaSliceMmaF8<QT, D, kF8Stages, 2>, grid, kMmaThreads, smem, stream, p);
+}
+
 template <typename QT, typename KVT>
 cudaError_t LaunchGeneric(const PaParams& p, cudaStream_t stream)
 {
@@ -903,6 +1259,10 @@ cudaError_t PreparePagedAttentionKernels()
     if (e == cudaSuccess) e = PrepareMma<__nv_bfloat16, 128>();
     if (e == cudaSuccess) e = PrepareMma<float, 64>();
     if (e == cudaSuccess) e = PrepareMma<float, 128>();
+    if (e == cudaSuccess) e = PrepareMmaF8<__nv_bfloat16, 64>();
+    if (e == cudaSuccess) e = PrepareMmaF8<__nv_bfloat16, 128>();
+    if (e == cudaSuccess) e = PrepareMmaF8<float, 64>();
+    if (e == cudaSuccess) e = PrepareMmaF8<float, 128>();
     return e;
   });
 }
@@ -942,9 +1302,9 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
   if (!query || !key_cache || !value_cache || !block_tables || !seq_lens || !out || !scratch) {
     return Fail(kInvalid, "%s: a required device pointer is null", op);
   }
-  if (!IsFloatType(q_dtype) || !IsFloatType(kv_dtype) || !IsFloatType(out_dtype)) {
-    return Fail(kInvalid, "%s: query, pools and out must be f32 or bf16 (got dtypes %d, %d, %d)", op, q_dtype,
-                kv_dtype, out_dtype);
+  if (!IsFloatType(q_dtype) || !IsPoolType(kv_dtype) || !IsFloatType(out_dtype)) {
+    return Fail(kInvalid, "%s: query and out must be f32 or bf16, the pools f32, bf16 or f8e4m3fn (got dtypes %d, %d, %d)", op,
+                q_dtype, kv_dtype, out_dtype);
   }
   if (num_rows < 1 || num_heads < 1 || head_dim < 1) {
     return Fail(kInvalid, "%s: query must be [numSeqs, numHeads, headDim] with positive dims, got [%d, %d, %d]", op,
@@ -1012,17 +1372,25 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
     p.S = 1;
     cudaError_t fe;
     if (q_dtype == TLALOC_B200_F32 && kv_dtype == TLALOC_B200_F32) fe = LaunchFaithful<float, float>(p, out_dtype, span, st);
-    else if (q_dtype == TLALOC_B200_F32) fe = LaunchFaithful<float, __nv_bfloat16>(p, out_dtype, span, st);
+    else if (q_dtype == TLALOC_B200_F32 && kv_dtype == TLALOC_B200_BF16) fe = LaunchFaithful<float, __nv_bfloat16>(p, out_dtype, span, st);
+    else if (q_dtype == TLALOC_B200_F32) fe = LaunchFaithful<float, __nv_fp8_e4m3>(p, out_dtype, span, st);
     else if (kv_dtype == TLALOC_B200_F32) fe = LaunchFaithful<__nv_bfloat16, float>(p, out_dtype, span, st);
-    else fe = LaunchFaithful<__nv_bfloat16, __nv_bfloat16>(p, out_dtype, span, st);
+    else if (kv_dtype == TLALOC_B200_BF16) fe = LaunchFaithful<__nv_bfloat16, __nv_bfloat16>(p, out_dtype, span, st);
+    else fe = LaunchFaithful<__nv_bfloat16, __nv_fp8_e4m3>(p, out_dtype, span, st);
     if (fe != cudaSuccess) return CudaFail("PAGED_ATTENTION parity-mode launch", fe);
     CountLaunches(1);
     return kOk;
   }
   // The tensor-core kernel copies K/V rows in 16-byte pieces: pools that start off a 16-byte boundary (a slice of a
   // larger allocation at an odd element) take the generic kernel, which has no alignment needs.
-  const bool mma = kv_dtype == TLALOC_B200_BF16 && (head_dim == 64 || head_dim == 128) && p.NQ <= kMmaQ &&
-                   keep == nullptr && block_size >= 8 && Aligned16(key_cache) && Aligned16(value_cache);
+  // $TLALOC_B200_PA_F8_GENERIC=1 sends e4m3fn pools to the generic kernel (a debugging aid).
+  static const bool f8_generic = [] {
+    const char* v = std::getenv("TLALOC_B200_PA_F8_GENERIC");
+    return v != nullptr && v[0] == '1';
+  }();
+  const bool f8 = kv_dtype == TLALOC_B200_F8E4M3FN;
+  const bool mma = (kv_dtype == TLALOC_B200_BF16 || (f8 && !f8_generic)) && (head_dim == 64 || head_dim == 128) && p.NQ <= kMmaQ &&
+                   keep == nullptr && (f8 ? block_size >= 16 : block_size >= 8) && Aligned16(key_cache) && Aligned16(value_cache);
   // Slice length: the preferred one (tensor-core kernel) or 256, stretched until `splits` slices cover the context.
   int slice = mma ? PreferredSlice(ctx, static_cast<long long>(num_tables) * num_kv_heads) : 256;
   if (static_cast<int64_t>(slice) * splits < ctx) slice = (ctx + splits - 1) / splits;
@@ -1037,19 +1405,26 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
   if (mma) {
     e = PreparePagedAttentionKernels();
     if (e != cudaSuccess) return CudaFail("PAGED_ATTENTION set-up", e);
-    if (q_dtype == TLALOC_B200_BF16) {
+    if (f8) {
+      if (q_dtype == TLALOC_B200_BF16) e = head_dim == 64 ? LaunchMmaF8<__nv_bfloat16, 64>(p, st) : LaunchMmaF8<__nv_bfloat16, 128>(p, st);
+      else e = head_dim == 64 ? LaunchMmaF8<float, 64>(p, st) : LaunchMmaF8<float, 128>(p, st);
+    } else if (q_dtype == TLALOC_B200_BF16) {
       e = head_dim == 64 ? LaunchMma<__nv_bfloat16, 64>(p, st) : LaunchMma<__nv_bfloat16, 128>(p, st);
     } else {
       e = head_dim == 64 ? LaunchMma<float, 64>(p, st) : LaunchMma<float, 128>(p, st);
     }
   } else if (q_dtype == TLALOC_B200_F32 && kv_dtype == TLALOC_B200_F32) {
     e = LaunchGeneric<float, float>(p, st);
-  } else if (q_dtype == TLALOC_B200_F32) {
+  } else if (q_dtype == TLALOC_B200_F32 && kv_dtype == TLALOC_B200_BF16) {
     e = LaunchGeneric<float, __nv_bfloat16>(p, st);
+  } else if (q_dtype == TLALOC_B200_F32) {
+    e = LaunchGeneric<float, __nv_fp8_e4m3>(p, st);
   } else if (kv_dtype == TLALOC_B200_F32) {
     e = LaunchGeneric<__nv_bfloat16, float>(p, st);
-  } else {
+  } else if (kv_dtype == TLALOC_B200_BF16) {
     e = LaunchGeneric<__nv_bfloat16, __nv_bfloat16>(p, st);
+  } else {
+    e = LaunchGeneric<__nv_bfloat16, __nv_fp8_e4m3>(p, st);
   }
   if (e != cudaSuccess) return CudaFail("PAGED_ATTENTION slice launch", e);
   const unsigned cgrid = static_cast<unsigned>((p.R * p.H + kCombineThreads / 32 - 1) / (kCombineThreads / 32));
@@ -1073,27 +1448,22 @@ extern "C" int tlaloc_b200_kv_cache_write(void* pool, int32_t pool_dtype, const 
 {
   const char* op = "KV_CACHE_WRITE";
   if (!pool || !new_kv || !slot_mapping) return Fail(kInvalid, "%s: a required device pointer is null", op);
-  if (!IsFloatType(pool_dtype) || !IsFloatType(new_dtype)) return Fail(kInvalid, "%s: pool and rows must be f32 or bf16", op);
+  if (!IsPoolType(pool_dtype) || !IsFloatType(new_dtype)) return Fail(kInvalid, "%s: the pool must be f32, bf16 or f8e4m3fn, the rows f32 or bf16", op);
   if (num_tokens < 0 || row_elems < 1 || num_slots < 1) return Fail(kInvalid, "%s: bad sizes", op);
   if (num_tokens == 0) return kOk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int threads = row_elems >= 256 ? 256 : 128;
   cudaError_t e;
-  if (pool_dtype == TLALOC_B200_F32 && new_dtype == TLALOC_B200_F32) {
-    e = LaunchChained(KvCacheWriteKernel<float, float>, num_tokens, threads, 0, st, static_cast<float*>(pool),
-                      static_cast<const float*>(new_kv), slot_mapping, row_elems, num_slots);
-  } else if (pool_dtype == TLALOC_B200_F32) {
-    e = LaunchChained(KvCacheWriteKernel<float, __nv_bfloat16>, num_tokens, threads, 0, st, static_cast<float*>(pool),
-                      static_cast<const __nv_bfloat16*>(new_kv), slot_mapping, row_elems, num_slots);
-  } else if (new_dtype == TLALOC_B200_F32) {
-    e = LaunchChained(KvCacheWriteKernel<__nv_bfloat16, float>, num_tokens, threads, 0, st,
-                      static_cast<__nv_bfloat16*>(pool), static_cast<const float*>(new_kv), slot_mapping, row_elems,
-                      num_slots);
-  } else {
-    e = LaunchChained(KvCacheWriteKernel<__nv_bfloat16, __nv_bfloat16>, num_tokens, threads, 0, st,
-                      static_cast<__nv_bfloat16*>(pool), static_cast<const __nv_bfloat16*>(new_kv), slot_mapping,
-                      row_elems, num_slots);
-  }
+#define TLALOC_KVW(PT, NT)                                                                                    \
+  e = LaunchChained(KvCacheWriteKernel<PT, NT>, num_tokens, threads, 0, st, static_cast<PT*>(pool),           \
+                    static_cast<const NT*>(new_kv), slot_mapping, row_elems, num_slots)
+  if (pool_dtype == TLALOC_B200_F32 && new_dtype == TLALOC_B200_F32) TLALOC_KVW(float, float);
+  else if (pool_dtype == TLALOC_B200_F32) TLALOC_KVW(float, __nv_bfloat16);
+  else if (pool_dtype == TLALOC_B200_BF16 && new_dtype == TLALOC_B200_F32) TLALOC_KVW(__nv_bfloat16, float);
+  else if (pool_dtype == TLALOC_B200_BF16) TLALOC_KVW(__nv_bfloat16, __nv_bfloat16);
+  else if (new_dtype == TLALOC_B200_F32) TLALOC_KVW(__nv_fp8_e4m3, float);
+  else TLALOC_KVW(__nv_fp8_e4m3, __nv_bfloat16);
+#undef TLALOC_KVW
   if (e != cudaSuccess) return CudaFail("KV_CACHE_WRITE launch", e);
   CountLaunches(1);
   return kOk;

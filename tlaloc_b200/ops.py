@@ -11,7 +11,7 @@ import torch
 from . import _native as N
 from .attrs import PagedAttentionShape, parse_paged_attention
 
-_DT = {torch.float32: N.F32, torch.bfloat16: N.BF16, torch.int8: N.S8, torch.int32: N.S32}
+_DT = {torch.float32: N.F32, torch.bfloat16: N.BF16, torch.int8: N.S8, torch.int32: N.S32, torch.float8_e4m3fn: N.F8E4M3FN}
 
 
 def _dt(t: torch.Tensor) -> int:

@@ -432,6 +432,22 @@ def tp_parity(torch, dev, rank, world, group) -> dict:
         w64 = want.astype(np.float64)
         ref = w64 / np.sqrt((w64 * w64).mean(axis=1, keepdims=True) + 1e-5) * gain.cpu().numpy().astype(np.float64)[None, :]
         norm_ok = bool(np.all(np.abs(normed.float().cpu().numpy() - ref) <= np.abs(ref) * 2.0 ** -7 + 1e-6))
+    if peer.can_sum_rows(0):  # the one-barrier form the decode step uses: residual + partials in rank order, kept locally
+        res_h = rank_input(99, 4)
+        peer.tensors[0].copy_(torch.from_numpy(rank_input(rank, 4)))
+        res = torch.from_numpy(res_h).to(dev)
+        out = torch.empty(shape, dtype=torch.float32, device=dev)
+        normed = torch.empty(shape, dtype=torch.bfloat16, device=dev)
+        gain = torch.from_numpy(np.random.default_rng(77).uniform(0.5, 1.5, size=shape[1]).astype(np.float32)).to(dev)
+        peer.sum_rows_(0, res, out, gain, 1e-5, norm_out=normed)
+        want = res_h + rank_input(0, 4)
+        for q in range(1, world):
+            want = want + rank_input(q, 4)
+        sum_exact &= bool(np.array_equal(out.cpu().numpy(), want))
+        w64 = want.astype(np.float64)
+        ref = w64 / np.sqrt((w64 * w64).mean(axis=1, keepdims=True) + 1e-5) * gain.cpu().numpy().astype(np.float64)[None, :]
+        norm_ok &= bool(np.all(np.abs(normed.float().cpu().numpy() - ref) <= np.abs(ref) * 2.0 ** -7 + 1e-6))
+        torch.distributed.barrier(group=group)  # every rank has read every partial before the buffers go away
     status = peer.status()
     peer.close()
 
@@ -525,7 +541,8 @@ def run_ours(args) -> dict:
         "step_hbm": {"weights_bytes": stb["weights"], "kv_bytes": stb["kv"], "achieved_gbs": step_gbs, "frac": step_gbs / pk["hbm_gbs"]},
     }
     if world > 1:
-        line["config"]["rank_sum"] = "peer-memory kernel" if dec.peer is not None else "nccl"
+        line["config"]["rank_sum"] = ("peer-memory kernel, one barrier (every rank sums all partials)" if dec.one_shot
+                                      else "peer-memory kernel, reduce-scatter + all-gather" if dec.peer is not None else "nccl")
         line["exchange_status"] = dec.exchange_status()  # 0: no bounded wait of the exchange kernel ever gave up
         line["tp_parity"] = parity
     if world == 1 and not args.lean:
@@ -741,6 +758,17 @@ def run_peer_sum(args) -> dict:
         row = {"shape": list(shp), "bytes": 4 * shp[0] * shp[1], "peer_us": timed(lambda: peer.all_reduce_(0))}
         if peer.can_fuse_norm(0):
             row["peer_with_rmsnorm_us"] = timed(lambda: peer.all_reduce_norm_(0, gain, 1e-5))
+        if peer.can_sum_rows(0):
+            two = PeerBuffers([shp, shp], rank=rank, world=world, group=group, device=dev)
+            hbuf = torch.zeros(shp, device=dev)
+            hn = torch.empty(shp, device=dev, dtype=torch.bfloat16)
+            turn = [0]
+
+            def one_barrier():
+                two.sum_rows_(turn[0] & 1, hbuf, hbuf, gain, 1e-5, norm_out=hn)
+                turn[0] += 1
+            row["one_barrier_with_residual_and_rmsnorm_us"] = timed(one_barrier)
+            row["exchange_status_one_barrier"] = two.status()
         row["nccl_us"] = timed(lambda: torch.distributed.all_reduce(priv, group=group))
         row["exchange_status"] = peer.status()
         rows.append(row)

@@ -295,6 +295,23 @@ int tlaloc_b200_peer_allreduce_rmsnorm_f32(void* const* bases, size_t data_offse
                                            uint32_t* state, const float* gain, float eps, int32_t rank, int32_t world,
                                            int32_t rows, int32_t cols, void* stream);
 
+/*
+ * The one-barrier form of the same sum, for the decode step: out = residual + sum over ranks of an f32 [rows, cols]
+ * PARTIAL matrix at partial_offset of every rank's buffer, added in rank order (identical bits on every rank), kept in
+ * this rank's LOCAL memory, with the RMSNorm that follows it: norm_out (bf16 [rows, cols], local, or NULL) = out *
+ * rsqrt(mean(out^2) + eps) * gain.  Each rank reads every rank's partial; nothing is stored to a peer, so there is one
+ * rendezvous (before the reads) instead of two.  What the caller owes for that: a rank must not overwrite this partial
+ * buffer until it has completed ONE MORE call of this function (on another partial buffer, e.g. alternating between
+ * two): every peer passes that call's rendezvous only after its reads of this one are done.
+ *   residual  local f32 [rows, cols] or NULL; may equal out (the residual stream updated in place)
+ *   flag words (world of them at flag_offset) and state as tlaloc_b200_peer_allreduce_f32; calls of the three functions
+ *   may be mixed on one state if every rank makes the same calls in the same order.
+ * cols a multiple of 4 up to 8192.  world == 1 is legal (out = residual + partial).
+ */
+int tlaloc_b200_peer_sum_rows_f32(void* const* bases, size_t partial_offset, size_t flag_offset, uint32_t* state,
+                                  const float* residual, float* out, void* norm_out, const float* gain, float eps,
+                                  int32_t rank, int32_t world, int32_t rows, int32_t cols, void* stream);
+
 /* ------------------------------------------------------------------ XLA typed-FFI registration */
 
 struct PJRT_Api;

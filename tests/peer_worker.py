@@ -79,7 +79,69 @@ def main():
         for i in (0, 1):
             assert np.array_equal(peer.tensors[i].cpu().numpy(), expected(shapes[i], round_)), (i, rep)
     assert peer.status() == 0
-    assert int(peer.state[0].item()) == 3 * len(shapes) + 2 + 2 + 3 * 20
+    calls = 3 * len(shapes) + 2 + 2 + 3 * 20
+    assert int(peer.state[0].item()) == calls
+    # The one-barrier form: out = residual + the ranks' partials in rank order, kept locally, with the RMSNorm.  Two
+    # partial buffers in turn (tensors 1 and a twin), eagerly and from a CUDA graph.
+    twin = PeerBuffers([shapes[1], shapes[1]], rank=rank, world=world, group=torch.distributed.group.WORLD, device=dev)
+    res = torch.empty(shapes[1], device=dev)
+    out = torch.empty(shapes[1], device=dev)
+    normed = torch.empty(shapes[1], device=dev, dtype=torch.bfloat16)
+
+    def check_one_shot(round_, which, use_res, gain_t):
+        want = expected(shapes[1], round_)
+        if use_res:
+            r = rank_input(shapes[1], 99, round_)
+            acc = r + rank_input(shapes[1], 0, round_)  # residual first, then the partials in rank order
+            for q in range(1, world):
+                acc = acc + rank_input(shapes[1], q, round_)
+            want = acc
+        assert np.array_equal(out.cpu().numpy(), want), (round_, which, use_res)
+        w64 = want.astype(np.float64)
+        ref = w64 / np.sqrt((w64 * w64).mean(axis=1, keepdims=True) + 1e-5)
+        if gain_t is not None:
+            ref = ref * gain_t.cpu().numpy().astype(np.float64)[None, :]
+        got = normed.float().cpu().numpy().astype(np.float64)
+        assert np.all(np.abs(got - ref) <= np.abs(ref) * 2.0 ** -7 + 1e-6), float(np.abs(got - ref).max())
+
+    for rep in range(4):
+        round_ += 1
+        which, use_res = rep % 2, rep >= 1
+        twin.tensors[which].copy_(torch.from_numpy(rank_input(shapes[1], rank, round_)))
+        if use_res:
+            res.copy_(torch.from_numpy(rank_input(shapes[1], 99, round_)))
+        twin.sum_rows_(which, res if use_res else None, out, gain if rep != 2 else None, 1e-5, norm_out=normed)
+        check_one_shot(round_, which, use_res, gain if rep != 2 else None)
+    # in place on the residual stream, replayed from a graph: h += sum(partial 0); h += sum(partial 1); ten times
+    hbuf = torch.zeros(shapes[1], device=dev)
+    srcs = [torch.empty(shapes[1], device=dev) for _ in range(2)]
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        for i in (0, 1):
+            twin.tensors[i].copy_(srcs[i])
+            twin.sum_rows_(i, hbuf, hbuf, gain, 1e-5, norm_out=normed)
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    torch.distributed.barrier()
+    g2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g2):
+        for _ in range(10):
+            for i in (0, 1):
+                twin.tensors[i].copy_(srcs[i])
+                twin.sum_rows_(i, hbuf, hbuf, gain, 1e-5, norm_out=normed)
+    round_ += 1
+    parts = [rank_input(shapes[1], q, round_) * np.float32(2.0 ** -6) for q in range(world)]
+    srcs[0].copy_(torch.from_numpy(parts[rank]))
+    srcs[1].copy_(torch.from_numpy(parts[rank] * np.float32(0.5)))
+    hbuf.zero_()
+    g2.replay()
+    want = np.zeros(shapes[1], np.float32)
+    for _ in range(10):
+        for scale_ in (np.float32(1.0), np.float32(0.5)):
+            for q in range(world):
+                want = want + parts[q] * scale_
+    assert np.array_equal(hbuf.cpu().numpy(), want)
+    assert twin.status() == 0 and int(twin.state[0].item()) == 4 + 2 + 20
     torch.distributed.barrier()
     torch.cuda.synchronize(dev)
     if rank == 0:

@@ -48,37 +48,28 @@ struct TcParams {
   int M, K, N;
   int Kc, ks;
   int weights_const;  // codes and scales are not written by the preceding kernel: fetch them before the dependency wait
-  int prefetch;       // blocks ahead of the tensor core at which a block's weights are asked into L2 (0 = never)
-  int prefetch_bulk;  // 1: through the bulk-copy unit (one request per 256-byte row), 0: one request per line
 };
 
 constexpr int kTcThreads = 512;                    // converter threads (16 warps)
-constexpr int kTcLaunchThreads = kTcThreads + 64;  // plus the warp whose first lane issues the MMAs and the L2 prefetch warp
 constexpr int kTcBN = 256;                         // output columns per CTA: the N of one MMA
 constexpr int kTcBK = 64;                          // k rows per block
 constexpr int kTcWBytes = kTcBN * kTcBK * 2;       // one block's weights as bf16
 constexpr int kTcTileStride = kTcBN + 4;
 constexpr uint32_t kTcSpinLimit = 1u << 22;
 
-// $TLALOC_B200_GEMM_PREFETCH: how many blocks ahead of the tensor core the weights are asked into L2 (default 8).
-int TcPrefetchDistance()
-{
-  static const int v = [] {
-    const char* e = std::getenv("TLALOC_B200_GEMM_PREFETCH");
-    const int x = e != nullptr ? std::atoi(e) : 8;
-    return x < 0 ? 0 : x > 64 ? 64 : x;
-  }();
-  return v;
-}
-
 __device__ int g_tc_status = 0;  // nonzero after an mbarrier wait timed out (sticky until read)
 
 // Shared memory: [activation strips, kBufs][bf16 weight tiles, kBufs][mbarriers, TMEM base].  An MMA always reads
 // 128 activation rows; with MPAD < 128 the rows past MPAD are whatever follows in shared memory, which only reaches
 // accumulator lanes that are never read.
-template <int MPAD>
+// AT ("A in TMEM", MPAD <= 128): the activation strip does not pass through shared memory at all; four extra warps
+// copy it from global memory to registers and on to tensor memory (tcgen05.st), where the MMA reads its A operand.
+// Shared memory then carries only the converted weights (written once, read once by the tensor core): a third less
+// traffic on what the profile shows to be the busiest unit of this kernel.
+template <int MPAD, bool AT = false>
 struct TcLayout {
-  static constexpr int kXBytes = MPAD * kTcBK * 2;
+  static_assert(!AT || MPAD <= 128, "two accumulators fill tensor memory: no room for the strip");
+  static constexpr int kXBytes = AT ? 0 : MPAD * kTcBK * 2;
   // Converter groups: group g converts blocks g, g + kGroups, ...  There are as many buffers as groups, so a buffer
   // always belongs to the same group and the parity a group waits for can only be the barrier's latest phase.
   static constexpr int kGroups = MPAD > 128 ? 2 : 4;
@@ -97,7 +88,12 @@ struct TcLayout {
   static constexpr int kScaleOffset = kBarOffset + 128;
   static constexpr int kBytes = kScaleOffset + kTcBN * 4 + 1024;  // slack to align to 1024
   static constexpr int kAccs = MPAD > 128 ? 2 : 1;  // accumulators of 128 activation rows x 256 columns
-  static constexpr int kTmemCols = kAccs * kTcBN;
+  static constexpr int kStripCols = kTcBK / 2;      // AT: a strip buffer is 64 bf16 per lane = 32 columns of 32 bits
+  static constexpr int kStripCol0 = kAccs * kTcBN;  // AT: the strip buffers follow the accumulator
+  static constexpr int kTmemCols = AT ? 512 : kAccs * kTcBN;  // a power of two >= 256 + 4 * 32
+  static constexpr int kStripWarps = AT ? 4 : 0;
+  static constexpr int kLaunchThreads = kTcThreads + 32 + 32 * kStripWarps;
+  static constexpr int kConvArrivals = kGroupWarps + kStripWarps;  // arrivals that complete a block's conv_done phase
   static_assert(kXBytes % 1024 == 0, "operand tiles start on 1024-byte boundaries");
 };
 
@@ -157,18 +153,13 @@ __device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count)
 {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
 }
-// One lane polls for the warp (32 pollers per warp would spend the SM's issue slots on the wait itself).
-__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity);
-__device__ __forceinline__ bool MbarWaitWarp(uint32_t bar, uint32_t parity, int lane)
+// Waits for the phase with the given parity.  Bounded twice over: a wait gives up after kTcWaitNs of wall time, and the
+// first wait of a CTA that gives up raises the CTA's abort word in shared memory, which every other wait polls, so a
+// pipeline that has stopped costs one time limit and not one per block.  Returns false when it gave up.
+constexpr unsigned long long kTcWaitNs = 200ull * 1000ull * 1000ull;  // 0.2 s: a block takes under a microsecond
+__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word)
 {
-  int ok = 1;
-  if (lane == 0) ok = MbarWait(bar, parity) ? 1 : 0;
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  return ok != 0;
-}
-// Waits for the phase with the given parity; gives up after kTcSpinLimit polls.  Returns false on a time-out.
-__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity)
-{
+  unsigned long long t0 = 0;
   for (uint32_t i = 0; i < kTcSpinLimit; ++i) {
     uint32_t done;
     asm volatile(
@@ -179,8 +170,24 @@ __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity)
         : "r"(bar), "r"(parity)
         : "memory");
     if (done) return true;
+    if ((i & 31u) == 31u) {
+      if (*abort_word != 0u) return false;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kTcWaitNs) break;
+    }
   }
+  *abort_word = 1u;
   return false;
+}
+// One lane polls for the warp (32 pollers per warp would spend the SM's issue slots on the wait itself).
+__device__ __forceinline__ bool MbarWaitWarp(uint32_t bar, uint32_t parity, int lane, volatile uint32_t* abort_word)
+{
+  int ok = 1;
+  if (lane == 0) ok = MbarWait(bar, parity, abort_word) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
 }
 
 // Shared-memory matrix descriptor of a 128-byte-swizzled operand tile: start address, leading and stride byte offsets
@@ -196,16 +203,6 @@ __host__ __device__ constexpr uint32_t InstrDesc()
 {
   return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(kTcBN >> 3) << 17) | (8u << 24);
 }
-// Asks the memory system to bring `bytes` (a multiple of 16, from a 16-byte aligned address) into L2; no data returns.
-// bulk: one request for the whole run through the bulk-copy unit; otherwise one request per 128-byte line.
-__device__ __forceinline__ void PrefetchL2(const int8_t* ptr, uint32_t bytes, bool bulk)
-{
-  if (bulk) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(ptr), "r"(bytes) : "memory");
-  } else {
-    for (uint32_t o = 0; o < bytes; o += 128) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(ptr + o) : "memory");
-  }
-}
 __device__ __forceinline__ void TcMma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
 {
   asm volatile(
@@ -213,6 +210,27 @@ __device__ __forceinline__ void TcMma(uint32_t d_tmem, uint64_t a_desc, uint64_t
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The same MMA with the A operand in tensor memory (lane = row, one 32-bit column = two consecutive k).
+__device__ __forceinline__ void TcMmaTs(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 registers of every lane of the warp into 32 consecutive columns of the lane's own row of tensor memory.
+__device__ __forceinline__ void TcSt32(uint32_t taddr, const uint32_t* r)
+{
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+      "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
 __device__ __forceinline__ void TcCommit(uint32_t bar)
@@ -290,10 +308,13 @@ __device__ __forceinline__ void ClusterReduceRows(cg::cluster_group& cluster, fl
   }
 }
 
-template <int MPAD, typename YT>
-__global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams p)
+// 96 registers per thread for both forms: 17 warps (544 threads) or, with the four strip warps, 21 warps (672 threads:
+// 21 x 32 x 96 = 64512 of the SM's 65536 registers).  Stated as a register count and not as launch bounds, which
+// would round the 672 threads up and leave the converters' loop 80 registers.
+template <int MPAD, typename YT, bool AT>
+__global__ void __maxnreg__(96) Int8GemmTcKernel(TcParams p)
 {
-  using L = TcLayout<MPAD>;
+  using L = TcLayout<MPAD, AT>;
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment of the operand tiles (the swizzle is a function of address bits 4..9).
   const uint32_t smem_base = (SmemAddr(smem_raw) + 1023u) & ~1023u;
@@ -308,11 +329,13 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
   const uint32_t mma_done0 = smem_base + L::kBarOffset, conv_done0 = mma_done0 + 8 * L::kBufs;
   const uint32_t tmem_slot_addr = smem_base + L::kBarOffset + 64;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + 64);
+  volatile uint32_t* abort_word = tmem_slot + 1;  // raised by the first wait that gives up
 
   if (tid == 0) {
+    *abort_word = 0u;
     for (int i = 0; i < L::kBufs; ++i) {
       MbarInit(mma_done0 + 8 * i, 1);
-      MbarInit(conv_done0 + 8 * i, L::kGroupWarps);
+      MbarInit(conv_done0 + 8 * i, L::kConvArrivals);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -361,20 +384,8 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
   // Everything above touched only shared memory and TMEM.  The weights and scales are the first global reads; when
   // the caller says no preceding kernel writes them they are requested BEFORE the dependency wait, so the coldest
   // loads of the launch travel while the predecessor drains.  The activations always come after it.
-  // Block bp of this CTA into L2, by the lanes of the prefetch warp: rows lane and lane + 32, the tile's columns.
-  const uint32_t tile_bytes = static_cast<uint32_t>(min(kTcBN, p.N - col0));
-  auto prefetch_block = [&](int bp) {
-    if (bp >= nblocks) return;
-    const int row = kb0 + bp * kTcBK + lane;
-    const int8_t* src = p.w + static_cast<size_t>(row) * p.N + col0;
-    if (row < ke) PrefetchL2(src, tile_bytes, p.prefetch_bulk != 0);
-    if (row + 32 < ke) PrefetchL2(src + static_cast<size_t>(32) * p.N, tile_bytes, p.prefetch_bulk != 0);
-  };
   uint4 wreg[kChunks];
   if (!p.weights_const) GridDependencySync();
-  if (warp == kTcThreads / 32 + 1 && p.prefetch > 0) {  // the blocks the converters do not already hold in registers
-    for (int bp = kG; bp < p.prefetch; ++bp) prefetch_block(bp);
-  }
 #pragma unroll
   for (int i = 0; i < kChunks; ++i)
     wreg[i] = LdWeights16(wp + static_cast<size_t>(grp) * blk + i * pass, col_ok && kb0 + grp * kTcBK + row0 + kRP * i < ke);
@@ -387,9 +398,9 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
     for (int b = grp; b < nblocks; b += kG) {
       const int buf = b % L::kBufs;
       // Block b - kBufs used this weight tile and this strip buffer.
-      if (b >= L::kBufs) ok = MbarWaitWarp(mma_done0 + buf * 8, ((b / L::kBufs) - 1) & 1, lane) && ok;
+      if (b >= L::kBufs) ok = MbarWaitWarp(mma_done0 + buf * 8, ((b / L::kBufs) - 1) & 1, lane, abort_word) && ok;
       const int k0 = kb0 + b * kTcBK;
-      {
+      if constexpr (!AT) {
         const uint32_t st = smem_base + buf * L::kXBytes + xdst0;
         const __nv_bfloat16* src = xsrc0 + b * kTcBK;
         if (k0 + kTcBK <= ke) {
@@ -431,7 +442,7 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
       // Uniform over the CTA: the next block exists, is a whole block, and the tile has all its 256 columns.
       if (tile_full && k0 + (kG + 1) * kTcBK <= ke) convert_block(std::true_type{});
       else convert_block(std::false_type{});
-      CpAsyncWait<0>();  // this thread's part of the strip has landed
+      if constexpr (!AT) CpAsyncWait<0>();  // this thread's part of the strip has landed
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // these writes (and the cp.async strip) -> tensor core
       __syncwarp();
       if (lane == 0) {
@@ -448,31 +459,67 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
       const uint64_t a_desc0 = SmemDesc(smem_base, 16, 1024), b_desc0 = SmemDesc(smem_base + L::kWOffset, 8192, 1024);
       for (int b = 0; b < nblocks; ++b) {
         const int buf = b % L::kBufs;
-        ok = MbarWait(conv_done0 + buf * 8, (b / L::kBufs) & 1) && ok;
+        ok = MbarWait(conv_done0 + buf * 8, (b / L::kBufs) & 1, abort_word) && ok;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((buf * L::kXBytes) >> 4);
         const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((buf * kTcWBytes) >> 4);
 #pragma unroll
         for (int ks = 0; ks < kTcBK / 16; ++ks) {
 #pragma unroll
-          for (int acc = 0; acc < L::kAccs; ++acc)
-            TcMma(tmem_base + acc * kTcBN, a_desc + static_cast<uint64_t>((acc * 16384 + ks * 32) >> 4),
-                  b_desc + static_cast<uint64_t>((ks * 2048) >> 4), idesc, (b > 0 || ks > 0) ? 1u : 0u);
+          for (int acc = 0; acc < L::kAccs; ++acc) {
+            if constexpr (AT) {
+              TcMmaTs(tmem_base, tmem_base + L::kStripCol0 + buf * L::kStripCols + ks * 8,
+                      b_desc + static_cast<uint64_t>((ks * 2048) >> 4), idesc, (b > 0 || ks > 0) ? 1u : 0u);
+            } else {
+              TcMma(tmem_base + acc * kTcBN, a_desc + static_cast<uint64_t>((acc * 16384 + ks * 32) >> 4),
+                    b_desc + static_cast<uint64_t>((ks * 2048) >> 4), idesc, (b > 0 || ks > 0) ? 1u : 0u);
+            }
+          }
         }
         TcCommit(mma_done0 + buf * 8);
       }
       // The last commit covers every MMA before it.  Its phase is unambiguous here: the converters of the last block
       // had already waited for the same barrier's previous phase.
-      if (nblocks > 0) ok = MbarWait(mma_done0 + ((nblocks - 1) % L::kBufs) * 8, ((nblocks - 1) / L::kBufs) & 1) && ok;
+      if (nblocks > 0) ok = MbarWait(mma_done0 + ((nblocks - 1) % L::kBufs) * 8, ((nblocks - 1) / L::kBufs) & 1, abort_word) && ok;
     }
-  } else if (p.prefetch > 0) {
-    // The prefetch warp: keeps the weights `prefetch` blocks ahead of the tensor core on their way into L2, so that the
-    // converters' register loads (which run one group period ahead and are limited by the registers a thread can
-    // spare) meet L2's latency, not HBM's.  It paces itself on the MMA completions, as an onlooker of those barriers;
-    // a wait that runs out only ends the prefetching.
-    for (int b = 0; b + p.prefetch < nblocks; ++b) {
-      if (!MbarWaitWarp(mma_done0 + (b % L::kBufs) * 8, (b / L::kBufs) & 1, lane)) break;
-      prefetch_block(b + p.prefetch);
+  } else if constexpr (AT) {
+    // The strip warps: warp w serves tensor-memory lanes 32 (w % 4) .. + 31, one activation row per lane.  A block's
+    // 64 k of a row are 128 contiguous bytes in global memory and, two k per 32-bit column, exactly the 32 registers a
+    // tcgen05.st of 32 columns takes.  The next block's row is requested before this one is stored, so the loop runs
+    // at the latency of one trip to L2 (the activations of a launch are a few megabytes, read by every CTA), well
+    // ahead of the converters; it is held back only by the buffers (a strip buffer is freed with its weight tile).
+    const int m = 32 * (warp & 3) + lane;
+    const bool row_ok = m < p.M;
+    const __nv_bfloat16* xrow = p.x + static_cast<size_t>(row_ok ? m : 0) * p.K + kb0;
+    auto load_row = [&](int b, uint4(&v)[8]) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int k = kb0 + b * kTcBK + 8 * i;
+        v[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (row_ok && b < nblocks && k < ke) v[i] = __ldg(reinterpret_cast<const uint4*>(xrow + b * kTcBK + 8 * i));
+      }
+    };
+    uint4 cur[8], nxt[8];
+    load_row(0, cur);
+    for (int b = 0; b < nblocks; ++b) {
+      load_row(b + 1, nxt);
+      const int buf = b % L::kBufs;
+      if (b >= L::kBufs) ok = MbarWaitWarp(mma_done0 + buf * 8, ((b / L::kBufs) - 1) & 1, lane, abort_word) && ok;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      uint32_t regs[32];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        regs[4 * i] = cur[i].x; regs[4 * i + 1] = cur[i].y; regs[4 * i + 2] = cur[i].z; regs[4 * i + 3] = cur[i].w;
+      }
+      TcSt32(tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + L::kStripCol0 + buf * L::kStripCols, regs);
+      asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(conv_done0 + buf * 8) : "memory");
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
     }
   }
   if (!ok) atomicExch(&g_tc_status, 1);
@@ -570,7 +617,22 @@ __global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams
 template <int MPAD, typename YT>
 cudaError_t PrepareTc()
 {
-  return cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD>::kBytes);
+  cudaError_t e = cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD, false>::kBytes);
+  if constexpr (MPAD <= 128) {
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD, true>::kBytes);
+  }
+  return e;
+}
+
+// $TLALOC_B200_GEMM_A=smem keeps the activation strip in shared memory for every shape (up to 128 rows it otherwise goes
+// through tensor memory).
+bool TcStripInTmem()
+{
+  static const bool v = [] {
+    const char* e = std::getenv("TLALOC_B200_GEMM_A");
+    return e == nullptr || std::string(e) != "smem";
+  }();
+  return v;
 }
 
 template <int MPAD, typename YT>
@@ -578,13 +640,20 @@ cudaError_t LaunchTc(const TcParams& p, cudaStream_t stream)
 {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + kTcBN - 1) / kTcBN, p.ks, 1);
-  cfg.blockDim = dim3(kTcLaunchThreads, 1, 1);
-  cfg.dynamicSmemBytes = TcLayout<MPAD>::kBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   cfg.numAttrs = ChainAttributes(attr, p.ks);
   cfg.attrs = attr;
-  return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT>, p);
+  if constexpr (MPAD <= 128) {
+    if (TcStripInTmem()) {
+      cfg.blockDim = dim3(TcLayout<MPAD, true>::kLaunchThreads, 1, 1);
+      cfg.dynamicSmemBytes = TcLayout<MPAD, true>::kBytes;
+      return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT, true>, p);
+    }
+  }
+  cfg.blockDim = dim3(TcLayout<MPAD, false>::kLaunchThreads, 1, 1);
+  cfg.dynamicSmemBytes = TcLayout<MPAD, false>::kBytes;
+  return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT, false>, p);
 }
 
 // CTAs of the kernel that can be resident at once when launched as clusters of ks (index [device][MPAD class][ks]);
@@ -598,8 +667,8 @@ void FillTcSlots(int device, int cls)
   for (int ks = 1; ks <= 8; ++ks) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(148, ks, 1);
-    cfg.blockDim = dim3(kTcLaunchThreads, 1, 1);
-    cfg.dynamicSmemBytes = TcLayout<MPAD>::kBytes;
+    cfg.blockDim = dim3(TcLayout<MPAD, true>::kLaunchThreads, 1, 1);
+    cfg.dynamicSmemBytes = TcLayout<MPAD, true>::kBytes;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
@@ -608,7 +677,7 @@ void FillTcSlots(int device, int cls)
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, Int8GemmTcKernel<MPAD, float>, &cfg) != cudaSuccess || clusters <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, Int8GemmTcKernel<MPAD, float, true>, &cfg) != cudaSuccess || clusters <= 0) {
       cudaGetLastError();
       clusters = (ks <= 2 ? 148 : ks <= 4 ? 128 : 112) / ks;  // a cautious guess when the query is not available
     }
@@ -691,12 +760,6 @@ cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const 
 {
   TcParams p;
   p.weights_const = weights_const ? 1 : 0;
-  p.prefetch = TcPrefetchDistance();
-  static const int bulk = [] {
-    const char* e = std::getenv("TLALOC_B200_GEMM_PREFETCH_BULK");
-    return e != nullptr ? std::atoi(e) : 0;
-  }();
-  p.prefetch_bulk = bulk;
   p.w = codes;
   p.scales = scales;
   p.K = k;

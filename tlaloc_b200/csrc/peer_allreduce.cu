@@ -285,6 +285,106 @@ PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, flo
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// The one-barrier form: out = residual + the sum over ranks of a partial matrix, with the following RMSNorm.
+//
+// Every rank reads every rank's partial (its own locally, the others over NVLink) and keeps the whole sum, added in
+// rank order, in LOCAL memory: nothing is stored to a peer, so the only rendezvous is the one before the reads ("every
+// partial is written").  There is no second barrier: a rank's partial buffer is next written two exchanges later (the
+// caller alternates between two partial buffers), and by then every peer has passed the arrival of the exchange in
+// between, which it enters only after its reads of this one have completed.  One CTA per row holds the row in
+// registers (cols <= 8192): 8 ranks x 4 vectors per thread in flight, the sum, the residual add, the row's sum of
+// squares, and the normalised bf16 row, all in one pass.  Per rank 7/8 of the matrix crosses NVLink inbound (as in
+// the two-phase form) but one flag round trip and the all-gather's store latency are gone.
+struct PeerSumTable
+{
+  const float* partial[kMaxRanks];
+  uint32_t* flags[kMaxRanks];
+};
+
+template <int W>
+__global__ void __launch_bounds__(kThreads, 1)
+PeerSumRowsKernel(PeerSumTable t, uint32_t* state, const float* residual, float* out, __nv_bfloat16* norm_out, const float* gain,
+                  float eps, int rank, int world_rt, int rows, int cols)
+{
+  GridDependencySync();
+  const int world = W > 0 ? W : world_rt;
+  __shared__ uint32_t s_epoch, s_dead;
+  __shared__ float red[kThreads / 32];
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    s_epoch = *reinterpret_cast<volatile uint32_t*>(state) + 1u;
+    s_dead = reinterpret_cast<volatile uint32_t*>(state)[2];
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const bool dead = s_dead != 0;
+  const unsigned long long limit_ns = WaitLimitNs(state);
+  // arrive: my partial is written (the producing kernel has completed: stream order); every CTA then waits, on LOCAL
+  // flag words, until every rank has said the same.
+  if (blockIdx.x == 0 && tid < world) StoreFlag(t.flags[tid] + rank, epoch);
+  if (!dead && tid < world) {
+    if (!WaitFlag(t.flags[rank] + tid, epoch, limit_ns)) atomicCAS(state + 2, 0u, 1u + tid);
+  }
+  __syncthreads();
+
+  const int row4 = cols >> 2;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t base = static_cast<size_t>(row) * cols;
+    float4 sum[kNormVec];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormVec; ++i) {
+      const int c = tid + i * kThreads;
+      sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < row4) {
+        float4 v[kMaxRanks];
+#pragma unroll
+        for (int q = 0; q < kMaxRanks; ++q)
+          if (q < world) v[q] = LoadPeer(t.partial[q] + base + 4 * c);
+        float4 a = residual != nullptr ? *reinterpret_cast<const float4*>(residual + base + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (residual == nullptr) a = v[0];
+        else { a.x += v[0].x; a.y += v[0].y; a.z += v[0].z; a.w += v[0].w; }
+#pragma unroll
+        for (int q = 1; q < kMaxRanks; ++q)
+          if (q < world) { a.x += v[q].x; a.y += v[q].y; a.z += v[q].z; a.w += v[q].w; }
+        sum[i] = a;
+        *reinterpret_cast<float4*>(out + base + 4 * c) = a;
+        ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, fmaf(a.w, a.w, ss))));
+      }
+    }
+    if (norm_out != nullptr) {
+      const float total = BlockSum512(ss, red);
+      const float rsq = static_cast<float>(1.0 / sqrt(static_cast<double>(total / static_cast<float>(cols) + eps)));
+#pragma unroll
+      for (int i = 0; i < kNormVec; ++i) {
+        const int c = tid + i * kThreads;
+        if (c < row4) {
+          const float4 g = gain != nullptr ? __ldg(reinterpret_cast<const float4*>(gain) + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+          const float4 a = sum[i];
+          float n0 = __fmul_rn(a.x, rsq), n1 = __fmul_rn(a.y, rsq), n2 = __fmul_rn(a.z, rsq), n3 = __fmul_rn(a.w, rsq);
+          if (gain != nullptr) { n0 = __fmul_rn(n0, g.x); n1 = __fmul_rn(n1, g.y); n2 = __fmul_rn(n2, g.z); n3 = __fmul_rn(n3, g.w); }
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(n0, n1), hi = __floats2bfloat162_rn(n2, n3);
+          uint2 packed;
+          packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+          packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(norm_out + base + 4 * c) = packed;
+        }
+      }
+    }
+  }
+  // The last CTA to finish closes the epoch (no flags to send: nobody waits for this rank's reads).
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(state + 1, 1u) == gridDim.x - 1) {
+      state[1] = 0;
+      __threadfence();
+      state[0] = epoch;
+    }
+  }
+}
+
 }  // namespace
 
 int LaunchPeerAllReduce(void* const* bases, size_t data_offset, size_t flag_offset, uint32_t* state, int rank, int world,
@@ -360,6 +460,40 @@ int LaunchPeerAllReduceNorm(void* const* bases, size_t data_offset, size_t norm_
   return kOk;
 }
 
+int LaunchPeerSumRows(void* const* bases, size_t partial_offset, size_t flag_offset, uint32_t* state, const float* residual,
+                      float* out, void* norm_out, const float* gain, float eps, int rank, int world, int rows, int cols,
+                      cudaStream_t st)
+{
+  const char* op = "peer_sum_rows";
+  if (world < 1 || world > kMaxRanks) return Fail(kInvalid, "%s: world %d outside [1, %d]", op, world, kMaxRanks);
+  if (rank < 0 || rank >= world) return Fail(kInvalid, "%s: rank %d outside [0, %d)", op, rank, world);
+  if (!bases || !state || !out) return Fail(kInvalid, "%s: null base table, state or out", op);
+  if (rows < 1 || cols < 4 || cols % 4 != 0 || cols > 4 * kNormVec * kThreads) {
+    return Fail(kInvalid, "%s: %d x %d: rows >= 1, cols a multiple of 4 up to %d", op, rows, cols, 4 * kNormVec * kThreads);
+  }
+  if (partial_offset % 16 != 0 || flag_offset % 4 != 0 || !Aligned16(residual) || !Aligned16(out) || !Aligned16(norm_out) || !Aligned16(gain)) {
+    return Fail(kInvalid, "%s: the partial offset, residual, out, norm_out and gain must be 16-byte aligned", op);
+  }
+  PeerSumTable t{};
+  for (int q = 0; q < world; ++q) {
+    if (!bases[q] || reinterpret_cast<uintptr_t>(bases[q]) % 16 != 0) return Fail(kInvalid, "%s: base of rank %d is null or not 16-byte aligned", op, q);
+    t.partial[q] = reinterpret_cast<const float*>(static_cast<const char*>(bases[q]) + partial_offset);
+    t.flags[q] = reinterpret_cast<uint32_t*>(static_cast<char*>(bases[q]) + flag_offset);
+  }
+  const int grid = rows < 148 ? rows : 148;
+  __nv_bfloat16* nout = static_cast<__nv_bfloat16*>(norm_out);
+  cudaError_t e;
+  switch (world) {
+    case 2: e = LaunchChained(PeerSumRowsKernel<2>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols); break;
+    case 4: e = LaunchChained(PeerSumRowsKernel<4>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols); break;
+    case 8: e = LaunchChained(PeerSumRowsKernel<8>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols); break;
+    default: e = LaunchChained(PeerSumRowsKernel<0>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols); break;
+  }
+  if (e != cudaSuccess) return CudaFail("peer_sum_rows launch", e);
+  CountLaunches(1);
+  return kOk;
+}
+
 }  // namespace tlaloc_b200
 
 using namespace tlaloc_b200;
@@ -418,4 +552,12 @@ extern "C" int tlaloc_b200_peer_allreduce_rmsnorm_f32(void* const* bases, size_t
 {
   return LaunchPeerAllReduceNorm(bases, data_offset, norm_offset, flag_offset, state, gain, eps, rank, world, rows, cols,
                                  static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tlaloc_b200_peer_sum_rows_f32(void* const* bases, size_t partial_offset, size_t flag_offset, uint32_t* state,
+                                             const float* residual, float* out, void* norm_out, const float* gain, float eps,
+                                             int32_t rank, int32_t world, int32_t rows, int32_t cols, void* stream)
+{
+  return LaunchPeerSumRows(bases, partial_offset, flag_offset, state, residual, out, norm_out, gain, eps, rank, world, rows, cols,
+                           static_cast<cudaStream_t>(stream));
 }

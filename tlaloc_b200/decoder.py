@@ -97,17 +97,24 @@ class Decoder:
         self.slot_mapping = torch.full((B,), -1, **i32)
         # step buffers
         nqkv = (self.hq + 2 * self.hk) * hd
-        # the two residual-stream buffers; under tensor parallelism they live in peer-mapped memory and are summed by
-        # the library's own exchange kernel (TLALOC_B200_TP_REDUCE=nccl keeps them private and calls NCCL instead)
-        self.peer = None
-        if world > 1 and os.environ.get("TLALOC_B200_TP_REDUCE", "peer") == "peer":
+        # Tensor parallelism, the sum over ranks after o_proj and down_proj.  $TLALOC_B200_TP_REDUCE:
+        #   "peer" (default)  the library's one-barrier kernel: the projections write their partial results into two
+        #                     alternating peer-mapped buffers, and every rank builds residual + sum (and the next
+        #                     RMSNorm) locally from all ranks' partials;
+        #   "peer2"           the two-phase in-place kernel (reduce-scatter + all-gather over the residual buffers);
+        #   "nccl"            NCCL's all-reduce on private buffers.
+        self.peer, self.one_shot = None, False
+        mode = os.environ.get("TLALOC_B200_TP_REDUCE", "peer") if world > 1 else "none"
+        if mode in ("peer", "peer2"):
             self.peer = PeerBuffers([(B, d), (B, d)], rank=rank, world=world, group=group, device=dev, norm_shape=(B, d))
-            self.h, self.h2 = self.peer.tensors
+            self.one_shot = mode == "peer" and self.peer.can_sum_rows(0)
+        if self.peer is not None and not self.one_shot:
+            self.h, self.h2 = self.peer.tensors  # summed in place
         else:
             self.h = torch.empty((B, d), **f32)
             self.h2 = torch.empty((B, d), **f32)
-        # RMSNorm output; with the peer-memory sum it lives in the peer block and the exchange kernel fills it
-        self.fuse_norm = (self.peer is not None and self.peer.can_fuse_norm(0)
+        # RMSNorm output; with the two-phase peer sum it lives in the peer block and the exchange kernel fills it
+        self.fuse_norm = (self.peer is not None and not self.one_shot and self.peer.can_fuse_norm(0)
                           and os.environ.get("TLALOC_B200_TP_FUSE_NORM", "1") != "0")
         self.hn = self.peer.norm_out if self.fuse_norm else torch.empty((B, d), **bf)
         self.qkv = torch.empty((B, nqkv), **f32)
@@ -203,14 +210,14 @@ class Decoder:
             ops.set_order_faithful(before)
 
     def _launch_step(self) -> None:
+        if self.one_shot:
+            return self._launch_step_one_shot()
         cfg, B = self.cfg, self.batch
         hd, hq, hk = cfg.head_dim, self.hq, self.hk
         ops.embedding(self.embed, self.token_ids, out=self.h)
         h, h2 = self.h, self.h2
         res_rank = self.rank == 0  # under tensor parallelism the residual enters the all-reduced sum once
-        q3 = self.qkv[:, :hq * hd].unflatten(1, (hq, hd))
-        k3 = self.qkv[:, hq * hd:(hq + hk) * hd].unflatten(1, (hk, hd))
-        v3 = self.qkv[:, (hq + hk) * hd:].unflatten(1, (hk, hd))
+        q3, k3, v3 = self._qkv_views()
         fused = self.fuse_norm  # the sum over ranks also produces the next RMSNorm's output
         for l, lw in enumerate(self.layers):
             if l == 0 or not fused:
@@ -236,6 +243,39 @@ class Decoder:
                 self._all_reduce(h)
         if not fused:
             ops.rmsnorm(h, self.final_norm, cfg.rms_eps, out=self.hn)
+        self._head_and_greedy()
+
+    def _launch_step_one_shot(self) -> None:
+        """The tensor-parallel step on the one-barrier sum: the residual stream `h` is local and identical on every rank;
+        o_proj and down_proj write their partial results into the two peer buffers in turn, and the sum kernel adds
+        every rank's partial to `h` and leaves the next RMSNorm's output in `hn`."""
+        cfg, B = self.cfg, self.batch
+        hd, hq = cfg.head_dim, self.hq
+        ops.embedding(self.embed, self.token_ids, out=self.h)
+        h, (p_o, p_down) = self.h, self.peer.tensors
+        q3, k3, v3 = self._qkv_views()
+        ops.rmsnorm(h, self.layers[0]["ln1"], cfg.rms_eps, out=self.hn)
+        for l, lw in enumerate(self.layers):
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True)
+            ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
+                              self.value_pools[l], q_out=self.q_rot)
+            ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
+                                scale=cfg.scale, out=self.att, scratch=self.att_scratch)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], out=p_o, weights_const=True)
+            self.peer.sum_rows_(0, h, h, lw["ln2"], cfg.rms_eps, norm_out=self.hn)
+            self.gate_up_proj(lw)
+            ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
+            ops.int8_gemm(self.act, *lw["down"], out=p_down, weights_const=True)
+            nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
+            self.peer.sum_rows_(1, h, h, nxt, cfg.rms_eps, norm_out=self.hn)
+        self._head_and_greedy()
+
+    def _qkv_views(self):
+        hd, hq, hk = self.cfg.head_dim, self.hq, self.hk
+        return (self.qkv[:, :hq * hd].unflatten(1, (hq, hd)), self.qkv[:, hq * hd:(hq + hk) * hd].unflatten(1, (hk, hd)),
+                self.qkv[:, (hq + hk) * hd:].unflatten(1, (hk, hd)))
+
+    def _head_and_greedy(self) -> None:
         if isinstance(self.head, tuple):
             ops.int8_gemm(self.hn, *self.head, out=self.logits, weights_const=True)
         else:

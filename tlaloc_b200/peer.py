@@ -105,6 +105,26 @@ class PeerBuffers:
             torch.cuda.current_stream(self.device).cuda_stream))
         return t, self.norm_out
 
+    def sum_rows_(self, index: int, residual, out, gain, eps: float, norm_out=None):
+        """The one-barrier form: out = residual + sum over ranks of tensor `index` (every rank's partial, added in rank
+        order) into LOCAL `out` (f32, may be `residual` itself), and RMSNorm(out) * gain as bf16 into local `norm_out`.
+        The caller must not overwrite tensor `index` again before one more sum_rows_ (on another tensor) has run."""
+        t = self.tensors[index]
+        if t.dim() != 2 or tuple(out.shape) != tuple(t.shape) or out.dtype != torch.float32 or not out.is_contiguous():
+            raise ValueError("sum_rows_: out must be a contiguous f32 tensor of the partial's [rows, cols] shape")
+        if norm_out is not None and (tuple(norm_out.shape) != tuple(t.shape) or norm_out.dtype != torch.bfloat16 or not norm_out.is_contiguous()):
+            raise ValueError("sum_rows_: norm_out must be a contiguous bf16 tensor of the partial's shape")
+        N.check(N.lib().tlaloc_b200_peer_sum_rows_f32(
+            self._bases, self.offsets[index], self.flag_offset, self.state.data_ptr(),
+            None if residual is None else residual.data_ptr(), out.data_ptr(), None if norm_out is None else norm_out.data_ptr(),
+            None if gain is None else gain.data_ptr(), float(eps), self.rank, self.world, t.shape[0], t.shape[1],
+            torch.cuda.current_stream(self.device).cuda_stream))
+        return out
+
+    def can_sum_rows(self, index: int) -> bool:
+        t = self.tensors[index]
+        return t.dim() == 2 and t.shape[1] % 4 == 0 and t.shape[1] <= 8192
+
     def status(self) -> int:
         """0, or the code a timed-out wait left (1 + 16 * phase + the rank that did not arrive).  Synchronises."""
         return int(self.state[2].item())

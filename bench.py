@@ -350,7 +350,8 @@ class StepBench:
             b.record()
             torch.cuda.synchronize(dev)
             us = a.elapsed_time(b) / L * 1e3
-            byts = k * n + 4 * n + 2 * B * k + 4 * B * n
+            out_bytes = 2 * B * (n // 2) if (name == "gate_up" and dec.fuse_swiglu) else 4 * B * n  # SwiGLU folded in: bf16 [B, F]
+            byts = k * n + 4 * n + 2 * B * k + out_bytes
             flops = 2.0 * B * k * n
             floor_us = max(byts / pk["hbm_gbs"] / 1e3, flops / pk["bf16_tflops_sustained"] / 1e6)
             rows.append({"proj": name, "K": int(k), "N": int(n), "M": B, "us": us, "gbs": byts / us / 1e3,

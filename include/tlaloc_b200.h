@@ -209,6 +209,21 @@ int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_t* codes, c
                           int32_t m, int32_t k, int32_t n, int32_t flags, void* stream);
 
 /*
+ * The MLP's gate and up projections with SwiGLU folded into the epilogue (mlpOut, HfDecoderGraph.kt:953-988:
+ * silu(proj(x, gate)) * proj(x, up)): one pass over both weights, and the [M, 2F] intermediate never reaches memory.
+ *   codes   int8 [K, N], N = 2F a multiple of 256, the two weights interleaved in column blocks of 128: columns
+ *           256t .. 256t+127 are gate columns 128t .. 128t+127, columns 256t+128 .. 256t+255 the same up columns
+ *           (both in the staged [in, out] layout; tlaloc_b200.sharding.interleave_gate_up builds it at load time)
+ *   scales  f32 [N] in the same column order, or NULL
+ *   y       [M, F] F32 | BF16: silu(gate * scale) * (up * scale), SiLU in f32 as tlaloc_b200_swiglu computes it
+ * More than 32 rows run on the tensor-core kernel; fewer rows, unaligned pointers, parity mode and GEMM_EXACT take an
+ * order-faithful kernel (slow).  scratch as tlaloc_b200_int8_gemm (an F32 x only).
+ */
+int tlaloc_b200_int8_gemm_swiglu(const void* x, int32_t x_dtype, const int8_t* codes, const float* scales, void* y,
+                                 int32_t y_dtype, float* scratch, size_t scratch_bytes, int32_t m, int32_t k, int32_t n,
+                                 int32_t flags, void* stream);
+
+/*
  * The same projection over an unquantized weight w [K, N] (F32 | BF16), order-faithful
  * (the embedding-free head of ReferenceDecodeGraph.kt:113-147 and a bf16 lm_head).
  */

@@ -122,3 +122,36 @@ def test_tiny_decoder_64_greedy_steps_match_the_oracle(kv_dtype, head_quant, exa
         assert worst <= 1e-5, worst
     else:
         assert mismatches == 0 and near_ties <= 2
+
+
+def test_batch_of_40_with_swiglu_in_the_projection_epilogue_matches_the_oracle():
+    """More than 32 rows and an FFN width that tiles in blocks of 128: the engine runs the tensor-core projection and
+    folds SwiGLU into the gate|up projection's epilogue (weights interleaved at load).  Against the oracle's step."""
+    from tlaloc_b200 import decoder as D
+    from tlaloc_b200 import sharding
+
+    dims = dict(num_layers=2, d_model=256, num_heads=4, num_kv_heads=2, head_dim=64, ffn=512, vocab=512)
+    shape = oracle.DecoderShape(**dims, kv_dtype="bf16", head_quant=True)
+    w = oracle.make_weights(shape, seed=7)
+    cfg = D.DecoderConfig(**dims, kv_dtype=torch.bfloat16, head_quant=True, max_positions=64)
+    B, bs, M = 40, 16, 2
+    rng = np.random.default_rng(3)
+    tables = (1 + rng.permutation(B * M)).reshape(B, M).astype(np.int32)
+    dec = D.Decoder(cfg, B, 1 + B * M, M)
+    assert dec.fuse_swiglu
+    dec.load_host_weights(w)
+    kp = [np.zeros((1 + B * M, bs, 2, 64), np.float32) for _ in range(2)]
+    vp = [np.zeros_like(a) for a in kp]
+    ids = rng.integers(0, 512, size=B).astype(np.int32)
+    for step in range(6):
+        pos = np.full(B, step, np.int32)
+        slots = sharding.slot_mapping(tables, pos, bs)
+        dec.set_inputs(ids, pos, tables, pos + 1, slots)
+        if step == 2:
+            dec.capture()
+        nxt = dec.step().cpu().numpy()
+        want = oracle.decode_step(shape, w, kp, vp, ids, pos, tables, pos + 1, slots, threads=8)
+        err = np.abs(dec.logits.cpu().numpy() - want)
+        assert np.all(err <= 2e-3 + 1e-2 * np.abs(want).max(axis=1, keepdims=True)), (step, float(err.max()))
+        ids = oracle.argmax(want).astype(np.int32)
+        assert np.mean(nxt == ids) >= 0.95

@@ -74,3 +74,38 @@ def test_paged_attention_int8_gemm_and_kv_write_through_call_frames():
     stream.synchronize()
     assert np.array_equal(outp.cpu().numpy(), oracle.kv_cache_write(pool, rows.reshape(3, -1), slots))
     assert xla.errors == []
+
+
+def test_paged_attention_handler_takes_e4m3fn_pools():
+    """An artifact exported with f8e4m3fn KV pools hands the handler buffers of XLA_FFI_DataType_F8E4M3FN (20)."""
+    from tlaloc_b200 import _native as N
+
+    lib = N.lib()
+    stream = torch.cuda.Stream(device=DEV)
+    xla = F.FakeXla(stream=stream.cuda_stream)
+    rng = np.random.default_rng(2)
+    R, H, Hkv, D, bs, nb, M = 3, 8, 2, 128, 16, 40, 20
+    q = rng.standard_normal((R, H, D)).astype(np.float32)
+    k = oracle.snap_e4m3((rng.standard_normal((nb, bs, Hkv, D)) * 2).astype(np.float32))
+    v = oracle.snap_e4m3((rng.standard_normal((nb, bs, Hkv, D)) * 2).astype(np.float32))
+    tab = np.stack([rng.permutation(nb)[:M] for _ in range(R)]).astype(np.int32)
+    lens = np.array([1, 300, 17], np.int32)
+    scale = D ** -0.5
+    S = (M * bs + 255) // 256
+    tq = torch.from_numpy(q).to(DEV)
+    tk = torch.from_numpy(oracle.e4m3_bits(k)).to(DEV)
+    tv = torch.from_numpy(oracle.e4m3_bits(v)).to(DEV)
+    tt, tl = torch.from_numpy(tab).to(DEV), torch.from_numpy(lens).to(DEV)
+    out = torch.zeros((R, H, D), device=DEV)
+    scratch = torch.empty((S, R, H, D + 2), device=DEV)
+    torch.cuda.synchronize()
+    F8 = 20
+    a = [xla.buffer(F.F32, tq.data_ptr(), q.shape), xla.buffer(F8, tk.data_ptr(), k.shape), xla.buffer(F8, tv.data_ptr(), v.shape),
+         xla.buffer(F.S32, tt.data_ptr(), tab.shape), xla.buffer(F.S32, tl.data_ptr(), lens.shape)]
+    r = [xla.buffer(F.F32, out.data_ptr(), q.shape), xla.buffer(F.F32, scratch.data_ptr(), scratch.shape)]
+    h = F.handler(lib, "tlaloc_paged_attention")
+    assert h(C.byref(xla.frame(F.INITIALIZE))) is None
+    assert h(C.byref(xla.frame(F.EXECUTE, a, r, {"scale": (F.F32, C.c_float(scale))}))) is None, xla.errors
+    stream.synchronize()
+    want = oracle.paged_attention(q, k, v, tab, lens, float(np.float32(scale)))
+    assert np.abs(out.cpu().numpy() - want).max() <= 1e-4

@@ -275,3 +275,33 @@ def test_every_code_value_converts_exactly(m):
     got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), None)
     torch.cuda.synchronize()
     assert np.array_equal(got.cpu().numpy(), want.astype(np.float32))
+
+
+@pytest.mark.parametrize("m,k,n2", [(128, 512, 512), (64, 4096, 2048), (33, 256, 256), (200, 1024, 7168), (128, 8192, 1024), (256, 688, 512), (8, 512, 512)])
+def test_gate_up_projection_with_swiglu_in_the_epilogue(m, k, n2):
+    """tlaloc_b200_int8_gemm_swiglu against the two-step path (gate|up projection, then the SwiGLU kernel) on the same
+    weights: the same f32 sums meet the same SiLU arithmetic, so the results are bit-equal on the tensor-core path; and
+    against the oracle.  Shapes cover one and several K slices per tile, one and two accumulators, and (8 rows) the
+    order-faithful fallback."""
+    from tlaloc_b200 import _native as N
+    from tlaloc_b200 import sharding
+
+    rng = np.random.default_rng(m + k + n2)
+    f = n2 // 2
+    x = oracle.snap_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    gate = (rng.integers(-127, 128, size=(k, f), dtype=np.int8), rng.uniform(0.001, 0.02, size=f).astype(np.float32))
+    up = (rng.integers(-127, 128, size=(k, f), dtype=np.int8), rng.uniform(0.001, 0.02, size=f).astype(np.float32))
+    codes, scales = sharding.interleave_gate_up(gate, up)
+    got = ops().int8_gemm_swiglu(dev(x, torch.bfloat16), dev(codes), dev(scales), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert N.lib().tlaloc_b200_device_status() == 0
+    g = ops().int8_gemm(dev(x, torch.bfloat16), dev(gate[0]), dev(gate[1]))
+    u = ops().int8_gemm(dev(x, torch.bfloat16), dev(up[0]), dev(up[1]))
+    two_step = ops().swiglu(g, u)
+    torch.cuda.synchronize()
+    want = oracle.swiglu(oracle.proj_int8(x, gate[0], gate[1], threads=8), oracle.proj_int8(x, up[0], up[1], threads=8))
+    close(got.cpu().numpy(), want)
+    if m > 32:
+        assert torch.equal(got, two_step)
+    got_b = ops().int8_gemm_swiglu(dev(x, torch.bfloat16), dev(codes), dev(scales))
+    assert got_b.dtype == torch.bfloat16 and np.array_equal(got_b.float().cpu().numpy(), oracle.snap_bf16(got.cpu().numpy()))

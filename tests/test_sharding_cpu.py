@@ -132,3 +132,29 @@ def test_sharding_helpers():
     assert sharding.merge_greedy(vals, ids, 64).tolist() == [7, 1, 64 + 5]  # a tie goes to the lower rank (lower ids)
     tables = np.array([[3, 9], [4, 1]], np.int32)
     assert sharding.slot_mapping(tables, np.array([5, 2]), 4).tolist() == [9 * 4 + 1, 4 * 4 + 2]
+
+
+def test_interleaved_gate_up_layout():
+    """Blocks of 256 columns: 128 gate columns, then the same 128 up columns (the layout the fused SwiGLU epilogue reads)."""
+    import numpy as np
+
+    from tlaloc_b200 import sharding
+
+    k, f = 6, 384
+    gate = (np.arange(k * f, dtype=np.int32).reshape(k, f) % 100).astype(np.int8), np.arange(f, dtype=np.float32)
+    up = (-(np.arange(k * f, dtype=np.int32).reshape(k, f) % 100)).astype(np.int8), -np.arange(f, dtype=np.float32) - 1
+    codes, scales = sharding.interleave_gate_up(gate, up)
+    assert codes.shape == (k, 2 * f) and scales.shape == (2 * f,)
+    for t in range(f // 128):
+        assert np.array_equal(codes[:, 256 * t:256 * t + 128], gate[0][:, 128 * t:128 * (t + 1)])
+        assert np.array_equal(codes[:, 256 * t + 128:256 * (t + 1)], up[0][:, 128 * t:128 * (t + 1)])
+        assert np.array_equal(scales[256 * t:256 * t + 128], gate[1][128 * t:128 * (t + 1)])
+        assert np.array_equal(scales[256 * t + 128:256 * (t + 1)], up[1][128 * t:128 * (t + 1)])
+    import pytest
+    with pytest.raises(ValueError):
+        sharding.interleave_gate_up((gate[0][:, :100], gate[1][:100]), (up[0][:, :100], up[1][:100]))
+    lw = {n: (np.zeros((256, 256), np.int8), np.zeros(256, np.float32)) for n in ("q", "k", "v", "o")}
+    lw.update(gate=(np.ones((256, 512), np.int8), np.ones(512, np.float32)), up=(np.full((256, 512), 2, np.int8), np.full(512, 2, np.float32)),
+              down=(np.zeros((512, 256), np.int8), np.zeros(256, np.float32)), ln1=np.ones(256, np.float32), ln2=np.ones(256, np.float32))
+    s = sharding.shard_layer(lw, 4, 4, 64, 512, rank=1, world=2, fuse_swiglu=True)
+    assert s["gate_up"][0].shape == (256, 512) and np.all(s["gate_up"][0][:, :128] == 1) and np.all(s["gate_up"][0][:, 128:256] == 2)

@@ -37,6 +37,7 @@ _SIGNATURES = {
     "tlaloc_b200_kv_cache_write": (ctypes.c_int, [_vp, _i32, _vp, _i32, _vp, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_int8_gemm_scratch_bytes": (_sz, [_i32] * 3),
     "tlaloc_b200_int8_gemm": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _sz, _i32, _i32, _i32, _i32, _vp]),
+    "tlaloc_b200_int8_gemm_swiglu": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _i32, _vp, _sz, _i32, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_dense_gemm_exact": (ctypes.c_int, [_vp, _i32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_embedding": (ctypes.c_int, [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_rmsnorm": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp]),

@@ -147,7 +147,8 @@ cudaError_t PrepareInt8GemmTcKernels();
 
 // The tensor-core projection (int8_gemm_tc.cu): rows [0, m) of y = (x @ codes) * scales (+ residual), x bf16.
 cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const float* scales, const float* residual,
-                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches, bool weights_const);
+                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches, bool weights_const,
+                             bool swiglu = false);
 // 1 if a bounded device-side wait has timed out since the last call (synchronous read), 0 if not, -1 on a CUDA error.
 int ReadTcStatus();
 

@@ -303,6 +303,40 @@ __global__ void __launch_bounds__(256) GemmExactKernel(const XT* x, const WT* w,
   y[static_cast<size_t>(i) * N + j] = FromF32<YT>(acc);
 }
 
+// The fused gate|up projection + SwiGLU in the interpreter's order, for shapes the tensor-core kernel does not take:
+// column j of the result reads gate column (j / 128) * 256 + j % 128 and up column 128 further on.
+template <typename XT, typename YT>
+__global__ void __launch_bounds__(256) GemmSwigluExactKernel(const XT* x, const int8_t* w, const float* scales, YT* y, int M, int K,
+                                                             int N, int round_x, int faithful)
+{
+  GridDependencySync();
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int i = blockIdx.y;
+  const int half = N >> 1;
+  if (j >= half) return;
+  const int cg = (j >> 7) * 256 + (j & 127), cu = cg + 128;
+  float g = 0.f, u = 0.f;
+  for (int p = 0; p < K; ++p) {
+    float a = ToF32(x[static_cast<size_t>(i) * K + p]);
+    if (round_x) a = __bfloat162float(__float2bfloat16_rn(a));
+    if (a == 0.f) continue;
+    g = __fadd_rn(g, __fmul_rn(a, ToF32(w[static_cast<size_t>(p) * N + cg])));
+    u = __fadd_rn(u, __fmul_rn(a, ToF32(w[static_cast<size_t>(p) * N + cu])));
+  }
+  if (scales != nullptr) {
+    g = __fmul_rn(g, scales[cg]);
+    u = __fmul_rn(u, scales[cu]);
+  }
+  float silu;
+  if (faithful) {
+    const double gd = static_cast<double>(g);
+    silu = static_cast<float>(gd / (1.0 + exp(-gd)));
+  } else {
+    silu = g / (1.f + expf(-g));
+  }
+  y[static_cast<size_t>(i) * half + j] = FromF32<YT>(__fmul_rn(silu, u));
+}
+
 template <int NT, typename YT>
 cudaError_t PrepareGemv()
 {
@@ -446,9 +480,11 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
   }
   static const int tc_min = [] {
     const char* v = std::getenv("TLALOC_B200_GEMM_TC_MIN");
-    return v != nullptr ? std::atoi(v) : 33;
+    return v != nullptr ? std::atoi(v) : 17;
   }();
-  if (m >= tc_min) {  // batches of rows: the tcgen05 kernel
+  // 17 rows and more: the tcgen05 kernel (measured at 32 rows: 123 vs 193 us at 57344 x 8192, 190 vs 216 us at the
+  // 128256 x 4096 head; at 17 rows 166 vs 198 us; at 8 rows the row-vector kernel is faster, 103 vs ~165 us)
+  if (m >= tc_min) {
     e = PrepareInt8GemmTcKernels();
     if (e != cudaSuccess) return CudaFail("INT8_PROJ set-up", e);
     int launches = 0;
@@ -503,5 +539,60 @@ extern "C" int tlaloc_b200_dense_gemm_exact(const void* x, int32_t x_dtype, cons
   }
   if (e != cudaSuccess) return CudaFail("MATMUL exact launch", e);
   CountLaunches(1);
+  return kOk;
+}
+
+extern "C" int tlaloc_b200_int8_gemm_swiglu(const void* x, int32_t x_dtype, const int8_t* codes, const float* scales, void* y,
+                                            int32_t y_dtype, float* scratch, size_t scratch_bytes, int32_t m, int32_t k, int32_t n,
+                                            int32_t flags, void* stream)
+{
+  const char* op = "INT8_PROJ_SWIGLU";
+  if (!x || !codes || !y) return Fail(kInvalid, "%s: a required device pointer is null", op);
+  if (!IsFloatType(x_dtype) || !IsFloatType(y_dtype)) return Fail(kInvalid, "%s: x and y must be f32 or bf16", op);
+  if (m < 1 || k < 1 || n < 256 || n % 256 != 0) {
+    return Fail(kInvalid, "%s: needs [M, K] x [K, N] with N a multiple of 256 (gate|up blocks of 128 + 128), got M %d K %d N %d", op, m, k, n);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  static const int tc_min = [] {
+    const char* v = std::getenv("TLALOC_B200_GEMM_TC_MIN");
+    return v != nullptr ? std::atoi(v) : 17;
+  }();
+  const bool aligned = Aligned16(codes) && (x_dtype == TLALOC_B200_F32 || Aligned16(x)) && (reinterpret_cast<uintptr_t>(y) & 7) == 0;
+  cudaError_t e;
+  if ((flags & TLALOC_B200_GEMM_EXACT) != 0 || OrderFaithful() || !FastShape(k, n) || !aligned || m < tc_min) {
+    const int faithful = (flags & TLALOC_B200_GEMM_EXACT) != 0 || OrderFaithful();
+    const int round_x = x_dtype == TLALOC_B200_F32 && (flags & TLALOC_B200_GEMM_X_F32_EXACT) == 0;
+    const dim3 grid((n / 2 + 255) / 256, m);
+#define TLALOC_SWIGLU_EXACT(XT, YT, RX)                                                                                  \
+  e = LaunchChained(GemmSwigluExactKernel<XT, YT>, grid, 256, 0, st, static_cast<const XT*>(x), codes, scales,         \
+                    static_cast<YT*>(y), m, k, n, RX, faithful)
+    if (x_dtype == TLALOC_B200_F32 && y_dtype == TLALOC_B200_F32) TLALOC_SWIGLU_EXACT(float, float, round_x);
+    else if (x_dtype == TLALOC_B200_F32) TLALOC_SWIGLU_EXACT(float, __nv_bfloat16, round_x);
+    else if (y_dtype == TLALOC_B200_F32) TLALOC_SWIGLU_EXACT(__nv_bfloat16, float, 0);
+    else TLALOC_SWIGLU_EXACT(__nv_bfloat16, __nv_bfloat16, 0);
+#undef TLALOC_SWIGLU_EXACT
+    if (e != cudaSuccess) return CudaFail("INT8_PROJ_SWIGLU exact launch", e);
+    CountLaunches(1);
+    return kOk;
+  }
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+  if (x_dtype == TLALOC_B200_F32) {
+    const size_t need = sizeof(__nv_bfloat16) * static_cast<size_t>(m) * k;
+    if (scratch == nullptr || scratch_bytes < need || !Aligned16(scratch)) {
+      return Fail(kInvalid, "%s: an f32 x needs %zu bytes of 16-byte aligned scratch for its bf16 copy, got %zu", op, need, scratch_bytes);
+    }
+    const size_t count = static_cast<size_t>(m) * k;
+    e = LaunchChained(ToBf16Kernel<float>, static_cast<unsigned>((count + 255) / 256), 256, 0, st, static_cast<const float*>(x),
+                      reinterpret_cast<__nv_bfloat16*>(scratch), count);
+    if (e != cudaSuccess) return CudaFail("INT8_PROJ_SWIGLU activation cast", e);
+    CountLaunches(1);
+    xb = reinterpret_cast<const __nv_bfloat16*>(scratch);
+  }
+  e = PrepareInt8GemmTcKernels();
+  if (e != cudaSuccess) return CudaFail("INT8_PROJ_SWIGLU set-up", e);
+  int launches = 0;
+  e = LaunchInt8GemmTc(xb, codes, scales, nullptr, y, y_dtype, m, k, n, st, &launches, (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0, true);
+  if (e != cudaSuccess) return CudaFail("INT8_PROJ_SWIGLU tensor-core launch", e);
+  CountLaunches(launches);
   return kOk;
 }

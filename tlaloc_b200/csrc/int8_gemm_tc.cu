@@ -48,9 +48,11 @@ struct TcParams {
   int M, K, N;
   int Kc, ks;
   int weights_const;  // codes and scales are not written by the preceding kernel: fetch them before the dependency wait
+  int swiglu;         // the columns are gate|up blocks of 128 + 128: y [M, N / 2] = silu(gate) * up (no residual)
 };
 
 constexpr int kTcThreads = 512;                    // converter threads (16 warps)
+constexpr int kTcLaunchThreads = kTcThreads + 32;  // plus one warp whose first lane issues the MMAs
 constexpr int kTcBN = 256;                         // output columns per CTA: the N of one MMA
 constexpr int kTcBK = 64;                          // k rows per block
 constexpr int kTcWBytes = kTcBN * kTcBK * 2;       // one block's weights as bf16
@@ -62,14 +64,9 @@ __device__ int g_tc_status = 0;  // nonzero after an mbarrier wait timed out (st
 // Shared memory: [activation strips, kBufs][bf16 weight tiles, kBufs][mbarriers, TMEM base].  An MMA always reads
 // 128 activation rows; with MPAD < 128 the rows past MPAD are whatever follows in shared memory, which only reaches
 // accumulator lanes that are never read.
-// AT ("A in TMEM", MPAD <= 128): the activation strip does not pass through shared memory at all; four extra warps
-// copy it from global memory to registers and on to tensor memory (tcgen05.st), where the MMA reads its A operand.
-// Shared memory then carries only the converted weights (written once, read once by the tensor core): a third less
-// traffic on what the profile shows to be the busiest unit of this kernel.
-template <int MPAD, bool AT = false>
+template <int MPAD>
 struct TcLayout {
-  static_assert(!AT || MPAD <= 128, "two accumulators fill tensor memory: no room for the strip");
-  static constexpr int kXBytes = AT ? 0 : MPAD * kTcBK * 2;
+  static constexpr int kXBytes = MPAD * kTcBK * 2;
   // Converter groups: group g converts blocks g, g + kGroups, ...  There are as many buffers as groups, so a buffer
   // always belongs to the same group and the parity a group waits for can only be the barrier's latest phase.
   static constexpr int kGroups = MPAD > 128 ? 2 : 4;
@@ -83,17 +80,13 @@ struct TcLayout {
   static constexpr int kPipeEnd = kWOffset + kBufs * kTcWBytes;
   static constexpr int kTileRows = MPAD < 128 ? MPAD : 128;
   static constexpr int kTileBytes = kTileRows * kTcTileStride * 4;  // epilogue tile of one accumulator; aliases the pipeline
-  // mma_done[kBufs], conv_done[kBufs], the TMEM base, then the tile's 256 scales: past both the pipeline and the tile
+  // mma_done[kBufs], conv_done[kBufs], the TMEM base and the abort word, then the tile's 256 scales: past both the
+  // pipeline and the tile
   static constexpr int kBarOffset = (kPipeEnd > kTileBytes ? kPipeEnd : kTileBytes + 15) / 16 * 16;
   static constexpr int kScaleOffset = kBarOffset + 128;
   static constexpr int kBytes = kScaleOffset + kTcBN * 4 + 1024;  // slack to align to 1024
   static constexpr int kAccs = MPAD > 128 ? 2 : 1;  // accumulators of 128 activation rows x 256 columns
-  static constexpr int kStripCols = kTcBK / 2;      // AT: a strip buffer is 64 bf16 per lane = 32 columns of 32 bits
-  static constexpr int kStripCol0 = kAccs * kTcBN;  // AT: the strip buffers follow the accumulator
-  static constexpr int kTmemCols = AT ? 512 : kAccs * kTcBN;  // a power of two >= 256 + 4 * 32
-  static constexpr int kStripWarps = AT ? 4 : 0;
-  static constexpr int kLaunchThreads = kTcThreads + 32 + 32 * kStripWarps;
-  static constexpr int kConvArrivals = kGroupWarps + kStripWarps;  // arrivals that complete a block's conv_done phase
+  static constexpr int kTmemCols = kAccs * kTcBN;
   static_assert(kXBytes % 1024 == 0, "operand tiles start on 1024-byte boundaries");
 };
 
@@ -212,27 +205,6 @@ __device__ __forceinline__ void TcMma(uint32_t d_tmem, uint64_t a_desc, uint64_t
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// The same MMA with the A operand in tensor memory (lane = row, one 32-bit column = two consecutive k).
-__device__ __forceinline__ void TcMmaTs(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
-{
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// 32 registers of every lane of the warp into 32 consecutive columns of the lane's own row of tensor memory.
-__device__ __forceinline__ void TcSt32(uint32_t taddr, const uint32_t* r)
-{
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
-      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
-      "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
 __device__ __forceinline__ void TcCommit(uint32_t bar)
 {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
@@ -268,6 +240,44 @@ __device__ __forceinline__ void StoreRow4(__nv_bfloat16* dst, float4 v, bool vec
   } else {
     dst[0] = __float2bfloat16_rn(v.x); dst[1] = __float2bfloat16_rn(v.y);
     dst[2] = __float2bfloat16_rn(v.z); dst[3] = __float2bfloat16_rn(v.w);
+  }
+}
+
+// SiLU(gate) * up as the decode step's SwiGLU kernel computes it (f32, the library exponential).
+__device__ __forceinline__ float SiluMulF32(float g, float u) { return __fmul_rn(g / (1.f + expf(-g)), u); }
+
+// The cluster reduction of a gate|up tile: thread n_local < 128 owns gate column n_local and up column 128 + n_local
+// of the tile, sums both over the ranks in rank order, and writes silu(gate * scale) * (up * scale) to column
+// col_out of the [M, N / 2] result.
+template <int NR, typename YT>
+__device__ __forceinline__ void ClusterReduceRowsSwiglu(cg::cluster_group& cluster, float* tile, YT* y, int M, int ld_out,
+                                                        float scale_g, float scale_u, int n_local, int col_out, int rank, int half)
+{
+  constexpr int kRows = NR <= 4 ? 16 / NR : 8 / NR;
+  constexpr int step = 2 * NR;
+  for (int m0 = rank + NR * half; m0 < M; m0 += kRows * step) {
+    float tg[NR][kRows], tu[NR][kRows];
+#pragma unroll
+    for (int q = 0; q < NR; ++q) {
+      const float* peer = cluster.map_shared_rank(tile, q) + n_local;
+#pragma unroll
+      for (int u = 0; u < kRows; ++u) {
+        const int m = m0 + u * step;
+        tg[q][u] = m < M ? peer[m * kTcTileStride] : 0.f;
+        tu[q][u] = m < M ? peer[m * kTcTileStride + 128] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kRows; ++u) {
+      const int m = m0 + u * step;
+      float g = tg[0][u], v = tu[0][u];
+#pragma unroll
+      for (int q = 1; q < NR; ++q) {
+        g += tg[q][u];
+        v += tu[q][u];
+      }
+      if (m < M) y[static_cast<size_t>(m) * ld_out + col_out] = FromF32<YT>(SiluMulF32(g * scale_g, v * scale_u));
+    }
   }
 }
 
@@ -308,13 +318,10 @@ __device__ __forceinline__ void ClusterReduceRows(cg::cluster_group& cluster, fl
   }
 }
 
-// 96 registers per thread for both forms: 17 warps (544 threads) or, with the four strip warps, 21 warps (672 threads:
-// 21 x 32 x 96 = 64512 of the SM's 65536 registers).  Stated as a register count and not as launch bounds, which
-// would round the 672 threads up and leave the converters' loop 80 registers.
-template <int MPAD, typename YT, bool AT>
-__global__ void __maxnreg__(96) Int8GemmTcKernel(TcParams p)
+template <int MPAD, typename YT>
+__global__ void __launch_bounds__(kTcLaunchThreads, 1) Int8GemmTcKernel(TcParams p)
 {
-  using L = TcLayout<MPAD, AT>;
+  using L = TcLayout<MPAD>;
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment of the operand tiles (the swizzle is a function of address bits 4..9).
   const uint32_t smem_base = (SmemAddr(smem_raw) + 1023u) & ~1023u;
@@ -335,7 +342,7 @@ __global__ void __maxnreg__(96) Int8GemmTcKernel(TcParams p)
     *abort_word = 0u;
     for (int i = 0; i < L::kBufs; ++i) {
       MbarInit(mma_done0 + 8 * i, 1);
-      MbarInit(conv_done0 + 8 * i, L::kConvArrivals);
+      MbarInit(conv_done0 + 8 * i, L::kGroupWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -400,7 +407,7 @@ __global__ void __maxnreg__(96) Int8GemmTcKernel(TcParams p)
       // Block b - kBufs used this weight tile and this strip buffer.
       if (b >= L::kBufs) ok = MbarWaitWarp(mma_done0 + buf * 8, ((b / L::kBufs) - 1) & 1, lane, abort_word) && ok;
       const int k0 = kb0 + b * kTcBK;
-      if constexpr (!AT) {
+      {
         const uint32_t st = smem_base + buf * L::kXBytes + xdst0;
         const __nv_bfloat16* src = xsrc0 + b * kTcBK;
         if (k0 + kTcBK <= ke) {
@@ -442,14 +449,14 @@ __global__ void __maxnreg__(96) Int8GemmTcKernel(TcParams p)
       // Uniform over the CTA: the next block exists, is a whole block, and the tile has all its 256 columns.
       if (tile_full && k0 + (kG + 1) * kTcBK <= ke) convert_block(std::true_type{});
       else convert_block(std::false_type{});
-      if constexpr (!AT) CpAsyncWait<0>();  // this thread's part of the strip has landed
+      CpAsyncWait<0>();  // this thread's part of the strip has landed
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // these writes (and the cp.async strip) -> tensor core
       __syncwarp();
       if (lane == 0) {
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(conv_done0 + buf * 8) : "memory");
       }
     }
-  } else if (warp == kTcThreads / 32) {
+  } else {
     // The MMA thread (one lane; nothing else may sit between a block's arrival and its MMAs): for each block, wait for
     // its converter group, then 4 K-steps of 128 x 256 x 16 per accumulator and a commit.  A = the activation strip
     // (K-major), B = the converted weights (MN-major).  Descriptors differ from block to block only in the 14-bit
@@ -466,15 +473,9 @@ __global__ void __maxnreg__(96) Int8GemmTcKernel(TcParams p)
 #pragma unroll
         for (int ks = 0; ks < kTcBK / 16; ++ks) {
 #pragma unroll
-          for (int acc = 0; acc < L::kAccs; ++acc) {
-            if constexpr (AT) {
-              TcMmaTs(tmem_base, tmem_base + L::kStripCol0 + buf * L::kStripCols + ks * 8,
-                      b_desc + static_cast<uint64_t>((ks * 2048) >> 4), idesc, (b > 0 || ks > 0) ? 1u : 0u);
-            } else {
-              TcMma(tmem_base + acc * kTcBN, a_desc + static_cast<uint64_t>((acc * 16384 + ks * 32) >> 4),
-                    b_desc + static_cast<uint64_t>((ks * 2048) >> 4), idesc, (b > 0 || ks > 0) ? 1u : 0u);
-            }
-          }
+          for (int acc = 0; acc < L::kAccs; ++acc)
+            TcMma(tmem_base + acc * kTcBN, a_desc + static_cast<uint64_t>((acc * 16384 + ks * 32) >> 4),
+                  b_desc + static_cast<uint64_t>((ks * 2048) >> 4), idesc, (b > 0 || ks > 0) ? 1u : 0u);
         }
         TcCommit(mma_done0 + buf * 8);
       }
@@ -482,48 +483,9 @@ __global__ void __maxnreg__(96) Int8GemmTcKernel(TcParams p)
       // had already waited for the same barrier's previous phase.
       if (nblocks > 0) ok = MbarWait(mma_done0 + ((nblocks - 1) % L::kBufs) * 8, ((nblocks - 1) / L::kBufs) & 1, abort_word) && ok;
     }
-  } else if constexpr (AT) {
-    // The strip warps: warp w serves tensor-memory lanes 32 (w % 4) .. + 31, one activation row per lane.  A block's
-    // 64 k of a row are 128 contiguous bytes in global memory and, two k per 32-bit column, exactly the 32 registers a
-    // tcgen05.st of 32 columns takes.  The next block's row is requested before this one is stored, so the loop runs
-    // at the latency of one trip to L2 (the activations of a launch are a few megabytes, read by every CTA), well
-    // ahead of the converters; it is held back only by the buffers (a strip buffer is freed with its weight tile).
-    const int m = 32 * (warp & 3) + lane;
-    const bool row_ok = m < p.M;
-    const __nv_bfloat16* xrow = p.x + static_cast<size_t>(row_ok ? m : 0) * p.K + kb0;
-    auto load_row = [&](int b, uint4(&v)[8]) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int k = kb0 + b * kTcBK + 8 * i;
-        v[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (row_ok && b < nblocks && k < ke) v[i] = __ldg(reinterpret_cast<const uint4*>(xrow + b * kTcBK + 8 * i));
-      }
-    };
-    uint4 cur[8], nxt[8];
-    load_row(0, cur);
-    for (int b = 0; b < nblocks; ++b) {
-      load_row(b + 1, nxt);
-      const int buf = b % L::kBufs;
-      if (b >= L::kBufs) ok = MbarWaitWarp(mma_done0 + buf * 8, ((b / L::kBufs) - 1) & 1, lane, abort_word) && ok;
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      uint32_t regs[32];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        regs[4 * i] = cur[i].x; regs[4 * i + 1] = cur[i].y; regs[4 * i + 2] = cur[i].z; regs[4 * i + 3] = cur[i].w;
-      }
-      TcSt32(tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + L::kStripCol0 + buf * L::kStripCols, regs);
-      asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-      __syncwarp();
-      if (lane == 0) {
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(conv_done0 + buf * 8) : "memory");
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
-    }
   }
   if (!ok) atomicExch(&g_tc_status, 1);
-  if (warp < kTcThreads / 32) CpAsyncWait<0>();
+  if (conv) CpAsyncWait<0>();
   if (tid < kTcBN) s_scales[tid] = my_scale;
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();  // every MMA has completed; the pipeline space is free
@@ -564,7 +526,24 @@ __global__ void __maxnreg__(96) Int8GemmTcKernel(TcParams p)
       __syncthreads();
       // 64 threads per row (four columns each), eight rows per pass.
       const int c4 = (tid & 63) * 4;
-      if (conv && col0 + c4 < p.N) {  // N is a multiple of 16: four columns are inside or outside together
+      if (p.swiglu) {
+        // gate|up tile (always whole: N is a multiple of 256 here): 32 threads per row, four output columns each
+        const int g4 = (tid & 31) * 4;
+        if (conv) {
+          const float4 sg = *reinterpret_cast<const float4*>(s_scales + g4), su = *reinterpret_cast<const float4*>(s_scales + 128 + g4);
+          const int ld_out = p.N >> 1;
+#pragma unroll 4
+          for (int m = tid >> 5; m < L::kTileRows; m += 16) {
+            const int row = acc * 128 + m;
+            if (row >= p.M) break;
+            const float4 g = *reinterpret_cast<const float4*>(tile + m * kTcTileStride + g4);
+            const float4 u = *reinterpret_cast<const float4*>(tile + m * kTcTileStride + 128 + g4);
+            const float4 v = make_float4(SiluMulF32(g.x * sg.x, u.x * su.x), SiluMulF32(g.y * sg.y, u.y * su.y),
+                                         SiluMulF32(g.z * sg.z, u.z * su.z), SiluMulF32(g.w * sg.w, u.w * su.w));
+            StoreRow4(y + static_cast<size_t>(row) * ld_out + (col0 >> 1) + g4, v, vec_ok);
+          }
+        }
+      } else if (conv && col0 + c4 < p.N) {  // N is a multiple of 16: four columns are inside or outside together
         const float4 sc = *reinterpret_cast<const float4*>(s_scales + c4);
 #pragma unroll 4
         for (int m = tid >> 6; m < L::kTileRows; m += 8) {
@@ -592,7 +571,21 @@ __global__ void __maxnreg__(96) Int8GemmTcKernel(TcParams p)
   if (nranks > 1) {  // only launched with one accumulator
     cluster.sync();
     const int n_local = tid & 255, col = col0 + n_local;
-    if (conv && col < p.N) {
+    if (p.swiglu) {
+      if (conv && n_local < 128) {
+        const float sg = s_scales[n_local], su = s_scales[128 + n_local];
+        const int half = tid >> 8, rk = static_cast<int>(rank), ld_out = p.N >> 1, col_out = (col0 >> 1) + n_local;
+        switch (nranks) {
+          case 2: ClusterReduceRowsSwiglu<2>(cluster, tile, y, p.M, ld_out, sg, su, n_local, col_out, rk, half); break;
+          case 3: ClusterReduceRowsSwiglu<3>(cluster, tile, y, p.M, ld_out, sg, su, n_local, col_out, rk, half); break;
+          case 4: ClusterReduceRowsSwiglu<4>(cluster, tile, y, p.M, ld_out, sg, su, n_local, col_out, rk, half); break;
+          case 5: ClusterReduceRowsSwiglu<5>(cluster, tile, y, p.M, ld_out, sg, su, n_local, col_out, rk, half); break;
+          case 6: ClusterReduceRowsSwiglu<6>(cluster, tile, y, p.M, ld_out, sg, su, n_local, col_out, rk, half); break;
+          case 7: ClusterReduceRowsSwiglu<7>(cluster, tile, y, p.M, ld_out, sg, su, n_local, col_out, rk, half); break;
+          default: ClusterReduceRowsSwiglu<8>(cluster, tile, y, p.M, ld_out, sg, su, n_local, col_out, rk, half); break;
+        }
+      }
+    } else if (conv && col < p.N) {
       const float scale = s_scales[n_local];
       const int half = tid >> 8, rk = static_cast<int>(rank);
       switch (nranks) {
@@ -617,22 +610,7 @@ __global__ void __maxnreg__(96) Int8GemmTcKernel(TcParams p)
 template <int MPAD, typename YT>
 cudaError_t PrepareTc()
 {
-  cudaError_t e = cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD, false>::kBytes);
-  if constexpr (MPAD <= 128) {
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD, true>::kBytes);
-  }
-  return e;
-}
-
-// $TLALOC_B200_GEMM_A=smem keeps the activation strip in shared memory for every shape (up to 128 rows it otherwise goes
-// through tensor memory).
-bool TcStripInTmem()
-{
-  static const bool v = [] {
-    const char* e = std::getenv("TLALOC_B200_GEMM_A");
-    return e == nullptr || std::string(e) != "smem";
-  }();
-  return v;
+  return cudaFuncSetAttribute(Int8GemmTcKernel<MPAD, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<MPAD>::kBytes);
 }
 
 template <int MPAD, typename YT>
@@ -640,20 +618,13 @@ cudaError_t LaunchTc(const TcParams& p, cudaStream_t stream)
 {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + kTcBN - 1) / kTcBN, p.ks, 1);
+  cfg.blockDim = dim3(kTcLaunchThreads, 1, 1);
+  cfg.dynamicSmemBytes = TcLayout<MPAD>::kBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   cfg.numAttrs = ChainAttributes(attr, p.ks);
   cfg.attrs = attr;
-  if constexpr (MPAD <= 128) {
-    if (TcStripInTmem()) {
-      cfg.blockDim = dim3(TcLayout<MPAD, true>::kLaunchThreads, 1, 1);
-      cfg.dynamicSmemBytes = TcLayout<MPAD, true>::kBytes;
-      return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT, true>, p);
-    }
-  }
-  cfg.blockDim = dim3(TcLayout<MPAD, false>::kLaunchThreads, 1, 1);
-  cfg.dynamicSmemBytes = TcLayout<MPAD, false>::kBytes;
-  return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT, false>, p);
+  return cudaLaunchKernelEx(&cfg, Int8GemmTcKernel<MPAD, YT>, p);
 }
 
 // CTAs of the kernel that can be resident at once when launched as clusters of ks (index [device][MPAD class][ks]);
@@ -667,8 +638,8 @@ void FillTcSlots(int device, int cls)
   for (int ks = 1; ks <= 8; ++ks) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(148, ks, 1);
-    cfg.blockDim = dim3(TcLayout<MPAD, true>::kLaunchThreads, 1, 1);
-    cfg.dynamicSmemBytes = TcLayout<MPAD, true>::kBytes;
+    cfg.blockDim = dim3(kTcLaunchThreads, 1, 1);
+    cfg.dynamicSmemBytes = TcLayout<MPAD>::kBytes;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
@@ -677,7 +648,7 @@ void FillTcSlots(int device, int cls)
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, Int8GemmTcKernel<MPAD, float, true>, &cfg) != cudaSuccess || clusters <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, Int8GemmTcKernel<MPAD, float>, &cfg) != cudaSuccess || clusters <= 0) {
       cudaGetLastError();
       clusters = (ks <= 2 ? 148 : ks <= 4 ? 128 : 112) / ks;  // a cautious guess when the query is not available
     }
@@ -756,10 +727,12 @@ cudaError_t PrepareInt8GemmTcKernels()
 
 // Rows [0, m) of the projection on the tensor-core kernel, at most 256 rows per launch.  x is bf16.
 cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const float* scales, const float* residual,
-                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches, bool weights_const)
+                             void* y, int y_dtype, int m, int k, int n, cudaStream_t st, int* launches, bool weights_const,
+                             bool swiglu)
 {
   TcParams p;
   p.weights_const = weights_const ? 1 : 0;
+  p.swiglu = swiglu ? 1 : 0;
   p.w = codes;
   p.scales = scales;
   p.K = k;
@@ -782,7 +755,7 @@ cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const 
     p.M = rows;
     p.x = x + static_cast<size_t>(m0) * k;
     p.residual = residual ? residual + static_cast<size_t>(m0) * n : nullptr;
-    p.y = static_cast<unsigned char*>(y) + static_cast<size_t>(m0) * n * ybytes;
+    p.y = static_cast<unsigned char*>(y) + static_cast<size_t>(m0) * (swiglu ? n / 2 : n) * ybytes;
     const cudaError_t e = y_dtype == TLALOC_B200_F32 ? LaunchTcRows<float>(p, rows, st) : LaunchTcRows<__nv_bfloat16>(p, rows, st);
     if (e != cudaSuccess) return e;
     ++*launches;

@@ -51,7 +51,6 @@ struct PaParams {
   int group, rpt, NQ;
   int window, keep_chunks, keep_chunk;
   int bs_shift;  // log2(bs) when bs is a power of two, else -1
-  int prefetch;  // tensor-core slice kernels: groups ahead at which a warp asks its K/V rows into L2 (0 = never)
   float scale;
 };
 
@@ -429,20 +428,6 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
     }
   };
 
-  // Group `it` of this warp on its way into L2: lane l asks for row l % 16 of K (l < 16) or V, one request per
-  // 128-byte line.  The copies of that group, issued NS - 1 groups ahead, then meet L2's latency instead of HBM's.
-  auto prefetch = [&](int it) {
-    const int t = t_begin + ((warp + kMmaWarps * it) << 4) + (lane & 15);
-    if (t >= c1) return;
-    const int blk_i = p.bs_shift >= 0 ? (t >> p.bs_shift) : t / p.bs;
-    const size_t off = ((static_cast<size_t>(tab[blk_i - b0]) * p.bs + (t - blk_i * p.bs)) * p.Hkv + kv) * D;
-    const unsigned char* row = reinterpret_cast<const unsigned char*>((lane < 16 ? kc : vc) + off);
-#pragma unroll
-    for (int b = 0; b < L::kRowBytes; b += 128) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(row + b) : "memory");
-  };
-  if (p.prefetch > 0)
-    for (int it = NS - 1; it < NS - 1 + p.prefetch && it < my_n; ++it) prefetch(it);
-
   for (int it = 0; it < NS - 1; ++it) {
     if (it < my_n) issue(it);
     CpAsyncCommit();
@@ -464,7 +449,6 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
   for (int it = 0; it < my_n; ++it) {
     if (it + NS - 1 < my_n) issue(it + NS - 1);
     CpAsyncCommit();
-    if (p.prefetch > 0 && it + NS - 1 + p.prefetch < my_n) prefetch(it + NS - 1 + p.prefetch);
     CpAsyncWait<NS - 1>();
     __syncwarp();
     const int t_base = t_begin + ((warp + kMmaWarps * it) << 4);
@@ -765,18 +749,6 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
     }
   };
 
-  auto prefetch = [&](int it) {  // as in PaSliceMma: the warp's group `it` on its way into L2
-    const int t = t_begin + ((warp + kMmaWarps * it) << 4) + (lane & 15);
-    if (t >= c1) return;
-    const int blk_i = p.bs_shift >= 0 ? (t >> p.bs_shift) : t / p.bs;
-    const size_t off = ((static_cast<size_t>(tab[blk_i - b0]) * p.bs + (t - blk_i * p.bs)) * p.Hkv + kv) * D;
-    const unsigned char* row = (lane < 16 ? kc : vc) + off;
-#pragma unroll
-    for (int b = 0; b < L::kRowBytes; b += 128) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(row + b) : "memory");
-  };
-  if (p.prefetch > 0)
-    for (int it = NS - 1; it < NS - 1 + p.prefetch && it < my_n; ++it) prefetch(it);
-
   for (int it = 0; it < NS - 1; ++it) {
     if (it < my_n) issue(it);
     CpAsyncCommit();
@@ -800,7 +772,6 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
   for (int it = 0; it < my_n; ++it) {
     if (it + NS - 1 < my_n) issue(it + NS - 1);
     CpAsyncCommit();
-    if (p.prefetch > 0 && it + NS - 1 + p.prefetch < my_n) prefetch(it + NS - 1 + p.prefetch);
     CpAsyncWait<NS - 1>();
     __syncwarp();
     const int t_base = t_begin + ((warp + kMmaWarps * it) << 4);
@@ -1389,12 +1360,6 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
   p.keep_chunks = keep ? keep_chunks : 0;
   p.keep_chunk = keep ? ctx / keep_chunks : 1;
   p.bs_shift = (block_size & (block_size - 1)) == 0 ? __builtin_ctz(block_size) : -1;
-  static const int pa_prefetch = [] {  // $TLALOC_B200_PA_PREFETCH: groups ahead (per warp) for the L2 prefetch; 0 = off
-    const char* v = std::getenv("TLALOC_B200_PA_PREFETCH");
-    const int x = v != nullptr ? std::atoi(v) : 0;
-    return x < 0 ? 0 : x > 16 ? 16 : x;
-  }();
-  p.prefetch = pa_prefetch;
   p.scale = scale;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);

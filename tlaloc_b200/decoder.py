@@ -75,6 +75,10 @@ class Decoder:
         sharding.check_world(cfg.num_heads, cfg.num_kv_heads, cfg.ffn, cfg.vocab, world)
         self.cfg, self.batch, self.device, self.rank, self.world, self.group = cfg, batch, torch.device(device), rank, world, group
         self.exact = bool(exact)
+        # SwiGLU in the gate|up projection's epilogue: batches the tensor-core kernel takes (more than 32 rows) and FFN
+        # widths that tile in blocks of 128 per rank; $TLALOC_B200_FUSE_SWIGLU=0 keeps the separate kernel
+        self.fuse_swiglu = (not exact and batch > 32 and (cfg.ffn // world) % 128 == 0
+                            and os.environ.get("TLALOC_B200_FUSE_SWIGLU", "1") != "0")
         self.hq, self.hk, self.f = cfg.num_heads // world, cfg.num_kv_heads // world, cfg.ffn // world
         self.num_blocks, self.max_blocks = num_blocks, max_blocks_per_seq
         dev, B, d, hd = self.device, batch, cfg.d_model, cfg.head_dim
@@ -142,7 +146,8 @@ class Decoder:
         self.final_norm = t(w.final_norm)
         self.layers = []
         for lw in w.layers:
-            s = sharding.shard_layer(lw, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.ffn, self.rank, self.world)
+            s = sharding.shard_layer(lw, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.ffn, self.rank, self.world,
+                                     fuse_swiglu=self.fuse_swiglu)
             self.layers.append({k: (tuple(t(x) for x in v) if isinstance(v, tuple) else t(v)) for k, v in s.items()})
         head = sharding.shard_head(w.head, cfg.vocab, self.rank, self.world)
         self.head = tuple(t(x) for x in head) if isinstance(head, tuple) else t(head, torch.bfloat16)
@@ -234,7 +239,6 @@ class Decoder:
                 self._all_reduce(h2)
                 ops.rmsnorm(h2, lw["ln2"], cfg.rms_eps, out=self.hn)
             self.gate_up_proj(lw)
-            ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
             ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True)
             if fused:
                 nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
@@ -264,7 +268,6 @@ class Decoder:
             ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], out=p_o, weights_const=True)
             self.peer.sum_rows_(0, h, h, lw["ln2"], cfg.rms_eps, norm_out=self.hn)
             self.gate_up_proj(lw)
-            ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
             ops.int8_gemm(self.act, *lw["down"], out=p_down, weights_const=True)
             nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
             self.peer.sum_rows_(1, h, h, nxt, cfg.rms_eps, norm_out=self.hn)
@@ -285,8 +288,13 @@ class Decoder:
             self._merge_greedy()
 
     def gate_up_proj(self, lw) -> None:
-        """The fused gate|up projection of one layer: normalised rows `hn` -> `gu` = [gate | up]."""
-        ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True)
+        """The MLP's first half for one layer: normalised rows `hn` -> `act` = silu(gate) * up, as one projection with
+        SwiGLU in its epilogue where the shape allows, else the fused gate|up projection and the SwiGLU kernel."""
+        if self.fuse_swiglu:
+            ops.int8_gemm_swiglu(self.hn, *lw["gate_up"], out=self.act, weights_const=True)
+        else:
+            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True)
+            ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
 
     def _merge_greedy(self) -> None:
         """Each rank's best (logit, local id) -> the global greedy token on every rank (sharding.merge_greedy)."""

@@ -131,6 +131,27 @@ def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.floa
     return out
 
 
+def int8_gemm_swiglu(x, codes, scales, *, out=None, out_dtype=torch.bfloat16, exact=False, scratch=None, weights_const=False):
+    """silu(x @ gate) * (x @ up) with gate and up interleaved in `codes` [K, 2F] in column blocks of 128 + 128
+    (sharding.interleave_gate_up); returns [M, F]."""
+    _dev(x, codes, scales)
+    M, K = x.shape
+    K2, Nn = codes.shape
+    if K2 != K or codes.dtype != torch.int8 or Nn % 256 or (scales is not None and tuple(scales.shape) != (Nn,)):
+        raise ValueError(f"INT8_PROJ_SWIGLU: x [M, K] x codes int8 [K, 2F] (2F a multiple of 256) with scales [2F]; got "
+                         f"{tuple(x.shape)}, {tuple(codes.shape)}")
+    if out is None:
+        out = torch.empty((M, Nn // 2), dtype=out_dtype, device=x.device)
+    _out("INT8_PROJ_SWIGLU out", out, (M, Nn // 2), (torch.float32, torch.bfloat16), x)
+    if scratch is None and not exact and x.dtype == torch.float32:
+        scratch = torch.empty((N.lib().tlaloc_b200_int8_gemm_scratch_bytes(M, K, Nn) + 3) // 4, dtype=torch.float32, device=x.device)
+    _out("INT8_PROJ_SWIGLU scratch", scratch, None, torch.float32, x)
+    flags = (N.GEMM_EXACT if exact else 0) | (N.GEMM_WEIGHTS_CONST if weights_const else 0)
+    N.check(N.lib().tlaloc_b200_int8_gemm_swiglu(_ptr(x), _dt(x), _ptr(codes), _ptr(scales), _ptr(out), _dt(out), _ptr(scratch),
+                                                 0 if scratch is None else scratch.numel() * 4, M, K, Nn, flags, _stream(x)))
+    return out
+
+
 def int8_gemm_scratch_bytes(m: int, k: int, n: int) -> int:
     return int(N.lib().tlaloc_b200_int8_gemm_scratch_bytes(m, k, n))
 

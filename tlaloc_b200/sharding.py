@@ -36,8 +36,10 @@ def _rows(codes_scales, lo, hi):
     return np.ascontiguousarray(codes[lo:hi, :]), scales
 
 
-def shard_layer(layer: dict, num_heads: int, num_kv_heads: int, head_dim: int, ffn: int, rank: int, world: int) -> dict:
-    """One layer's weights for `rank`; q|k|v and gate|up are returned fused along the output axis."""
+def shard_layer(layer: dict, num_heads: int, num_kv_heads: int, head_dim: int, ffn: int, rank: int, world: int,
+                fuse_swiglu: bool = False) -> dict:
+    """One layer's weights for `rank`; q|k|v and gate|up are returned fused along the output axis (gate|up as two halves,
+    or, with `fuse_swiglu`, interleaved in blocks of 128 for the projection that applies SwiGLU in its epilogue)."""
     hq, hk, f = num_heads // world, num_kv_heads // world, ffn // world
     q = _cols(layer["q"], rank * hq * head_dim, (rank + 1) * hq * head_dim)
     k = _cols(layer["k"], rank * hk * head_dim, (rank + 1) * hk * head_dim)
@@ -47,10 +49,24 @@ def shard_layer(layer: dict, num_heads: int, num_kv_heads: int, head_dim: int, f
     return {
         "qkv": (np.concatenate([q[0], k[0], v[0]], axis=1), np.concatenate([q[1], k[1], v[1]])),
         "o": _rows(layer["o"], rank * hq * head_dim, (rank + 1) * hq * head_dim),
-        "gate_up": (np.concatenate([gate[0], up[0]], axis=1), np.concatenate([gate[1], up[1]])),
+        "gate_up": (interleave_gate_up(gate, up) if fuse_swiglu
+                    else (np.concatenate([gate[0], up[0]], axis=1), np.concatenate([gate[1], up[1]]))),
         "down": _rows(layer["down"], rank * f, (rank + 1) * f),
         "ln1": layer["ln1"], "ln2": layer["ln2"],
     }
+
+
+def interleave_gate_up(gate, up):
+    """gate and up as (codes [K, F], scales [F]) -> the fused-SwiGLU layout of tlaloc_b200_int8_gemm_swiglu: one
+    (codes [K, 2F], scales [2F]) whose column blocks of 256 hold 128 gate columns then the same 128 up columns.
+    F must be a multiple of 128."""
+    (gc, gs), (uc, us) = gate, up
+    k, f = gc.shape
+    if uc.shape != gc.shape or f % 128:
+        raise ValueError(f"interleave_gate_up: gate and up must both be [K, F] with F a multiple of 128, got {gc.shape}, {uc.shape}")
+    codes = np.stack([gc.reshape(k, f // 128, 128), uc.reshape(k, f // 128, 128)], axis=2).reshape(k, 2 * f)
+    scales = np.stack([np.asarray(gs).reshape(f // 128, 128), np.asarray(us).reshape(f // 128, 128)], axis=1).reshape(2 * f)
+    return np.ascontiguousarray(codes), np.ascontiguousarray(scales)
 
 
 def shard_head(head, vocab: int, rank: int, world: int):

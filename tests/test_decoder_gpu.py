@@ -154,4 +154,7 @@ def test_batch_of_40_with_swiglu_in_the_projection_epilogue_matches_the_oracle()
         err = np.abs(dec.logits.cpu().numpy() - want)
         assert np.all(err <= 2e-3 + 1e-2 * np.abs(want).max(axis=1, keepdims=True)), (step, float(err.max()))
         ids = oracle.argmax(want).astype(np.int32)
-        assert np.mean(nxt == ids) >= 0.95
+        # a different token only where the oracle's own logits rank the two closer than the runs' logits differ
+        for i in np.nonzero(nxt != ids)[0]:
+            assert float(want[i, ids[i]] - want[i, nxt[i]]) <= 2.0 * float(err[i].max()), (step, i)
+        assert np.mean(nxt == ids) >= 0.9

@@ -151,6 +151,14 @@ cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const 
                              bool swiglu = false);
 // 1 if a bounded device-side wait has timed out since the last call (synchronous read), 0 if not, -1 on a CUDA error.
 int ReadTcStatus();
+// The same projection with the codes fed to the tensor core as int8 and the activations as two int8 planes
+// (int8_gemm_i8.cu); m <= 128 rows per call.
+bool Int8GemmI8Applies(const void* codes, int m, int k, int n);
+size_t Int8GemmI8ScratchBytes(int m, int k);
+cudaError_t LaunchInt8GemmI8(const void* x, int x_dtype, const int8_t* codes, const float* scales, const float* residual,
+                             void* y, int y_dtype, void* scratch, int m, int k, int n, cudaStream_t st, int* launches,
+                             bool weights_const, bool swiglu);
+int ReadI8Status();
 
 inline bool Aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 

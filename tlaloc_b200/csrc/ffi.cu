@@ -292,7 +292,11 @@ extern "C" const char* tlaloc_b200_last_error(void) { return ErrorBuffer(); }
 
 extern "C" long long tlaloc_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
-extern "C" int tlaloc_b200_device_status(void) { return ReadTcStatus(); }
+extern "C" int tlaloc_b200_device_status(void)
+{
+  const int a = ReadTcStatus(), b = ReadI8Status();
+  return a < 0 || b < 0 ? -1 : (a | b);
+}
 
 extern "C" int tlaloc_b200_set_order_faithful(int on)
 {

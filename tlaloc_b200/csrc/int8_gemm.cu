@@ -431,13 +431,30 @@ cudaError_t LaunchGemvRows(const GemmParams& p, int rows, cudaStream_t st)
 
 }  // namespace
 
-// Scratch: the bf16 copy of an f32 x, nothing else.
+// Scratch: the bf16 copy of an f32 x, or the two int8 planes of the activations and their row steps.
 extern "C" size_t tlaloc_b200_int8_gemm_scratch_bytes(int32_t m, int32_t k, int32_t n)
 {
   (void)n;
   if (m <= 0 || k <= 0) return 0;
-  return (sizeof(__nv_bfloat16) * static_cast<size_t>(m) * k + 255) / 256 * 256;
+  return (Int8GemmI8ScratchBytes(m, k) + 255) / 256 * 256;
 }
+
+namespace {
+int TcMinRows()
+{
+  static const int tc_min = [] {
+    const char* v = std::getenv("TLALOC_B200_GEMM_TC_MIN");
+    return v != nullptr ? std::atoi(v) : 17;
+  }();
+  return tc_min;
+}
+// 17 to 128 rows with room in the scratch: the int8 tensor-core kernel.
+bool UseI8(const int8_t* codes, const void* scratch, size_t scratch_bytes, int m, int k, int n, int flags)
+{
+  return (flags & TLALOC_B200_GEMM_BF16_MMA) == 0 && m >= TcMinRows() && Int8GemmI8Applies(codes, m, k, n) && scratch != nullptr && Aligned16(scratch) &&
+         scratch_bytes >= Int8GemmI8ScratchBytes(m, k);
+}
+}  // namespace
 
 extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_t* codes, const float* scales,
                                      const float* residual, void* y, int32_t y_dtype, float* scratch,
@@ -464,6 +481,14 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
   }
   e = PrepareInt8GemmKernels();
   if (e != cudaSuccess) return CudaFail("INT8_PROJ set-up", e);
+  if (UseI8(codes, scratch, scratch_bytes, m, k, n, flags)) {
+    int launches = 0;
+    e = LaunchInt8GemmI8(x, x_dtype, codes, scales, residual, y, y_dtype, scratch, m, k, n, st, &launches,
+                         (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0, false);
+    if (e != cudaSuccess) return CudaFail("INT8_PROJ int8 tensor-core launch", e);
+    CountLaunches(launches);
+    return kOk;
+  }
   const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
   if (x_dtype == TLALOC_B200_F32) {
     const size_t need = sizeof(__nv_bfloat16) * static_cast<size_t>(m) * k;
@@ -478,10 +503,7 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
     CountLaunches(1);
     xb = reinterpret_cast<const __nv_bfloat16*>(scratch);
   }
-  static const int tc_min = [] {
-    const char* v = std::getenv("TLALOC_B200_GEMM_TC_MIN");
-    return v != nullptr ? std::atoi(v) : 17;
-  }();
+  const int tc_min = TcMinRows();
   // 17 rows and more: the tcgen05 kernel (measured at 32 rows: 123 vs 193 us at 57344 x 8192, 190 vs 216 us at the
   // 128256 x 4096 head; at 17 rows 166 vs 198 us; at 8 rows the row-vector kernel is faster, 103 vs ~165 us)
   if (m >= tc_min) {
@@ -553,10 +575,7 @@ extern "C" int tlaloc_b200_int8_gemm_swiglu(const void* x, int32_t x_dtype, cons
     return Fail(kInvalid, "%s: needs [M, K] x [K, N] with N a multiple of 256 (gate|up blocks of 128 + 128), got M %d K %d N %d", op, m, k, n);
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  static const int tc_min = [] {
-    const char* v = std::getenv("TLALOC_B200_GEMM_TC_MIN");
-    return v != nullptr ? std::atoi(v) : 17;
-  }();
+  const int tc_min = TcMinRows();
   const bool aligned = Aligned16(codes) && (x_dtype == TLALOC_B200_F32 || Aligned16(x)) && (reinterpret_cast<uintptr_t>(y) & 7) == 0;
   cudaError_t e;
   if ((flags & TLALOC_B200_GEMM_EXACT) != 0 || OrderFaithful() || !FastShape(k, n) || !aligned || m < tc_min) {
@@ -573,6 +592,14 @@ extern "C" int tlaloc_b200_int8_gemm_swiglu(const void* x, int32_t x_dtype, cons
 #undef TLALOC_SWIGLU_EXACT
     if (e != cudaSuccess) return CudaFail("INT8_PROJ_SWIGLU exact launch", e);
     CountLaunches(1);
+    return kOk;
+  }
+  if (UseI8(codes, scratch, scratch_bytes, m, k, n, flags)) {
+    int launches = 0;
+    e = LaunchInt8GemmI8(x, x_dtype, codes, scales, nullptr, y, y_dtype, scratch, m, k, n, st, &launches,
+                         (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0, true);
+    if (e != cudaSuccess) return CudaFail("INT8_PROJ_SWIGLU int8 tensor-core launch", e);
+    CountLaunches(launches);
     return kOk;
   }
   const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);

@@ -1,0 +1,527 @@
+// The int8 weight-only projection for 17 to 128 rows with the weights left as int8 all the way to the tensor core:
+// y = (cast(x) @ cast(codes)) * scale (HfDecoderGraph.proj, ir/.../inference/HfDecoderGraph.kt:625-655).
+//
+// The bf16 form of this projection (int8_gemm_tc.cu) spends its time turning codes into bf16 on the ALUs and pushing them
+// through shared memory twice.  Here the codes go global -> shared memory by TMA and are read by tcgen05.mma.kind::i8
+// as they are; it is the ACTIVATIONS that change form.  A row of x (bf16; an f32 x is rounded to bf16 first, as the
+// bf16 kernel does) is written as
+//     x[m, k] ~ (256 hi[m, k] + lo[m, k]) * s[m],   s[m] a power of two, hi in [-127, 127], lo in [-128, 127]
+// i.e. a 16-bit fixed-point number under a per-row power-of-two scale: every element within 2^8 of the row's largest
+// magnitude is represented EXACTLY (a bf16 has 8 significant bits), smaller ones are rounded to the nearest multiple of
+// s[m], an absolute error of at most 2^-16 of the row's largest magnitude.  Then
+//     y[m, n] = (256 sum_k hi w + sum_k lo w) * s[m] * scale[n]
+// with both sums exact in int32 (|sum| <= 127 * 127 * K), two MMAs per K step into two TMEM accumulators.  Integer-valued
+// activations come out exact; for others the difference from the f32-accumulating bf16 kernel is far below bf16's own
+// rounding of the inputs.  A row holding an infinity or a NaN gets s = NaN, so its whole output row is NaN.
+//
+// Formulation: D[m, n] = sum_k X[m, k] W[k, n], activation rows = the MMA's M (TMEM lanes), 256 weight columns = its N.
+// A CTA owns 256 columns and one slice of K, walked in blocks of 128 rows through a three-stage ring:
+//   producer thread  one lane; per block four TMA loads (hi strip, lo strip: K-major 128-byte-swizzled [128 rows][128 k];
+//                    the block's codes as two MN-major 128-byte-swizzled boxes [128 k][128 n]: W's rows are contiguous
+//                    along N, which is MN-major, so nothing is transposed) onto the stage's mbarrier;
+//   MMA thread       one lane; per block 4 K-steps x {hi, lo} of 128 x 256 x 32, then a commit that hands the stage back;
+//   sixteen warps    sleep at the CTA barrier until the last MMA has completed, then run the epilogue shared with the
+//                    bf16 kernel (tile in shared memory, scale / residual / SwiGLU, cluster sum over the K slices).
+// Rows past M and k past K are outside the tensor maps and arrive as zeros.  Every mbarrier wait is bounded.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace tlaloc_b200 {
+namespace {
+
+using namespace tc;
+
+constexpr int kI8BK = 128;                        // k rows per block
+constexpr int kI8Stages = 3;
+constexpr int kI8StripBytes = 128 * kI8BK;        // one plane of the activation strip: 128 rows x 128 k
+constexpr int kI8AtomBytes = kI8BK * 128;         // 128 k rows x 128 columns of codes
+constexpr int kI8StageBytes = 2 * kI8StripBytes + 2 * kI8AtomBytes;
+constexpr int kI8PipeBytes = kI8Stages * kI8StageBytes;
+constexpr int kI8TileBytes = 128 * kTcTileStride * 4;  // the epilogue's f32 tile; aliases the ring
+constexpr int kI8BarOffset = kI8PipeBytes > kI8TileBytes ? kI8PipeBytes : (kI8TileBytes + 15) / 16 * 16;
+constexpr int kI8ScaleOffset = kI8BarOffset + 128;
+constexpr int kI8SmemBytes = kI8ScaleOffset + kTcBN * 4 + 1024;  // slack to align to 1024
+constexpr int kI8Workers = 512;                   // the epilogue's threads
+constexpr int kI8Threads = kI8Workers + 64;       // plus the MMA warp and the producer warp
+constexpr int kI8QMax = 127 * 256;                // largest |256 hi + lo| that keeps hi within int8
+static_assert(kI8PipeBytes >= kI8TileBytes, "the tile aliases the ring");
+
+__device__ int g_i8_status = 0;  // nonzero after an mbarrier wait timed out (sticky until read)
+
+struct I8Params {
+  const float* scales;
+  const float* residual;
+  const float* row_scale;  // [M]: s[m]
+  void* y;
+  int M, K, N;
+  int Kc, ks;
+  int weights_const;  // codes and scales are not written by the preceding kernel: fetch them before the dependency wait
+  int swiglu;
+};
+
+// ---- activations -> hi / lo planes ----------------------------------------------------------------------------------
+template <typename XT>
+__device__ __forceinline__ float AsBf16Value(XT v);
+template <>
+__device__ __forceinline__ float AsBf16Value<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float AsBf16Value<float>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// One CTA per row: the row's largest magnitude, the power-of-two step s, then q = x / s (exact: a power of two) rounded
+// to the nearest integer and split as q = 256 hi + lo.
+template <typename XT>
+__global__ void __launch_bounds__(256) QuantizeRowsI8Kernel(const XT* __restrict__ x, int8_t* __restrict__ hi,
+                                                            int8_t* __restrict__ lo, float* __restrict__ row_scale, int K)
+{
+  GridDependencySync();
+  const int m = blockIdx.x, tid = threadIdx.x;
+  const XT* row = x + static_cast<size_t>(m) * K;
+  constexpr int kVec = 16 / sizeof(XT);  // elements per 16-byte load
+  const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0 && K % kVec == 0;
+  float amax = 0.f;
+  bool bad = false;
+  auto see = [&](float v) {
+    const float a = fabsf(v);
+    bad = bad || !(a <= 3.4e38f);
+    amax = fmaxf(amax, a);
+  };
+  if (vec) {
+    for (int i = tid * kVec; i < K; i += 256 * kVec) {
+      const uint4 u = *reinterpret_cast<const uint4*>(row + i);
+      const XT* e = reinterpret_cast<const XT*>(&u);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) see(AsBf16Value<XT>(e[j]));
+    }
+  } else {
+    for (int i = tid; i < K; i += 256) see(AsBf16Value<XT>(row[i]));
+  }
+  __shared__ float s_max[8];
+  __shared__ int s_bad[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const int any_bad = __any_sync(0xffffffffu, bad);
+  if ((tid & 31) == 0) {
+    s_max[tid >> 5] = amax;
+    s_bad[tid >> 5] = any_bad;
+  }
+  __syncthreads();
+  amax = s_max[0];
+  int row_bad = s_bad[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) {
+    amax = fmaxf(amax, s_max[w]);
+    row_bad |= s_bad[w];
+  }
+  // s = 2^e, the smallest power of two with amax / s <= 127 * 256
+  int e = 0;
+  if (amax > 0.f) {
+    int p;
+    frexpf(amax, &p);  // amax = f 2^p, f in [0.5, 1)
+    e = min(max(p - 15, -126), 126);
+    if (ldexpf(amax, -e) > static_cast<float>(kI8QMax)) ++e;
+  }
+  const float inv = ldexpf(1.f, -e);
+  if (tid == 0) row_scale[m] = row_bad ? __int_as_float(0x7fc00000) : ldexpf(1.f, e);
+  int8_t* hrow = hi + static_cast<size_t>(m) * K;
+  int8_t* lrow = lo + static_cast<size_t>(m) * K;
+  auto split = [&](float v, int8_t& h, int8_t& l) {
+    int q = row_bad ? 0 : __float2int_rn(v * inv);
+    q = min(max(q, -kI8QMax), kI8QMax);
+    const int hq = (q + 128) >> 8;
+    h = static_cast<int8_t>(hq);
+    l = static_cast<int8_t>(q - (hq << 8));
+  };
+  if (vec) {
+    for (int i = tid * kVec; i < K; i += 256 * kVec) {
+      const uint4 u = *reinterpret_cast<const uint4*>(row + i);
+      const XT* el = reinterpret_cast<const XT*>(&u);
+      alignas(8) int8_t h[kVec], l[kVec];
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) split(AsBf16Value<XT>(el[j]), h[j], l[j]);
+      if constexpr (kVec == 8) {
+        *reinterpret_cast<uint2*>(hrow + i) = *reinterpret_cast<const uint2*>(h);
+        *reinterpret_cast<uint2*>(lrow + i) = *reinterpret_cast<const uint2*>(l);
+      } else {
+        *reinterpret_cast<uint32_t*>(hrow + i) = *reinterpret_cast<const uint32_t*>(h);
+        *reinterpret_cast<uint32_t*>(lrow + i) = *reinterpret_cast<const uint32_t*>(l);
+      }
+    }
+  } else {
+    for (int i = tid; i < K; i += 256) split(AsBf16Value<XT>(row[i]), hrow[i], lrow[i]);
+  }
+}
+
+// ---- the projection --------------------------------------------------------------------------------------------------
+// kind::i8 instruction descriptor: s32 accumulator, signed 8-bit A and B, A K-major, B MN-major, M = 128, N = 256.
+__host__ __device__ constexpr uint32_t InstrDescI8()
+{
+  return (2u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(kTcBN >> 3) << 17) | (8u << 24);
+}
+__device__ __forceinline__ void TcMmaI8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void MbarExpectTx(uint32_t bar, uint32_t bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// One box of a two-dimensional tensor map into shared memory; (x, y) = (innermost coordinate, row).  x times the element
+// size is always a multiple of 128 bytes here.
+__device__ __forceinline__ void TmaLoad2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar, uint64_t policy)
+{
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar), "l"(policy)
+      : "memory");
+}
+
+template <typename YT>
+__global__ void __launch_bounds__(kI8Threads, 1)
+    Int8GemmI8Kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_hi,
+                     const __grid_constant__ CUtensorMap map_lo, I8Params p)
+{
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = (SmemAddr(smem_raw) + 1023u) & ~1023u;  // the swizzle is a function of address bits 4..9
+  unsigned char* smem = smem_raw + (smem_base - SmemAddr(smem_raw));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int col0 = blockIdx.x * kTcBN;
+  const int kb0 = blockIdx.y * p.Kc;
+  const int ke = min(p.K, kb0 + p.Kc);
+  const int nblocks = ke > kb0 ? (ke - kb0 + kI8BK - 1) / kI8BK : 0;
+  // full[i]: the four boxes of the block in stage i have landed; empty[i]: its MMAs have completed.
+  const uint32_t full0 = smem_base + kI8BarOffset, empty0 = full0 + 8 * kI8Stages;
+  const uint32_t tmem_slot_addr = smem_base + kI8BarOffset + 64;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kI8BarOffset + 64);
+  volatile uint32_t* abort_word = tmem_slot + 1;  // raised by the first wait that gives up
+  float* s_scales = reinterpret_cast<float*>(smem + kI8ScaleOffset);
+
+  if (tid == 0) {
+    *abort_word = 0u;
+    for (int i = 0; i < kI8Stages; ++i) {
+      MbarInit(full0 + 8 * i, 1);
+      MbarInit(empty0 + 8 * i, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tmem_slot_addr), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  bool ok = true;
+  if (warp == kI8Workers / 32 + 1) {
+    // The producer.  Constant weights are requested before the dependency wait (the coldest loads of the launch travel
+    // while the predecessor drains); the activation planes, which the preceding kernel wrote, after it.
+    if (lane == 0) {
+      uint64_t stream_policy, keep_policy;
+      asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(stream_policy));
+      asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(keep_policy));
+      auto load_w = [&](int b) {
+        const int s = b % kI8Stages;
+        const uint32_t dst = smem_base + s * kI8StageBytes + 2 * kI8StripBytes;
+        TmaLoad2d(dst, &map_w, col0, kb0 + b * kI8BK, full0 + 8 * s, stream_policy);
+        TmaLoad2d(dst + kI8AtomBytes, &map_w, col0 + 128, kb0 + b * kI8BK, full0 + 8 * s, stream_policy);
+      };
+      auto load_x = [&](int b) {
+        const int s = b % kI8Stages;
+        const uint32_t dst = smem_base + s * kI8StageBytes;
+        TmaLoad2d(dst, &map_hi, kb0 + b * kI8BK, 0, full0 + 8 * s, keep_policy);
+        TmaLoad2d(dst + kI8StripBytes, &map_lo, kb0 + b * kI8BK, 0, full0 + 8 * s, keep_policy);
+      };
+      const int first = min(nblocks, kI8Stages);
+      if (!p.weights_const) GridDependencySync();
+      for (int b = 0; b < first; ++b) {
+        MbarExpectTx(full0 + 8 * (b % kI8Stages), kI8StageBytes);
+        load_w(b);
+      }
+      if (p.weights_const) GridDependencySync();
+      for (int b = 0; b < first; ++b) load_x(b);
+      for (int b = first; b < nblocks; ++b) {
+        const int s = b % kI8Stages;
+        ok = MbarWait(empty0 + 8 * s, ((b / kI8Stages) - 1) & 1, abort_word) && ok;
+        MbarExpectTx(full0 + 8 * s, kI8StageBytes);
+        load_w(b);
+        load_x(b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == kI8Workers / 32) {
+    // The MMA thread: per block, 4 K-steps of 32; the hi plane into accumulator columns 0..255, the lo plane into
+    // 256..511, both against the same codes.
+    if (lane == 0) {
+      constexpr uint32_t idesc = InstrDescI8();
+      const uint64_t hi0 = SmemDesc(smem_base, 16, 1024), lo0 = SmemDesc(smem_base + kI8StripBytes, 16, 1024);
+      const uint64_t w0 = SmemDesc(smem_base + 2 * kI8StripBytes, kI8AtomBytes, 1024);
+      for (int b = 0; b < nblocks; ++b) {
+        const int s = b % kI8Stages;
+        ok = MbarWait(full0 + 8 * s, (b / kI8Stages) & 1, abort_word) && ok;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint64_t stage = static_cast<uint64_t>((s * kI8StageBytes) >> 4);
+#pragma unroll
+        for (int ks = 0; ks < kI8BK / 32; ++ks) {
+          const uint32_t acc = (b > 0 || ks > 0) ? 1u : 0u;
+          const uint64_t wd = w0 + stage + static_cast<uint64_t>((ks * 32 * 128) >> 4);
+          TcMmaI8(tmem_base, hi0 + stage + static_cast<uint64_t>((ks * 32) >> 4), wd, idesc, acc);
+          TcMmaI8(tmem_base + kTcBN, lo0 + stage + static_cast<uint64_t>((ks * 32) >> 4), wd, idesc, acc);
+        }
+        TcCommit(empty0 + 8 * s);
+      }
+      // The last commit covers every MMA before it.
+      if (nblocks > 0) ok = MbarWait(empty0 + 8 * ((nblocks - 1) % kI8Stages), ((nblocks - 1) / kI8Stages) & 1, abort_word) && ok;
+    }
+    __syncwarp();
+  } else {
+    if (!p.weights_const) GridDependencySync();
+    if (tid < kTcBN) s_scales[tid] = (p.scales != nullptr && col0 + tid < p.N) ? __ldg(p.scales + col0 + tid) : 1.f;
+    if (p.weights_const) GridDependencySync();  // the residual and the row scales belong to earlier kernels
+  }
+  if (!ok) atomicExch(&g_i8_status, 1);
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();  // every MMA has completed and every box has landed; the ring's space is free
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+
+  // Epilogue: warp w reads TMEM lanes 32 (w % 4) .. + 31 (lane = activation row) and the quarter w / 4 of the columns,
+  // 32 at a time from both accumulators, and writes (256 hi + lo) * s[row] as f32 to the row-major tile.
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned nranks = cluster.num_blocks();
+  const bool worker = warp < kI8Workers / 32;
+  float* tile = reinterpret_cast<float*>(smem);
+  const EpilogueOut out{p.residual, p.y, p.M, p.N, p.swiglu};
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0;
+  if (worker) {
+    const int lg = warp & 3, wq = warp >> 2;
+    const int m = lg * 32 + lane;
+    const float rs = m < p.M ? __ldg(p.row_scale + m) : 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t a[32], b[32];
+      if (nblocks > 0) {
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + wq * 64 + h * 32;
+        TcLd32(taddr, a);
+        TcLd32(taddr + kTcBN, b);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) a[e] = b[e] = 0u;
+      }
+      float4* dst = reinterpret_cast<float4*>(tile + m * kTcTileStride + wq * 64 + h * 32);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float4 v;
+        v.x = fmaf(static_cast<float>(static_cast<int>(a[4 * c])), 256.f, static_cast<float>(static_cast<int>(b[4 * c]))) * rs;
+        v.y = fmaf(static_cast<float>(static_cast<int>(a[4 * c + 1])), 256.f, static_cast<float>(static_cast<int>(b[4 * c + 1]))) * rs;
+        v.z = fmaf(static_cast<float>(static_cast<int>(a[4 * c + 2])), 256.f, static_cast<float>(static_cast<int>(b[4 * c + 2]))) * rs;
+        v.w = fmaf(static_cast<float>(static_cast<int>(a[4 * c + 3])), 256.f, static_cast<float>(static_cast<int>(b[4 * c + 3]))) * rs;
+        dst[c] = v;
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  if (nranks == 1) {
+    __syncthreads();
+    if (worker) EpilogueRows<128, YT>(tile, s_scales, out, col0, 0, tid, vec_ok);
+    __syncthreads();
+  } else {
+    cluster.sync();
+    if (worker) EpilogueCluster<YT>(cluster, tile, s_scales, out, col0, tid);
+    cluster.sync();  // no CTA leaves while a peer may still read its tile
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ---- host -----------------------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn EncodeTiled()
+{
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) != cudaSuccess || res != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      ptr = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// A [rows][inner] byte matrix with rows `pitch` bytes apart, read in boxes of 128 bytes x 128 rows, 128-byte swizzle,
+// zeros outside.
+bool ByteMatrixMap(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch)
+{
+  EncodeTiledFn encode = EncodeTiled();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {inner, rows};
+  const cuuint64_t strides[1] = {pitch};
+  const cuuint32_t box[2] = {128, 128};
+  const cuuint32_t elem[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int g_i8_slots[kMaxDevices][9];  // resident CTAs when launched as clusters of ks
+
+void FillI8Slots(int device)
+{
+  for (int ks = 1; ks <= 8; ++ks) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(148, ks, 1);
+    cfg.blockDim = dim3(kI8Threads, 1, 1);
+    cfg.dynamicSmemBytes = kI8SmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = ks;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, Int8GemmI8Kernel<float>, &cfg) != cudaSuccess || clusters <= 0) {
+      cudaGetLastError();
+      clusters = (ks <= 2 ? 148 : ks <= 4 ? 128 : 112) / ks;  // a cautious guess when the query is not available
+    }
+    g_i8_slots[device][ks] = clusters * ks;
+  }
+}
+
+cudaError_t PrepareI8()
+{
+  static OncePerDevice once;
+  return once.Run([](int device) {
+    cudaError_t e = cudaFuncSetAttribute(Int8GemmI8Kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kI8SmemBytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(Int8GemmI8Kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kI8SmemBytes);
+    if (e == cudaSuccess) FillI8Slots(device);
+    return e;
+  });
+}
+
+// K slices (1..8): the lowest modelled time in units of one 128-row block of one CTA,
+//   waves(ks) * (blocks per slice + fixed cost of a CTA [+ cost of the cluster reduction]).
+// $TLALOC_B200_GEMM_KS overrides.
+int ChooseI8Slices(int k, int n)
+{
+  static const int forced = [] {
+    const char* e = std::getenv("TLALOC_B200_GEMM_KS");
+    return e != nullptr ? std::atoi(e) : 0;
+  }();
+  if (forced >= 1 && forced <= 8) return forced;
+  const int tiles = (n + kTcBN - 1) / kTcBN;
+  const int nb = (k + kI8BK - 1) / kI8BK;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) device = 0;
+  int best = 1;
+  double best_cost = 1e30;
+  for (int ks = 1; ks <= 8; ++ks) {
+    if (ks > 1 && nb / ks < 2) break;
+    const int slots = g_i8_slots[device][ks] > 0 ? g_i8_slots[device][ks] : 148 / ks * ks;
+    const int waves = (tiles * ks + slots - 1) / slots;
+    const double per_cta = (nb + ks - 1) / ks + 6.0 + (ks > 1 ? 5.0 + 1.0 * ks : 0.0);
+    const double cost = waves * per_cta;
+    if (cost < best_cost * 0.97) {
+      best_cost = cost;
+      best = ks;
+    }
+  }
+  return best;
+}
+
+template <typename YT>
+cudaError_t LaunchI8(const CUtensorMap& mw, const CUtensorMap& mh, const CUtensorMap& ml, const I8Params& p, cudaStream_t stream)
+{
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.N + kTcBN - 1) / kTcBN, p.ks, 1);
+  cfg.blockDim = dim3(kI8Threads, 1, 1);
+  cfg.dynamicSmemBytes = kI8SmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  cfg.numAttrs = ChainAttributes(attr, p.ks);
+  cfg.attrs = attr;
+  return cudaLaunchKernelEx(&cfg, Int8GemmI8Kernel<YT>, mw, mh, ml, p);
+}
+
+}  // namespace
+
+size_t Int8GemmI8ScratchBytes(int m, int k) { return 2 * static_cast<size_t>(m) * k + 4 * static_cast<size_t>(m); }
+
+bool Int8GemmI8Applies(const void* codes, int m, int k, int n)
+{
+  static const bool enabled = [] {
+    const char* v = std::getenv("TLALOC_B200_GEMM_I8");
+    return v == nullptr || std::atoi(v) != 0;
+  }();
+  return enabled && m >= 1 && m <= 128 && k % 16 == 0 && n % 16 == 0 && Aligned16(codes) && EncodeTiled() != nullptr;
+}
+
+// Rows [0, m), m <= 128, of the projection on the int8 tensor-core kernel.  scratch (16-byte aligned,
+// Int8GemmI8ScratchBytes(m, k) bytes) receives the activation planes and the row steps.
+cudaError_t LaunchInt8GemmI8(const void* x, int x_dtype, const int8_t* codes, const float* scales, const float* residual,
+                             void* y, int y_dtype, void* scratch, int m, int k, int n, cudaStream_t st, int* launches,
+                             bool weights_const, bool swiglu)
+{
+  cudaError_t e = PrepareI8();
+  if (e != cudaSuccess) return e;
+  int8_t* hi = static_cast<int8_t*>(scratch);
+  int8_t* lo = hi + static_cast<size_t>(m) * k;
+  float* row_scale = reinterpret_cast<float*>(lo + static_cast<size_t>(m) * k);
+  e = x_dtype == TLALOC_B200_F32
+          ? LaunchChained(QuantizeRowsI8Kernel<float>, static_cast<unsigned>(m), 256, 0, st, static_cast<const float*>(x), hi, lo, row_scale, k)
+          : LaunchChained(QuantizeRowsI8Kernel<__nv_bfloat16>, static_cast<unsigned>(m), 256, 0, st,
+                          static_cast<const __nv_bfloat16*>(x), hi, lo, row_scale, k);
+  if (e != cudaSuccess) return e;
+  ++*launches;
+  CUtensorMap mw, mh, ml;
+  if (!ByteMatrixMap(&mw, codes, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(n)) ||
+      !ByteMatrixMap(&mh, hi, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k)) ||
+      !ByteMatrixMap(&ml, lo, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k))) {
+    return cudaErrorInvalidValue;
+  }
+  I8Params p;
+  p.scales = scales;
+  p.residual = residual;
+  p.row_scale = row_scale;
+  p.y = y;
+  p.M = m;
+  p.K = k;
+  p.N = n;
+  p.ks = ChooseI8Slices(k, n);
+  const int nb = (k + kI8BK - 1) / kI8BK;
+  p.Kc = (nb + p.ks - 1) / p.ks * kI8BK;
+  p.weights_const = weights_const ? 1 : 0;
+  p.swiglu = swiglu ? 1 : 0;
+  e = y_dtype == TLALOC_B200_F32 ? LaunchI8<float>(mw, mh, ml, p, st) : LaunchI8<__nv_bfloat16>(mw, mh, ml, p, st);
+  if (e != cudaSuccess) return e;
+  ++*launches;
+  return cudaSuccess;
+}
+
+int ReadI8Status()
+{
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_i8_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_i8_status, &zero, sizeof(int));
+  }
+  return v;
+}
+
+}  // namespace tlaloc_b200

@@ -75,9 +75,9 @@ class Decoder:
         sharding.check_world(cfg.num_heads, cfg.num_kv_heads, cfg.ffn, cfg.vocab, world)
         self.cfg, self.batch, self.device, self.rank, self.world, self.group = cfg, batch, torch.device(device), rank, world, group
         self.exact = bool(exact)
-        # SwiGLU in the gate|up projection's epilogue: batches the tensor-core kernel takes (more than 32 rows) and FFN
+        # SwiGLU in the gate|up projection's epilogue: batches the tensor-core kernels take (17 rows and more) and FFN
         # widths that tile in blocks of 128 per rank; $TLALOC_B200_FUSE_SWIGLU=0 keeps the separate kernel
-        self.fuse_swiglu = (not exact and batch > 32 and (cfg.ffn // world) % 128 == 0
+        self.fuse_swiglu = (not exact and batch >= 17 and (cfg.ffn // world) % 128 == 0
                             and os.environ.get("TLALOC_B200_FUSE_SWIGLU", "1") != "0")
         self.hq, self.hk, self.f = cfg.num_heads // world, cfg.num_kv_heads // world, cfg.ffn // world
         self.num_blocks, self.max_blocks = num_blocks, max_blocks_per_seq
@@ -126,6 +126,10 @@ class Decoder:
         self.att = torch.empty((B, self.hq, hd), **bf)
         self.gu = torch.empty((B, 2 * self.f), **f32)
         self.act = torch.empty((B, self.f), **bf)
+        # scratch of the projections (the activations' int8 planes), shared: the projections of a step run one at a time
+        kmax = max(d, self.hq * hd, self.f)
+        self.proj_scratch = (torch.empty((ops.int8_gemm_scratch_bytes(B, kmax, 0) + 3) // 4, **f32)
+                             if 17 <= B <= 128 and not self.exact else None)
         self.logits = torch.empty((B, cfg.vocab // world), **f32)
         self.next_ids = torch.zeros((B,), **i32)
         self.best = torch.empty((B,), **f32)
@@ -227,19 +231,19 @@ class Decoder:
         for l, lw in enumerate(self.layers):
             if l == 0 or not fused:
                 ops.rmsnorm(h, lw["ln1"], cfg.rms_eps, out=self.hn)
-            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True)
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True, scratch=self.proj_scratch)
             ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
                               self.value_pools[l], q_out=self.q_rot)
             ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
                                 scale=cfg.scale, out=self.att, scratch=self.att_scratch)
-            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, weights_const=True)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, weights_const=True, scratch=self.proj_scratch)
             if fused:
                 self.peer.all_reduce_norm_(1, lw["ln2"], cfg.rms_eps)
             else:
                 self._all_reduce(h2)
                 ops.rmsnorm(h2, lw["ln2"], cfg.rms_eps, out=self.hn)
             self.gate_up_proj(lw)
-            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True)
+            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True, scratch=self.proj_scratch)
             if fused:
                 nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
                 self.peer.all_reduce_norm_(0, nxt, cfg.rms_eps)
@@ -260,15 +264,15 @@ class Decoder:
         q3, k3, v3 = self._qkv_views()
         ops.rmsnorm(h, self.layers[0]["ln1"], cfg.rms_eps, out=self.hn)
         for l, lw in enumerate(self.layers):
-            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True)
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True, scratch=self.proj_scratch)
             ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
                               self.value_pools[l], q_out=self.q_rot)
             ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
                                 scale=cfg.scale, out=self.att, scratch=self.att_scratch)
-            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], out=p_o, weights_const=True)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], out=p_o, weights_const=True, scratch=self.proj_scratch)
             self.peer.sum_rows_(0, h, h, lw["ln2"], cfg.rms_eps, norm_out=self.hn)
             self.gate_up_proj(lw)
-            ops.int8_gemm(self.act, *lw["down"], out=p_down, weights_const=True)
+            ops.int8_gemm(self.act, *lw["down"], out=p_down, weights_const=True, scratch=self.proj_scratch)
             nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
             self.peer.sum_rows_(1, h, h, nxt, cfg.rms_eps, norm_out=self.hn)
         self._head_and_greedy()
@@ -280,7 +284,7 @@ class Decoder:
 
     def _head_and_greedy(self) -> None:
         if isinstance(self.head, tuple):
-            ops.int8_gemm(self.hn, *self.head, out=self.logits, weights_const=True)
+            ops.int8_gemm(self.hn, *self.head, out=self.logits, weights_const=True, bf16_mma=True)  # logits: f32 accumulation
         else:
             self.logits.copy_(ops.dense_gemm_exact(self.hn, self.head))
         ops.argmax(self.logits, out=self.next_ids)
@@ -291,9 +295,9 @@ class Decoder:
         """The MLP's first half for one layer: normalised rows `hn` -> `act` = silu(gate) * up, as one projection with
         SwiGLU in its epilogue where the shape allows, else the fused gate|up projection and the SwiGLU kernel."""
         if self.fuse_swiglu:
-            ops.int8_gemm_swiglu(self.hn, *lw["gate_up"], out=self.act, weights_const=True)
+            ops.int8_gemm_swiglu(self.hn, *lw["gate_up"], out=self.act, weights_const=True, scratch=self.proj_scratch)
         else:
-            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True)
+            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True, scratch=self.proj_scratch)
             ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
 
     def _merge_greedy(self) -> None:

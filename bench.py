@@ -243,6 +243,46 @@ class StepBench:
         ms_total = self.max_over_ranks(a.elapsed_time(b))
         return self.batch * K / (ms_total / 1e3), ms_total / K, clocks.summary()
 
+    def time_with_bf16_projections(self, local_gpu: int) -> dict:
+        """The same K replays with the layers' projections on the bf16 form of the tensor-core kernel (f32
+        accumulation of exact bf16 products) instead of the int8 form; the step graph is captured again for it and
+        once more afterwards."""
+        dec = self.dec
+        if not dec.i8_mma:
+            return {"note": "this batch size does not use the int8 form"}
+        dec.i8_mma = False
+        dec.capture()
+        value, ms_step, _ = self.time_value(local_gpu)
+        dec.i8_mma = True
+        dec.capture()
+        return {"value": value, "unit": UNIT, "ms_per_step": ms_step}
+
+    def int8_form_check(self) -> dict:
+        """What the int8 form of the projection does to this step's own numbers: layer 0's q|k|v, o and down
+        projections on the activations the step left behind, in both forms, against a double-precision product."""
+        from tlaloc_b200 import ops
+
+        torch, dec = self.torch, self.dec
+        lw = dec.layers[0]
+        B = self.batch
+        rows = {}
+        for name, x in (("qkv", dec.hn), ("o", dec.att.view(B, -1)), ("down", dec.act)):
+            codes, scales = lw[name]
+            ref = torch.empty((B, codes.shape[1]), dtype=torch.float64, device=self.dev)
+            xd = x.double()
+            for c0 in range(0, codes.shape[1], 4096):  # column blocks keep the double copy of the codes small
+                ref[:, c0:c0 + 4096] = (xd @ codes[:, c0:c0 + 4096].double()) * scales[c0:c0 + 4096].double()
+            rms = float(ref.pow(2).mean().sqrt())
+            out = {"output_rms": rms}
+            for form, flag in (("int8", True), ("bf16", False)):
+                y = ops.int8_gemm(x, codes, scales, i8_mma=flag).double()
+                err = (y - ref).abs()
+                out[form] = {"rms_err_over_output_rms": float(err.pow(2).mean().sqrt()) / max(rms, 1e-30), "max_abs_err": float(err.max()),
+                             "beyond_rel_1e-2_abs_2e-3": int((err > 2e-3 + 1e-2 * ref.abs()).sum())}
+            rows[name] = out
+        return {"rows": rows, "what": "layer 0 projections of this step, each form against an f64 product of the same bf16 "
+                                      "activations and int8 codes; the int8 form carries a row as 16-bit fixed point"}
+
     def time_e2e(self) -> dict:
         """Host buffers in, next tokens out, every step."""
         torch, dec, K, W = self.torch, self.dec, self.K, self.W
@@ -332,11 +372,12 @@ class StepBench:
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         L = len(dec.layers)
         hq, hd = dec.hq, self.cfg.head_dim
+        how = dict(weights_const=True, scratch=dec.proj_scratch, i8_mma=dec.i8_mma)  # as the step launches them
         calls = {
-            "qkv": lambda lw: ops.int8_gemm(dec.hn, *lw["qkv"], out=dec.qkv, weights_const=True),
-            "o": lambda lw: ops.int8_gemm(dec.att.view(B, hq * hd), *lw["o"], residual=dec.h, out=dec.h2, weights_const=True),
+            "qkv": lambda lw: ops.int8_gemm(dec.hn, *lw["qkv"], out=dec.qkv, **how),
+            "o": lambda lw: ops.int8_gemm(dec.att.view(B, hq * hd), *lw["o"], residual=dec.h, out=dec.h2, **how),
             "gate_up": lambda lw: dec.gate_up_proj(lw),
-            "down": lambda lw: ops.int8_gemm(dec.act, *lw["down"], residual=dec.h2, out=dec.h, weights_const=True),
+            "down": lambda lw: ops.int8_gemm(dec.act, *lw["down"], residual=dec.h2, out=dec.h, **how),
         }
         rows, t_sum, f_sum = [], 0.0, 0.0
         for name, fn in calls.items():
@@ -358,7 +399,8 @@ class StepBench:
                          "tflops": flops / us / 1e6, "floor_us": floor_us, "frac_of_floor": floor_us / us})
             t_sum += us
             f_sum += floor_us
-        return {"kernel": "Int8GemmTcKernel" if B > 32 else "Int8GemvKernel", "bound": "hbm | tensor (the slower floor)",
+        kernel = "QuantizeRowsI8Kernel + Int8GemmI8Kernel" if dec.i8_mma else "Int8GemmTcKernel" if B >= 17 else "Int8GemvKernel"
+        return {"kernel": kernel, "bound": "hbm | tensor (the slower floor)",
                 "rows": rows, "us_per_layer": t_sum, "floor_us_per_layer": f_sum, "frac": f_sum / t_sum,
                 "peak_kind": pk["kind"], "hbm_gbs": pk["hbm_gbs"], "bf16_tflops_sustained": pk["bf16_tflops_sustained"]}
 
@@ -543,7 +585,8 @@ def run_ours(args) -> dict:
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": f"int8 weights x bf16, f32 accumulate; {'bf16' if args.kv == 'bf16' else 'f8e4m3fn'} KV", "data": "synthetic",
+        "dtype": (f"int8 weights x bf16 activations ({'rows as 16-bit fixed point on the int8 tensor-core form, int32 accumulate' if dec.i8_mma else 'f32 accumulate'}"
+                  f"; head and attention f32 accumulate); {'bf16' if args.kv == 'bf16' else 'f8e4m3fn'} KV"), "data": "synthetic",
         "config": workload_config(sb.wl_name, batch, cfg.num_layers, world, {
             "mean_context": float(lens_now.mean()), "kv_blocks_per_layer": sb.num_blocks,
             "kv_blocks_logical": sb.logical_blocks, "kv_aliased": bool(sb.aliased),
@@ -559,6 +602,8 @@ def run_ours(args) -> dict:
         line["tp_parity"] = parity
     if world == 1 and not args.lean:
         line["roofline_projection"] = sb.projection_roofline(pk)
+        line["int8_form_check"] = sb.int8_form_check()
+        line["with_bf16_projections"] = sb.time_with_bf16_projections(local)
     if world > 1:
         # Print first, then leave without tearing the communicator down: destroying a process group whose
         # collectives live inside a CUDA graph blocks, and the process is about to exit anyway.
@@ -669,9 +714,12 @@ def operator_int8_projection(torch, dev, pk, only="") -> dict:
 
     rows = []
     shapes, ms = [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)], (1, 8, 32, 128, 256)
-    if only:  # one shape "NxKxM", for profiler captures
-        n, k, m = (int(v) for v in only.lower().split("x"))
+    forms = {32: ("bf16", "int8"), 128: ("bf16", "int8")}  # the tensor-core kernel's two forms where both apply
+    if only:  # one shape "NxKxM" or "NxKxMxi8", for profiler captures
+        parts = only.lower().split("x")
+        n, k, m = (int(v) for v in parts[:3])
         shapes, ms = [(n, k)], (m,)
+        forms = {m: ("int8",) if parts[3:] == ["i8"] else ("bf16",)}
     for (n, k) in shapes:
         nbuf = max(4, int(400e6 // (k * n)) + 1)  # distinct weight buffers, > 3x L2 in total, visited round robin
         ws = [torch.randint(-127, 128, (k, n), dtype=torch.int8, device=dev) for _ in range(nbuf)]
@@ -680,18 +728,22 @@ def operator_int8_projection(torch, dev, pk, only="") -> dict:
             x = torch.randn((m, k), device=dev).to(torch.bfloat16)
             y = torch.empty((m, n), dtype=torch.float32, device=dev)
             scr = torch.empty((ops.int8_gemm_scratch_bytes(m, k, n) + 3) // 4, dtype=torch.float32, device=dev)
+            for form in forms.get(m, ("",)):
+                i8 = form == "int8"
 
-            def fn():
-                for w in ws:
-                    ops.int8_gemm(x, w, sc, out=y, weights_const=True, scratch=scr)
-            best, med = _time_graph(torch, fn, 10)
-            byts = k * n + 4 * n + 2 * m * k + 4 * m * n
-            us = med / nbuf * 1e3
-            row = {"N": n, "K": k, "M": m, "us": us, "gbs": byts / us / 1e3, "tflops": 2.0 * m * n * k / us / 1e6}
-            row["frac_hbm"] = row["gbs"] / pk["hbm_gbs"]
-            if m >= 256:
-                row["frac_tensor"] = row["tflops"] / pk["bf16_tflops"]
-            rows.append(row)
+                def fn():
+                    for w in ws:
+                        ops.int8_gemm(x, w, sc, out=y, weights_const=True, scratch=scr, i8_mma=i8)
+                best, med = _time_graph(torch, fn, 10)
+                byts = k * n + 4 * n + 2 * m * k + 4 * m * n
+                us = med / nbuf * 1e3
+                row = {"N": n, "K": k, "M": m, "us": us, "gbs": byts / us / 1e3, "tflops": 2.0 * m * n * k / us / 1e6}
+                if form:
+                    row["tensor_core_form"] = form
+                row["frac_hbm"] = row["gbs"] / pk["hbm_gbs"]
+                if m >= 256:
+                    row["frac_tensor"] = row["tflops"] / pk["bf16_tflops"]
+                rows.append(row)
         del ws
     return {"rows": rows, "hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "peak_kind": pk["kind"]}
 

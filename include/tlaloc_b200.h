@@ -190,12 +190,12 @@ size_t tlaloc_b200_int8_gemm_scratch_bytes(int32_t m, int32_t k, int32_t n);
  *   y       device [M, N]  y_dtype F32 | BF16
  *   scratch device memory, 16-byte aligned, contents undefined on entry and exit, or NULL:
  *           tlaloc_b200_int8_gemm_scratch_bytes(m, k, n) bytes.  An F32 x needs it (its bf16 copy); with it, 17 to 128
- *           rows take the int8 tensor-core kernel below, without it the bf16 one.
+ *           rows may take the int8 tensor-core kernel below (TLALOC_B200_GEMM_I8_MMA).
  *
  * Kernels by row count: up to 16 rows a row-vector kernel (HBM-bound); 17 rows and more a tcgen05 kernel, in one of two
  * forms.  BF16 form: the codes become exact bf16 on the way into shared memory, bf16 x bf16 -> f32 in tensor memory;
- * only the f32 summation order differs from the reference's.  INT8 form (17 to 128 rows, K and N multiples of 16,
- * scratch given, $TLALOC_B200_GEMM_I8 not 0, TLALOC_B200_GEMM_BF16_MMA not set): the codes reach the tensor core as they
+ * only the f32 summation order differs from the reference's.  INT8 form (opt-in: flag TLALOC_B200_GEMM_I8_MMA, 17 to 128
+ * rows, K and N multiples of 16, scratch given, $TLALOC_B200_GEMM_I8 not 0; otherwise the BF16 form runs): the codes reach the tensor core as they
  * are (TMA, kind::i8) and each activation row becomes a 16-bit fixed-point number under a power-of-two row step s[m],
  * x ~ (256 hi + lo) s[m] with hi, lo int8, so y = (256 sum hi w + sum lo w) s[m] scale[n] with exact int32 sums.
  * Elements within 2^8 of their row's largest magnitude are exact (so are integer-valued rows); the rest round to a
@@ -217,8 +217,9 @@ size_t tlaloc_b200_int8_gemm_scratch_bytes(int32_t m, int32_t k, int32_t n);
 /* codes and scales are constants of the program: no kernel placed just before this call in the stream writes them.
  * Lets the batched-row kernel request its first weights while that kernel is still finishing (results are the same). */
 #define TLALOC_B200_GEMM_WEIGHTS_CONST 4
-/* keep the BF16 form of the tensor-core kernel (f32 accumulation of exact products) even where the INT8 form applies */
-#define TLALOC_B200_GEMM_BF16_MMA 8
+/* take the INT8 form of the tensor-core kernel where it applies (activations as 16-bit fixed point per row, exact
+ * int32 sums); without it the BF16 form (f32 accumulation of exact products) runs */
+#define TLALOC_B200_GEMM_I8_MMA 8
 int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_t* codes, const float* scales,
                           const float* residual, void* y, int32_t y_dtype, float* scratch, size_t scratch_bytes,
                           int32_t m, int32_t k, int32_t n, int32_t flags, void* stream);

@@ -42,6 +42,7 @@ class TlalocB200Ffm private constructor(arena: Arena, library: Path) {
         const val GEMM_EXACT = 1
         const val GEMM_X_F32_EXACT = 2
         const val GEMM_WEIGHTS_CONST = 4
+        const val GEMM_I8_MMA = 8
 
         fun load(arena: Arena, library: Path): TlalocB200Ffm {
             val lib = TlalocB200Ffm(arena, library)
@@ -121,6 +122,18 @@ class TlalocB200Ffm private constructor(arena: Arena, library: Path) {
             JAVA_INT, ADDRESS,                    // flags, stream
         ),
     )
+    private val int8GemmSwiglu = handle(
+        "tlaloc_b200_int8_gemm_swiglu",
+        FunctionDescriptor.of(
+            JAVA_INT,
+            ADDRESS, JAVA_INT,                    // x, x_dtype
+            ADDRESS, ADDRESS,                     // codes (gate|up interleaved in blocks of 128 + 128), scales
+            ADDRESS, JAVA_INT,                    // y [M, N / 2], y_dtype
+            ADDRESS, JAVA_LONG,                   // scratch, scratch_bytes
+            JAVA_INT, JAVA_INT, JAVA_INT,         // m, k, n
+            JAVA_INT, ADDRESS,                    // flags, stream
+        ),
+    )
     private val denseGemmExact = handle(
         "tlaloc_b200_dense_gemm_exact",
         FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS),
@@ -166,6 +179,14 @@ class TlalocB200Ffm private constructor(arena: Arena, library: Path) {
         "tlaloc_b200_peer_allreduce_rmsnorm_f32",
         FunctionDescriptor.of(
             JAVA_INT, ADDRESS, JAVA_LONG, JAVA_LONG, JAVA_LONG, ADDRESS, ADDRESS, JAVA_FLOAT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS,
+        ),
+    )
+    private val peerSumRows = handle(
+        "tlaloc_b200_peer_sum_rows_f32",
+        FunctionDescriptor.of(
+            JAVA_INT, ADDRESS, JAVA_LONG, JAVA_LONG, ADDRESS,   // bases, partial_offset, flag_offset, state
+            ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_FLOAT,     // residual, out, norm_out, gain, eps
+            JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS,    // rank, world, rows, cols, stream
         ),
     )
     private val registerKernels = handle("TlalocRegisterKernels", FunctionDescriptor.of(ADDRESS, ADDRESS))
@@ -242,6 +263,15 @@ class TlalocB200Ffm private constructor(arena: Arena, library: Path) {
         int8Gemm.invokeExact(ptr(x), xDtype, ptr(codes), ptr(scales), ptr(residual), ptr(y), yDtype, ptr(scratch), scratchBytes, m, k, n, flags, ptr(stream)) as Int,
     )
 
+    /** silu(x @ gate) * (x @ up) over one weight [K, 2F] with gate and up interleaved in column blocks of 128 + 128 (mlpOut). */
+    @Suppress("LongParameterList")
+    fun int8GemmSwiglu(
+        x: Long, xDtype: Int, codes: Long, scales: Long, y: Long, yDtype: Int, scratch: Long, scratchBytes: Long,
+        m: Int, k: Int, n: Int, flags: Int, stream: Long,
+    ) = check(
+        int8GemmSwiglu.invokeExact(ptr(x), xDtype, ptr(codes), ptr(scales), ptr(y), yDtype, ptr(scratch), scratchBytes, m, k, n, flags, ptr(stream)) as Int,
+    )
+
     fun denseGemmExact(x: Long, xDtype: Int, w: Long, wDtype: Int, y: Long, m: Int, k: Int, n: Int, flags: Int, stream: Long) =
         check(denseGemmExact.invokeExact(ptr(x), xDtype, ptr(w), wDtype, ptr(y), m, k, n, flags, ptr(stream)) as Int)
 
@@ -305,6 +335,21 @@ class TlalocB200Ffm private constructor(arena: Arena, library: Path) {
         val table = arena.allocate(ADDRESS, bases.size.toLong())
         bases.forEachIndexed { i, b -> table.setAtIndex(ADDRESS, i.toLong(), ptr(b)) }
         check(peerAllReduceNorm.invokeExact(table, dataOffset, normOffset, flagOffset, ptr(state), ptr(gain), eps, rank, bases.size, rows, cols, ptr(stream)) as Int)
+    }
+
+    /** The one-barrier sum: out = residual + the ranks' partials at partialOffset, and the RMSNorm of it, all local. */
+    @Suppress("LongParameterList")
+    fun peerSumRowsF32(
+        arena: Arena, bases: LongArray, partialOffset: Long, flagOffset: Long, state: Long, residual: Long, out: Long, normOut: Long,
+        gain: Long, eps: Float, rank: Int, rows: Int, cols: Int, stream: Long,
+    ) {
+        val table = arena.allocate(ADDRESS, bases.size.toLong())
+        bases.forEachIndexed { i, b -> table.setAtIndex(ADDRESS, i.toLong(), ptr(b)) }
+        check(
+            peerSumRows.invokeExact(
+                table, partialOffset, flagOffset, ptr(state), ptr(residual), ptr(out), ptr(normOut), ptr(gain), eps, rank, bases.size, rows, cols, ptr(stream),
+            ) as Int,
+        )
     }
 
     /** TlalocRegisterKernels(PJRT_Api*): null on success, else the library's message. */

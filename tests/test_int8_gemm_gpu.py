@@ -38,15 +38,16 @@ def model_like_weights(rng, k, n):
     return oracle.quantize_int8((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
 
 
-def make(rng, m, k, n, x_int=False):
-    """Integer activations (exactness cases), or normalised ones against uniform codes whose scales give outputs of
-    order 1, as a model's projections do."""
+def make(rng, m, k, n, x_int=False, unit_outputs=False):
+    """The operator sweep's inputs: uniform codes, scales U(0.001, 0.02), N(0, 1) activations (outputs of rms ~60), or
+    integer activations for the exactness cases.  `unit_outputs` divides the scales by 64 so that the outputs are of
+    order 1, as a model's projections are: the cases that also run the int8 tensor-core form use it, because that
+    form's absolute error scales with the output (see the error-bound test) while the abs 2e-3 bar does not."""
     codes = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    scales = (rng.uniform(0.001, 0.02, size=n) / (64.0 if unit_outputs else 1.0)).astype(np.float32)
     if x_int:
-        scales = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
         x = rng.integers(-8, 9, size=(m, k)).astype(np.float32)
     else:
-        scales = (rng.uniform(0.001, 0.02, size=n) / 64.0).astype(np.float32)
         x = oracle.snap_bf16(rng.standard_normal((m, k)).astype(np.float32))
     return x, codes, scales
 
@@ -73,12 +74,12 @@ def test_integer_activations_give_the_exact_integer_dot_product(m, k, n):
     assert np.array_equal(got.cpu().numpy(), want * scales[None, :])
 
 
-@pytest.mark.parametrize("bf16_mma", [False, True])
+@pytest.mark.parametrize("i8_mma", [True, False])
 @pytest.mark.parametrize("m", [17, 33, 64, 100, 128, 256, 300])
 @pytest.mark.parametrize("k,n", [(4096, 4096), (1024, 14336), (14336, 1024), (256, 688), (688, 256), (2048, 4112), (64, 256), (8240, 1296)])
-def test_batched_rows_on_the_tensor_core_kernel_are_exact_on_integer_activations(m, k, n, bf16_mma):
-    """17 rows and more take a tcgen05 kernel: up to 128 rows the int8 form (codes by TMA, activations as two int8
-    planes) unless `bf16_mma` keeps the bf16 form (int8 -> bf16 in shared memory); accumulators in TMEM either way.
+def test_batched_rows_on_the_tensor_core_kernel_are_exact_on_integer_activations(m, k, n, i8_mma):
+    """17 rows and more take a tcgen05 kernel: the bf16 form (int8 -> bf16 in shared memory) or, with `i8_mma` and up to
+    128 rows, the int8 form (codes by TMA, activations as two int8 planes); accumulators in TMEM either way.
     K = 688 is not a multiple of 16, which the int8 form needs: those cases run the bf16 form twice."""
     from tlaloc_b200 import _native as N
 
@@ -87,25 +88,25 @@ def test_batched_rows_on_the_tensor_core_kernel_are_exact_on_integer_activations
     want = (x.astype(np.float64) @ codes.astype(np.float64)).astype(np.float32)  # exact: every partial sum is an integer below 2^53
     scales = np.exp2(rng.integers(-8, -2, size=n)).astype(np.float32)
     res = rng.integers(-50, 50, size=(m, n)).astype(np.float32)
-    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), residual=dev(res), bf16_mma=bf16_mma)
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), residual=dev(res), i8_mma=i8_mma)
     torch.cuda.synchronize()
     assert N.lib().tlaloc_b200_device_status() == 0
     assert np.array_equal(got.cpu().numpy(), want * scales[None, :] + res)
 
 
-@pytest.mark.parametrize("bf16_mma", [False, True])
+@pytest.mark.parametrize("i8_mma", [True, False])
 @pytest.mark.parametrize("m", [64, 256])
-def test_batched_rows_against_the_oracle(m, bf16_mma):
+def test_batched_rows_against_the_oracle(m, i8_mma):
     rng = np.random.default_rng(8)
     k, n = 4096, 14336
-    x, codes, scales = make(rng, m, k, n)
+    x, codes, scales = make(rng, m, k, n, unit_outputs=i8_mma)
     want = oracle.proj_int8(x, codes, scales, round_x_bf16=True, threads=8)
-    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), bf16_mma=bf16_mma)
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), i8_mma=i8_mma)
     torch.cuda.synchronize()
     worst = close(got.cpu().numpy(), want)
     assert worst <= 1e-4 * max(1.0, np.abs(want).max())
     # declaring the weights constant only moves their first loads ahead of the dependency wait: same bits
-    again = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), weights_const=True, bf16_mma=bf16_mma)
+    again = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), weights_const=True, i8_mma=i8_mma)
     torch.cuda.synchronize()
     assert torch.equal(again, got)
 
@@ -201,9 +202,9 @@ STEP_SHAPES = [(8192, 10240), (8192, 8192), (8192, 57344), (28672, 8192),
                (8192, 1280), (1024, 8192), (8192, 7168), (3584, 8192)]
 
 
-@pytest.mark.parametrize("bf16_mma", [False, True])
+@pytest.mark.parametrize("i8_mma", [True, False])
 @pytest.mark.parametrize("k,n", STEP_SHAPES)
-def test_decode_step_shapes_at_128_rows(k, n, bf16_mma):
+def test_decode_step_shapes_at_128_rows(k, n, i8_mma):
     """Exact on integer activations over the whole output; against the oracle on a sample of rows for N(0,1) ones;
     on the int8 and on the bf16 form of the tensor-core kernel."""
     from tlaloc_b200 import _native as N
@@ -216,13 +217,13 @@ def test_decode_step_shapes_at_128_rows(k, n, bf16_mma):
     scales = np.exp2(rng.integers(-8, -2, size=n)).astype(np.float32)
     res = rng.integers(-50, 50, size=(m, n)).astype(np.float32)
     want, tc = _exact_want_on_device(x, codes, scales, res)
-    got = ops().int8_gemm(dev(x, torch.bfloat16), tc, dev(scales), residual=dev(res), weights_const=True, bf16_mma=bf16_mma)
+    got = ops().int8_gemm(dev(x, torch.bfloat16), tc, dev(scales), residual=dev(res), weights_const=True, i8_mma=i8_mma)
     torch.cuda.synchronize()
     assert N.lib().tlaloc_b200_device_status() == 0
     assert torch.equal(got, want)
     xn = oracle.snap_bf16(rng.standard_normal((m, k)).astype(np.float32))
-    sc = (rng.uniform(0.001, 0.02, size=n) / 64.0).astype(np.float32)  # outputs of order 1, like a model's
-    got = ops().int8_gemm(dev(xn, torch.bfloat16), tc, dev(sc), bf16_mma=bf16_mma).cpu().numpy()
+    sc = (rng.uniform(0.001, 0.02, size=n) / (64.0 if i8_mma else 1.0)).astype(np.float32)  # int8 form: outputs of order 1
+    got = ops().int8_gemm(dev(xn, torch.bfloat16), tc, dev(sc), i8_mma=i8_mma).cpu().numpy()
     rows = [0, 77, 127]
     wantn = oracle.proj_int8(xn[rows], codes, sc, round_x_bf16=True, threads=oracle.host_threads())
     worst = close(got[rows], wantn)
@@ -244,7 +245,7 @@ def test_vocabulary_head_shape_at_1_32_and_256_rows(m):
     assert N.lib().tlaloc_b200_device_status() == 0
     assert torch.equal(got, want)
     xn = oracle.snap_bf16(rng.standard_normal((m, k)).astype(np.float32))
-    sc = (rng.uniform(0.001, 0.02, size=n) / 64.0).astype(np.float32)
+    sc = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
     got = ops().int8_gemm(dev(xn, torch.bfloat16), tc, dev(sc)).cpu().numpy()
     rows = sorted({0, m // 2, m - 1})
     wantn = oracle.proj_int8(xn[rows], codes, sc, round_x_bf16=True, threads=oracle.host_threads())
@@ -295,9 +296,9 @@ def test_every_code_value_converts_exactly(m):
     assert np.array_equal(got.cpu().numpy(), want.astype(np.float32))
 
 
-@pytest.mark.parametrize("bf16_mma", [False, True])
+@pytest.mark.parametrize("i8_mma", [True, False])
 @pytest.mark.parametrize("m,k,n2", [(128, 512, 512), (64, 4096, 2048), (33, 256, 256), (200, 1024, 7168), (128, 8192, 1024), (256, 688, 512), (8, 512, 512)])
-def test_gate_up_projection_with_swiglu_in_the_epilogue(m, k, n2, bf16_mma):
+def test_gate_up_projection_with_swiglu_in_the_epilogue(m, k, n2, i8_mma):
     """tlaloc_b200_int8_gemm_swiglu against the two-step path (gate|up projection, then the SwiGLU kernel) on the same
     weights: the same f32 sums meet the same SiLU arithmetic, so the results are bit-equal on the bf16 tensor-core
     kernel and within f32 rounding of the K slices' partial sums on the int8 one; and against the oracle.  Shapes cover
@@ -310,20 +311,20 @@ def test_gate_up_projection_with_swiglu_in_the_epilogue(m, k, n2, bf16_mma):
     x = oracle.snap_bf16(rng.standard_normal((m, k)).astype(np.float32))
     gate, up = model_like_weights(rng, k, f), model_like_weights(rng, k, f)
     codes, scales = sharding.interleave_gate_up(gate, up)
-    got = ops().int8_gemm_swiglu(dev(x, torch.bfloat16), dev(codes), dev(scales), out_dtype=torch.float32, bf16_mma=bf16_mma)
+    got = ops().int8_gemm_swiglu(dev(x, torch.bfloat16), dev(codes), dev(scales), out_dtype=torch.float32, i8_mma=i8_mma)
     torch.cuda.synchronize()
     assert N.lib().tlaloc_b200_device_status() == 0
-    g = ops().int8_gemm(dev(x, torch.bfloat16), dev(gate[0]), dev(gate[1]), bf16_mma=bf16_mma)
-    u = ops().int8_gemm(dev(x, torch.bfloat16), dev(up[0]), dev(up[1]), bf16_mma=bf16_mma)
+    g = ops().int8_gemm(dev(x, torch.bfloat16), dev(gate[0]), dev(gate[1]), i8_mma=i8_mma)
+    u = ops().int8_gemm(dev(x, torch.bfloat16), dev(up[0]), dev(up[1]), i8_mma=i8_mma)
     two_step = ops().swiglu(g, u)
     torch.cuda.synchronize()
     want = oracle.swiglu(oracle.proj_int8(x, gate[0], gate[1], threads=8), oracle.proj_int8(x, up[0], up[1], threads=8))
     close(got.cpu().numpy(), want)
-    if m > 32 and (bf16_mma or m > 128 or k % 16):
+    if m > 32 and (not i8_mma or m > 128 or k % 16):
         assert torch.equal(got, two_step)
     elif m > 32:
         assert torch.allclose(got, two_step, rtol=1e-5, atol=1e-6)
-    got_b = ops().int8_gemm_swiglu(dev(x, torch.bfloat16), dev(codes), dev(scales), bf16_mma=bf16_mma)
+    got_b = ops().int8_gemm_swiglu(dev(x, torch.bfloat16), dev(codes), dev(scales), i8_mma=i8_mma)
     assert got_b.dtype == torch.bfloat16 and np.array_equal(got_b.float().cpu().numpy(), oracle.snap_bf16(got.cpu().numpy()))
 
 
@@ -346,13 +347,13 @@ def test_int8_tensor_core_kernel_stays_inside_its_error_bound_on_outlier_channel
     x[:, ::97] *= 60.0
     x = oracle.snap_bf16(x)
     exact = (torch.from_numpy(x).to(DEV).double() @ torch.from_numpy(codes).to(DEV).double()).cpu().numpy() * scales[None, :].astype(np.float64)
-    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales)).double().cpu().numpy()
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), i8_mma=True).double().cpu().numpy()
     bound = 0.5 * _row_steps(x)[:, None] * (scales.astype(np.float64) * np.abs(codes.astype(np.float64)).sum(axis=0))[None, :]
     err = np.abs(got - exact)
     assert np.all(err <= bound + 4e-7 * np.abs(exact) + 1e-30), float((err - bound).max())
     assert err.max() > 0  # the bound is not vacuous: these rows do lose bits
     assert np.sqrt((err ** 2).mean()) <= 1e-3 * np.sqrt((exact ** 2).mean())
-    got_bf = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), bf16_mma=True).double().cpu().numpy()
+    got_bf = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales)).double().cpu().numpy()
     assert np.sqrt(((got_bf - exact) ** 2).mean()) <= 1e-5 * np.sqrt((exact ** 2).mean())
 
 
@@ -360,10 +361,10 @@ def test_int8_tensor_core_kernel_rows_with_infinity_or_nan_come_out_nan_and_leav
     rng = np.random.default_rng(21)
     m, k, n = 40, 512, 512
     x, codes, scales = make(rng, m, k, n)
-    clean = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales)).cpu().numpy()
+    clean = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), i8_mma=True).cpu().numpy()
     x[3, 17] = np.inf
     x[9, 400] = np.nan
-    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales)).cpu().numpy()
+    got = ops().int8_gemm(dev(x, torch.bfloat16), dev(codes), dev(scales), i8_mma=True).cpu().numpy()
     assert np.isnan(got[3]).all() and np.isnan(got[9]).all()
     keep = [r for r in range(m) if r not in (3, 9)]
     assert np.array_equal(got[keep], clean[keep])
@@ -371,7 +372,7 @@ def test_int8_tensor_core_kernel_rows_with_infinity_or_nan_come_out_nan_and_leav
     x = oracle.snap_bf16(rng.standard_normal((m, k)).astype(np.float32))
     x[5] = 0.0
     xf = x + rng.uniform(-1e-4, 1e-4, size=x.shape).astype(np.float32) * (x != 0)
-    a = ops().int8_gemm(dev(oracle.snap_bf16(xf), torch.bfloat16), dev(codes), dev(scales))
-    b = ops().int8_gemm(dev(xf), dev(codes), dev(scales))
+    a = ops().int8_gemm(dev(oracle.snap_bf16(xf), torch.bfloat16), dev(codes), dev(scales), i8_mma=True)
+    b = ops().int8_gemm(dev(xf), dev(codes), dev(scales), i8_mma=True)
     torch.cuda.synchronize()
     assert torch.equal(a, b) and not a[5].any()

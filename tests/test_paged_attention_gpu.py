@@ -327,6 +327,29 @@ def test_one_kv_head_per_rank_shape_against_the_oracle_on_sampled_rows():
         assert err.max() <= tol_of(want), (r, float(err.max()))
 
 
+def test_long_contexts_with_empty_tables_between_and_a_window_on_the_tensor_core_kernel():
+    """48 tables x 8 KV heads at up to 16384 positions (four 4096-position slices each), tables of length 0 and 1 in
+    between, and a sliding window that moves the first live position off zero.  Pool blocks are shared between tables
+    (512 physical blocks) to keep the case small; the oracle walks sampled rows."""
+    rng = np.random.default_rng(48)
+    B, Hq, Hk, Dh, bs, nb, width = 48, 16, 8, 128, 16, 512, 1024
+    lens = rng.integers(15000, 16385, size=B).astype(np.int32)
+    lens[[3, 4, 20, 47]] = 0
+    lens[[0, 7, 30]] = [16384, 1, 8193]
+    q = as_bf16(rng.standard_normal((B, Hq, Dh)).astype(np.float32))
+    k = as_bf16(rng.standard_normal((nb, bs, Hk, Dh)).astype(np.float32))
+    v = as_bf16(rng.standard_normal((nb, bs, Hk, Dh)).astype(np.float32))
+    tab = rng.integers(0, nb, size=(B, width)).astype(np.int32)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(Dh)))
+    rows = [0, 2, 3, 7, 19, 20, 21, 30, 46, 47]
+    for w in (None, 5000):
+        got = run(q, k, v, tab, lens, scale, q_dtype=torch.bfloat16, kv_dtype=torch.bfloat16, sliding_window=w,
+                  out=torch.empty((B, Hq, Dh), dtype=torch.float32, device=DEV))
+        want = oracle.paged_attention(q[rows], k, v, tab[rows], lens[rows], scale, sliding_window=w, threads=oracle.host_threads())
+        assert np.abs(got[rows] - want).max() <= tol_of(want), w
+        assert not got[[3, 4, 20, 47]].any()  # a row of length 0 is all zeros
+
+
 def test_pools_off_a_16_byte_boundary_take_the_generic_kernel():
     """A pool that starts 2 bytes into an allocation must not reach the tensor-core kernel's 16-byte copies."""
     rng = np.random.default_rng(13)

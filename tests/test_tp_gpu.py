@@ -37,7 +37,7 @@ def run_ranks(worker: str, world: int = 2, limit: float = 240.0, **extra_env) ->
 
 
 @two_gpus
-@pytest.mark.parametrize("reduce", ["peer", "peer2", "nccl"])
+@pytest.mark.parametrize("reduce", ["peer1", "peer2", "nccl"])
 def test_two_gpu_tensor_parallel_decoder_matches_the_oracle(reduce):
     outs = run_ranks("tp_worker.py", TLALOC_B200_TP_REDUCE=reduce)
     assert "TP2 ok" in outs[0]

@@ -12,7 +12,7 @@ from . import build as _build
 
 F32, BF16, S8, S32, F8E4M3FN = 11, 16, 2, 4, 20
 OK, INVALID_ARGUMENT, UNSUPPORTED, INTERNAL = 0, -1, -2, -3
-GEMM_EXACT, GEMM_X_F32_EXACT, GEMM_WEIGHTS_CONST, GEMM_BF16_MMA = 1, 2, 4, 8
+GEMM_EXACT, GEMM_X_F32_EXACT, GEMM_WEIGHTS_CONST, GEMM_I8_MMA = 1, 2, 4, 8
 
 _lib = None
 

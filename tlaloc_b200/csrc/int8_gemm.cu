@@ -448,10 +448,10 @@ int TcMinRows()
   }();
   return tc_min;
 }
-// 17 to 128 rows with room in the scratch: the int8 tensor-core kernel.
+// 17 to 128 rows, the caller's consent and room in the scratch: the int8 tensor-core kernel.
 bool UseI8(const int8_t* codes, const void* scratch, size_t scratch_bytes, int m, int k, int n, int flags)
 {
-  return (flags & TLALOC_B200_GEMM_BF16_MMA) == 0 && m >= TcMinRows() && Int8GemmI8Applies(codes, m, k, n) && scratch != nullptr && Aligned16(scratch) &&
+  return (flags & TLALOC_B200_GEMM_I8_MMA) != 0 && m >= TcMinRows() && Int8GemmI8Applies(codes, m, k, n) && scratch != nullptr && Aligned16(scratch) &&
          scratch_bytes >= Int8GemmI8ScratchBytes(m, k);
 }
 }  // namespace

@@ -102,16 +102,22 @@ class Decoder:
         # step buffers
         nqkv = (self.hq + 2 * self.hk) * hd
         # Tensor parallelism, the sum over ranks after o_proj and down_proj.  $TLALOC_B200_TP_REDUCE:
-        #   "peer" (default)  the library's one-barrier kernel: the projections write their partial results into two
-        #                     alternating peer-mapped buffers, and every rank builds residual + sum (and the next
-        #                     RMSNorm) locally from all ranks' partials;
-        #   "peer2"           the two-phase in-place kernel (reduce-scatter + all-gather over the residual buffers);
+        #   "peer" (default)  the library's peer-memory kernels: at 2 ranks the one-barrier kernel ("peer1"), at more the
+        #                     two-phase one ("peer2");
+        #   "peer1"           the one-barrier kernel: the projections write their partial results into two alternating
+        #                     peer-mapped buffers, and every rank builds residual + sum (and the next RMSNorm) locally
+        #                     from all ranks' partials.  Every rank reads (world - 1) whole buffers, so its traffic
+        #                     grows with the world size: 4 MiB at 2 ranks, 28 MiB at 8;
+        #   "peer2"           the two-phase in-place kernel (reduce-scatter + all-gather over the residual buffers,
+        #                     2 (world - 1) / world buffers of traffic per rank whatever the world size);
         #   "nccl"            NCCL's all-reduce on private buffers.
         self.peer, self.one_shot = None, False
         mode = os.environ.get("TLALOC_B200_TP_REDUCE", "peer") if world > 1 else "none"
-        if mode in ("peer", "peer2"):
+        if mode == "peer":
+            mode = "peer1" if world <= 2 else "peer2"
+        if mode in ("peer1", "peer2"):
             self.peer = PeerBuffers([(B, d), (B, d)], rank=rank, world=world, group=group, device=dev, norm_shape=(B, d))
-            self.one_shot = mode == "peer" and self.peer.can_sum_rows(0)
+            self.one_shot = mode == "peer1" and self.peer.can_sum_rows(0)
         if self.peer is not None and not self.one_shot:
             self.h, self.h2 = self.peer.tensors  # summed in place
         else:
@@ -126,10 +132,12 @@ class Decoder:
         self.att = torch.empty((B, self.hq, hd), **bf)
         self.gu = torch.empty((B, 2 * self.f), **f32)
         self.act = torch.empty((B, self.f), **bf)
-        # scratch of the projections (the activations' int8 planes), shared: the projections of a step run one at a time
+        # Batches of 17 to 128 rows run the layers' projections on the int8 tensor-core kernel (the activations as
+        # 16-bit fixed point per row; $TLALOC_B200_GEMM_I8=0 keeps the bf16 one).  Their int8 planes live in a scratch
+        # that the projections share: the projections of a step run one at a time.
+        self.i8_mma = 17 <= B <= 128 and not self.exact
         kmax = max(d, self.hq * hd, self.f)
-        self.proj_scratch = (torch.empty((ops.int8_gemm_scratch_bytes(B, kmax, 0) + 3) // 4, **f32)
-                             if 17 <= B <= 128 and not self.exact else None)
+        self.proj_scratch = torch.empty((ops.int8_gemm_scratch_bytes(B, kmax, 0) + 3) // 4, **f32) if self.i8_mma else None
         self.logits = torch.empty((B, cfg.vocab // world), **f32)
         self.next_ids = torch.zeros((B,), **i32)
         self.best = torch.empty((B,), **f32)
@@ -231,19 +239,19 @@ class Decoder:
         for l, lw in enumerate(self.layers):
             if l == 0 or not fused:
                 ops.rmsnorm(h, lw["ln1"], cfg.rms_eps, out=self.hn)
-            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True, scratch=self.proj_scratch)
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
             ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
                               self.value_pools[l], q_out=self.q_rot)
             ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
                                 scale=cfg.scale, out=self.att, scratch=self.att_scratch)
-            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, weights_const=True, scratch=self.proj_scratch)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
             if fused:
                 self.peer.all_reduce_norm_(1, lw["ln2"], cfg.rms_eps)
             else:
                 self._all_reduce(h2)
                 ops.rmsnorm(h2, lw["ln2"], cfg.rms_eps, out=self.hn)
             self.gate_up_proj(lw)
-            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True, scratch=self.proj_scratch)
+            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
             if fused:
                 nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
                 self.peer.all_reduce_norm_(0, nxt, cfg.rms_eps)
@@ -264,15 +272,15 @@ class Decoder:
         q3, k3, v3 = self._qkv_views()
         ops.rmsnorm(h, self.layers[0]["ln1"], cfg.rms_eps, out=self.hn)
         for l, lw in enumerate(self.layers):
-            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True, scratch=self.proj_scratch)
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
             ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
                               self.value_pools[l], q_out=self.q_rot)
             ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
                                 scale=cfg.scale, out=self.att, scratch=self.att_scratch)
-            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], out=p_o, weights_const=True, scratch=self.proj_scratch)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], out=p_o, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
             self.peer.sum_rows_(0, h, h, lw["ln2"], cfg.rms_eps, norm_out=self.hn)
             self.gate_up_proj(lw)
-            ops.int8_gemm(self.act, *lw["down"], out=p_down, weights_const=True, scratch=self.proj_scratch)
+            ops.int8_gemm(self.act, *lw["down"], out=p_down, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
             nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
             self.peer.sum_rows_(1, h, h, nxt, cfg.rms_eps, norm_out=self.hn)
         self._head_and_greedy()
@@ -284,7 +292,7 @@ class Decoder:
 
     def _head_and_greedy(self) -> None:
         if isinstance(self.head, tuple):
-            ops.int8_gemm(self.hn, *self.head, out=self.logits, weights_const=True, bf16_mma=True)  # logits: f32 accumulation
+            ops.int8_gemm(self.hn, *self.head, out=self.logits, weights_const=True)  # the logits stay on f32 accumulation
         else:
             self.logits.copy_(ops.dense_gemm_exact(self.hn, self.head))
         ops.argmax(self.logits, out=self.next_ids)
@@ -295,9 +303,9 @@ class Decoder:
         """The MLP's first half for one layer: normalised rows `hn` -> `act` = silu(gate) * up, as one projection with
         SwiGLU in its epilogue where the shape allows, else the fused gate|up projection and the SwiGLU kernel."""
         if self.fuse_swiglu:
-            ops.int8_gemm_swiglu(self.hn, *lw["gate_up"], out=self.act, weights_const=True, scratch=self.proj_scratch)
+            ops.int8_gemm_swiglu(self.hn, *lw["gate_up"], out=self.act, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
         else:
-            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True, scratch=self.proj_scratch)
+            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
             ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
 
     def _merge_greedy(self) -> None:

@@ -107,11 +107,11 @@ def kv_cache_write(pool, new_kv, slot_mapping):
 
 
 def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.float32, exact=False, x_f32_exact=False,
-              scratch=None, weights_const=False, bf16_mma=False):
+              scratch=None, weights_const=False, i8_mma=False):
     """y = (cast(x) @ cast(codes)) * scales (+ residual): x [M, K], codes int8 [K, N] (in, out), scales f32 [N].
     `weights_const`: no kernel queued just before this call writes codes or scales (true of a loaded model).
-    `bf16_mma`: 17 to 128 rows stay on the bf16 tensor-core kernel (f32 accumulation of exact products) instead of the
-    int8 one (activations as 16-bit fixed point per row)."""
+    `i8_mma`: 17 to 128 rows take the int8 tensor-core kernel (codes straight to the tensor core, activations as 16-bit
+    fixed point per row, exact int32 sums) instead of the bf16 one (f32 accumulation of exact products)."""
     _dev(x, codes, scales, residual)
     M, K = x.shape
     K2, Nn = codes.shape
@@ -121,13 +121,13 @@ def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.floa
         out = torch.empty((M, Nn), dtype=out_dtype, device=x.device)
     _out("INT8_PROJ out", out, (M, Nn), (torch.float32, torch.bfloat16), x)
     _out("INT8_PROJ residual", residual, (M, Nn), torch.float32, x)
-    # an f32 x is cast to bf16 in the scratch; 17 to 128 rows leave their int8 planes there
-    if scratch is None and not exact and (x.dtype == torch.float32 or 17 <= M <= 128):
+    # an f32 x is cast to bf16 in the scratch; the int8 tensor-core kernel leaves the activations' int8 planes there
+    if scratch is None and not exact and (x.dtype == torch.float32 or (i8_mma and 17 <= M <= 128)):
         scratch = torch.empty((N.lib().tlaloc_b200_int8_gemm_scratch_bytes(M, K, Nn) + 3) // 4, dtype=torch.float32,
                               device=x.device)
     _out("INT8_PROJ scratch", scratch, None, torch.float32, x)
     flags = ((N.GEMM_EXACT if exact else 0) | (N.GEMM_X_F32_EXACT if x_f32_exact else 0)
-             | (N.GEMM_WEIGHTS_CONST if weights_const else 0) | (N.GEMM_BF16_MMA if bf16_mma else 0))
+             | (N.GEMM_WEIGHTS_CONST if weights_const else 0) | (N.GEMM_I8_MMA if i8_mma else 0))
     N.check(N.lib().tlaloc_b200_int8_gemm(_ptr(x), _dt(x), _ptr(codes), _ptr(scales), _ptr(residual), _ptr(out), _dt(out),
                                           _ptr(scratch), 0 if scratch is None else scratch.numel() * 4, M, K, Nn, flags,
                                           _stream(x)))
@@ -135,7 +135,7 @@ def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.floa
 
 
 def int8_gemm_swiglu(x, codes, scales, *, out=None, out_dtype=torch.bfloat16, exact=False, scratch=None, weights_const=False,
-                     bf16_mma=False):
+                     i8_mma=False):
     """silu(x @ gate) * (x @ up) with gate and up interleaved in `codes` [K, 2F] in column blocks of 128 + 128
     (sharding.interleave_gate_up); returns [M, F]."""
     _dev(x, codes, scales)
@@ -147,10 +147,10 @@ def int8_gemm_swiglu(x, codes, scales, *, out=None, out_dtype=torch.bfloat16, ex
     if out is None:
         out = torch.empty((M, Nn // 2), dtype=out_dtype, device=x.device)
     _out("INT8_PROJ_SWIGLU out", out, (M, Nn // 2), (torch.float32, torch.bfloat16), x)
-    if scratch is None and not exact and (x.dtype == torch.float32 or 17 <= M <= 128):
+    if scratch is None and not exact and (x.dtype == torch.float32 or (i8_mma and 17 <= M <= 128)):
         scratch = torch.empty((N.lib().tlaloc_b200_int8_gemm_scratch_bytes(M, K, Nn) + 3) // 4, dtype=torch.float32, device=x.device)
     _out("INT8_PROJ_SWIGLU scratch", scratch, None, torch.float32, x)
-    flags = (N.GEMM_EXACT if exact else 0) | (N.GEMM_WEIGHTS_CONST if weights_const else 0) | (N.GEMM_BF16_MMA if bf16_mma else 0)
+    flags = (N.GEMM_EXACT if exact else 0) | (N.GEMM_WEIGHTS_CONST if weights_const else 0) | (N.GEMM_I8_MMA if i8_mma else 0)
     N.check(N.lib().tlaloc_b200_int8_gemm_swiglu(_ptr(x), _dt(x), _ptr(codes), _ptr(scales), _ptr(out), _dt(out), _ptr(scratch),
                                                  0 if scratch is None else scratch.numel() * 4, M, K, Nn, flags, _stream(x)))
     return out

@@ -232,8 +232,8 @@ int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_t* codes, c
  *           (both in the staged [in, out] layout; tlaloc_b200.sharding.interleave_gate_up builds it at load time)
  *   scales  f32 [N] in the same column order, or NULL
  *   y       [M, F] F32 | BF16: silu(gate * scale) * (up * scale), SiLU in f32 as tlaloc_b200_swiglu computes it
- * More than 32 rows run on the tensor-core kernel; fewer rows, unaligned pointers, parity mode and GEMM_EXACT take an
- * order-faithful kernel (slow).  scratch as tlaloc_b200_int8_gemm (an F32 x only).
+ * 17 rows and more run on a tensor-core kernel; fewer rows, unaligned pointers, parity mode and GEMM_EXACT take an
+ * order-faithful kernel (slow).  scratch and flags as tlaloc_b200_int8_gemm (an F32 x, or TLALOC_B200_GEMM_I8_MMA).
  */
 int tlaloc_b200_int8_gemm_swiglu(const void* x, int32_t x_dtype, const int8_t* codes, const float* scales, void* y,
                                  int32_t y_dtype, float* scratch, size_t scratch_bytes, int32_t m, int32_t k, int32_t n,

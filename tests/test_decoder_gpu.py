@@ -125,7 +125,7 @@ def test_tiny_decoder_64_greedy_steps_match_the_oracle(kv_dtype, head_quant, exa
 
 
 def test_batch_of_40_with_swiglu_in_the_projection_epilogue_matches_the_oracle():
-    """More than 32 rows and an FFN width that tiles in blocks of 128: the engine runs the tensor-core projection and
+    """17 to 128 rows and an FFN width that tiles in blocks of 128: the engine runs the int8 tensor-core projection and
     folds SwiGLU into the gate|up projection's epilogue (weights interleaved at load).  Against the oracle's step."""
     from tlaloc_b200 import decoder as D
     from tlaloc_b200 import sharding

@@ -62,6 +62,20 @@ def test_paged_attention_int8_gemm_and_kv_write_through_call_frames():
     stream.synchronize()
     wanty = oracle.proj_int8(x, codes, scales, round_x_bf16=True) + res
     assert np.abs(y.cpu().numpy() - wanty).max() <= 1e-4 * max(1.0, np.abs(wanty).max())
+    # --- the same call with 40 integer-valued rows and the i8_mma attribute: the int8 tensor-core kernel, exact sums
+    m2 = 40
+    x2 = rng.integers(-8, 9, size=(m2, kk)).astype(np.float32)
+    tx2, y2 = t(x2), torch.zeros((m2, n), device=DEV)
+    sc2 = torch.empty((m2 * kk,), device=DEV)  # 4 bytes per element: more than the two int8 planes and the row steps need
+    torch.cuda.synchronize()
+    before = lib.tlaloc_b200_launch_count()
+    a = [xla.buffer(F.F32, tx2.data_ptr(), x2.shape), xla.buffer(F.S8, tw.data_ptr(), codes.shape), xla.buffer(F.F32, ts.data_ptr(), (n,))]
+    r = [xla.buffer(F.F32, y2.data_ptr(), (m2, n)), xla.buffer(F.F32, sc2.data_ptr(), (m2 * kk,))]
+    assert F.handler(lib, "tlaloc_int8_gemm")(C.byref(xla.frame(F.EXECUTE, a, r, {"i8_mma": (F.S32, C.c_int32(1))}))) is None, xla.errors
+    stream.synchronize()
+    assert lib.tlaloc_b200_launch_count() - before == 2  # the row quantizer and the projection
+    want2 = (x2.astype(np.float64) @ codes.astype(np.float64)).astype(np.float32) * scales[None, :]
+    assert np.array_equal(y2.cpu().numpy(), want2)
     # --- KV write into a distinct result buffer: the pool is copied, then the rows land; negative slot = padding
     pool = rng.standard_normal((6, 16, 2, 64)).astype(np.float32)
     rows = rng.standard_normal((3, 2, 64)).astype(np.float32)

@@ -87,3 +87,59 @@ def test_the_operator_configuration_shape():
     tab = np.stack([rng.permutation(nb)[:width] for _ in range(B)]).astype(np.int32)
     got, ref = both(q, k, v, tab, lens, float(D ** -0.5), torch.bfloat16)
     assert np.abs(got - ref).max() <= 1e-4, float(np.abs(got - ref).max())
+
+
+def test_same_gpu_timing_of_both_kernels_on_the_operator_configuration(capsys):
+    """Both handlers on the operator configuration with nothing shared between sequences (every (sequence, 16
+    positions) its own block: all K/V bytes come from HBM), f32 query, bf16 pools, 20 calls each after 3 warm-ups, CUDA
+    events on the handlers' stream.  Prints the two times (run with -s to see them); asserts only that both ran and
+    agree."""
+    rng = np.random.default_rng(1)
+    B, H, Hkv, D, bs, width = 32, 32, 8, 128, 16, 512
+    lens = rng.integers(512, 8193, size=B).astype(np.int32)
+    need = (lens + bs - 1) // bs
+    nb = int(need.sum()) + 1
+    perm = 1 + rng.permutation(nb - 1)
+    tab = np.zeros((B, width), np.int32)
+    o = 0
+    for i in range(B):
+        tab[i, :need[i]] = perm[o:o + need[i]]
+        o += int(need[i])
+    from tlaloc_b200 import _native as N
+
+    g = torch.Generator(device=DEV)
+    g.manual_seed(1)
+    tk = torch.randn((nb, bs, Hkv, D), device=DEV, generator=g).to(torch.bfloat16)
+    tv = torch.randn((nb, bs, Hkv, D), device=DEV, generator=g).to(torch.bfloat16)
+    tq = torch.randn((B, H, D), device=DEV, generator=g)
+    tt, tl = torch.from_numpy(tab).to(DEV), torch.from_numpy(lens).to(DEV)
+    S = (width * bs + 255) // 256
+    stream = torch.cuda.Stream(device=DEV)
+    xla = F.FakeXla(stream=stream.cuda_stream)
+    scale = float(D ** -0.5)
+    times, outs = {}, {}
+    for name, h in (("this library", F.handler(N.lib(), "tlaloc_paged_attention")), ("reference kernel", ref_handler())):
+        assert h(C.byref(xla.frame(F.INITIALIZE))) is None, xla.errors
+        out = torch.zeros((B, H, D), device=DEV)
+        scratch = torch.zeros((S, B, H, D + 2), device=DEV)
+        a = [xla.buffer(F.F32, tq.data_ptr(), tq.shape), xla.buffer(F.BF16, tk.data_ptr(), tk.shape), xla.buffer(F.BF16, tv.data_ptr(), tv.shape),
+             xla.buffer(F.S32, tt.data_ptr(), tab.shape), xla.buffer(F.S32, tl.data_ptr(), lens.shape)]
+        r = [xla.buffer(F.F32, out.data_ptr(), tq.shape), xla.buffer(F.F32, scratch.data_ptr(), scratch.shape)]
+        frame = xla.frame(F.EXECUTE, a, r, {"scale": (F.F32, C.c_float(scale))})
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                assert h(C.byref(frame)) is None, xla.errors
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(20):
+                assert h(C.byref(frame)) is None, xla.errors
+            e1.record(stream)
+        stream.synchronize()
+        times[name] = e0.elapsed_time(e1) / 20 * 1e3
+        outs[name] = out.cpu().numpy()
+    byts = 2 * int(lens.sum()) * Hkv * D * 2 + B * H * D * 8
+    with capsys.disabled():
+        for name, us in times.items():
+            print(f"\n{name}: {us:.1f} us per call, {byts / us / 1e3:.0f} GB/s on the live K/V bytes (f32 query, bf16 pools, nothing shared)")
+    assert np.abs(outs["this library"] - outs["reference kernel"]).max() <= 1e-4

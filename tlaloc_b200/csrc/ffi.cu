@@ -185,8 +185,9 @@ AbiFfiError* PagedAttentionHandler(AbiFfiCallFrame* frame)
 }
 
 // tlaloc_int8_gemm: operands x [M,K] (f32|bf16), codes s8 [K,N], scales f32 [N], optional residual f32 [M,N];
-// results y [M,N] (f32|bf16), optional scratch (any f32 buffer; needed for an f32 x).  Attribute exact (s32,
-// optional, nonzero = the order-faithful kernel).  The custom-call form of HfDecoderGraph.proj over an int8
+// results y [M,N] (f32|bf16), optional scratch (any f32 buffer; needed for an f32 x and for i8_mma).  Attributes
+// exact (s32, optional, nonzero = the order-faithful kernel) and i8_mma (s32, optional, nonzero = 17 to 128 rows on the
+// int8 tensor-core kernel, TLALOC_B200_GEMM_I8_MMA).  The custom-call form of HfDecoderGraph.proj over an int8
 // weight, which the reference leaves to XLA as convert + dot_general + multiply.
 AbiFfiError* Int8GemmHandler(AbiFfiCallFrame* frame)
 {
@@ -212,10 +213,13 @@ AbiFfiError* Int8GemmHandler(AbiFfiCallFrame* frame)
   if (res != nullptr && (res->rank != 2 || res->dtype != TLALOC_B200_F32 || res->dims[0] != y->dims[0] || res->dims[1] != y->dims[1])) {
     return invalid("the residual must be f32 [M, N]");
   }
-  int64_t exact = 0;
+  int64_t exact = 0, i8_mma = 0;
   for (int64_t i = 0; i < frame->attrs.size; ++i) {
-    if (frame->attrs.types[i] == kAbiFfiAttrScalar && NameIs(frame->attrs.names[i], "exact")) {
+    if (frame->attrs.types[i] != kAbiFfiAttrScalar) continue;
+    if (NameIs(frame->attrs.names[i], "exact")) {
       if (!ScalarInt(static_cast<const AbiFfiScalar*>(frame->attrs.values[i]), &exact)) return invalid("'exact' must be s32");
+    } else if (NameIs(frame->attrs.names[i], "i8_mma")) {
+      if (!ScalarInt(static_cast<const AbiFfiScalar*>(frame->attrs.values[i]), &i8_mma)) return invalid("'i8_mma' must be s32");
     }
   }
   size_t scratch_bytes = 0;
@@ -229,8 +233,8 @@ AbiFfiError* Int8GemmHandler(AbiFfiCallFrame* frame)
       x->data, x->dtype, static_cast<const int8_t*>(w->data), static_cast<const float*>(s->data),
       res ? static_cast<const float*>(res->data) : nullptr, y->data, y->dtype,
       scratch ? static_cast<float*>(scratch->data) : nullptr, scratch_bytes, static_cast<int32_t>(x->dims[0]),
-      static_cast<int32_t>(x->dims[1]), static_cast<int32_t>(w->dims[1]), exact != 0 ? TLALOC_B200_GEMM_EXACT : 0,
-      stream);
+      static_cast<int32_t>(x->dims[1]), static_cast<int32_t>(w->dims[1]),
+      (exact != 0 ? TLALOC_B200_GEMM_EXACT : 0) | (i8_mma != 0 ? TLALOC_B200_GEMM_I8_MMA : 0), stream);
   return FromStatus(api, target, status);
 }
 

@@ -1,7 +1,8 @@
 // The int8 weight-only projection y = (cast(x) @ cast(codes)) * scale for sm_100a
 // (HfDecoderGraph.proj over WeightQuant.INT8, ir/.../inference/HfDecoderGraph.kt:625-655).
 //
-//   Int8GemvKernel   decode rows (M <= 32 per launch; more rows run as several launches).  HBM-bound: every
+//   Int8GemvKernel   decode rows (M <= 32 per launch; by default only up to 16 rows come here, 17 and more go to the
+//                    tensor-core kernels of int8_gemm_tc.cu and int8_gemm_i8.cu).  HBM-bound: every
 //                    weight byte is read once, from the reference's own [K, N] layout (no repacking).  A CTA owns
 //                    128 output columns and one slice of K; each of its four warps is an independent cp.async
 //                    pipeline over its own 32-row stages (a 32 x 128 int8 weight tile plus the matching 32-wide

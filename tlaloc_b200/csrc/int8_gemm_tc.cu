@@ -1,4 +1,4 @@
-// The int8 weight-only projection for batches of rows (33 and more; at most 256 per launch) on the 5th-generation tensor
+// The int8 weight-only projection for batches of rows (17 and more; at most 256 per launch) on the 5th-generation tensor
 // cores: y = (cast(x) @ cast(codes)) * scale (HfDecoderGraph.proj, ir/.../inference/HfDecoderGraph.kt:625-655).
 //
 // Formulation: D[m, n] = sum_k X[m, k] W[k, n].  The activation rows are the MMA's M dimension (TMEM lanes, always

@@ -373,10 +373,11 @@ class StepBench:
         L = len(dec.layers)
         hq, hd = dec.hq, self.cfg.head_dim
         how = dict(weights_const=True, scratch=dec.proj_scratch, i8_mma=dec.i8_mma)  # as the step launches them
+        xp = bool(dec.norm_planes)  # q|k|v and gate|up find their input's planes already written by the RMSNorm kernel
         calls = {
-            "qkv": lambda lw: ops.int8_gemm(dec.hn, *lw["qkv"], out=dec.qkv, **how),
+            "qkv": lambda lw: ops.int8_gemm(dec.hn, *lw["qkv"], out=dec.qkv, x_planes=xp, **how),
             "o": lambda lw: ops.int8_gemm(dec.att.view(B, hq * hd), *lw["o"], residual=dec.h, out=dec.h2, **how),
-            "gate_up": lambda lw: dec.gate_up_proj(lw),
+            "gate_up": lambda lw: dec.gate_up_proj(lw, x_planes=xp),
             "down": lambda lw: ops.int8_gemm(dec.act, *lw["down"], residual=dec.h2, out=dec.h, **how),
         }
         rows, t_sum, f_sum = [], 0.0, 0.0

@@ -220,6 +220,9 @@ size_t tlaloc_b200_int8_gemm_scratch_bytes(int32_t m, int32_t k, int32_t n);
 /* take the INT8 form of the tensor-core kernel where it applies (activations as 16-bit fixed point per row, exact
  * int32 sums); without it the BF16 form (f32 accumulation of exact products) runs */
 #define TLALOC_B200_GEMM_I8_MMA 8
+/* with GEMM_I8_MMA: the scratch already holds the activation planes of this x (written by tlaloc_b200_rmsnorm_planes or
+ * tlaloc_b200_peer_sum_rows_f32 for exactly this [m, k]); ignored when the call does not take the INT8 form */
+#define TLALOC_B200_GEMM_X_PLANES 16
 int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_t* codes, const float* scales,
                           const float* residual, void* y, int32_t y_dtype, float* scratch, size_t scratch_bytes,
                           int32_t m, int32_t k, int32_t n, int32_t flags, void* stream);
@@ -258,6 +261,16 @@ int tlaloc_b200_embedding(const void* table, int32_t table_dtype, const int32_t*
  */
 int tlaloc_b200_rmsnorm(const float* x, const float* gain, void* out, int32_t out_dtype, int32_t rows, int32_t n,
                         float eps, void* stream);
+
+/*
+ * The same with a BF16 out, and the normalised rows also written as the activation planes of the int8 tensor-core
+ * projection (see tlaloc_b200_int8_gemm): `planes` is that projection's scratch for an [rows, n] activation
+ * (tlaloc_b200_int8_gemm_scratch_bytes(rows, n, 0) bytes, 16-byte aligned; n a multiple of 16).  The projection that
+ * consumes `out` is then called with the same scratch and TLALOC_B200_GEMM_X_PLANES and skips its own quantizer launch.
+ * The planes are exactly what that launch would have written.
+ */
+int tlaloc_b200_rmsnorm_planes(const float* x, const float* gain, void* out, void* planes, int32_t rows, int32_t n, float eps,
+                               void* stream);
 
 /*
  * RoPE (HfDecoderGraph.kt:792-818, HF rotate_half with the duplicated cos/sin tables of
@@ -337,11 +350,14 @@ int tlaloc_b200_peer_allreduce_rmsnorm_f32(void* const* bases, size_t data_offse
  *   residual  local f32 [rows, cols] or NULL; may equal out (the residual stream updated in place)
  *   flag words (world of them at flag_offset) and state as tlaloc_b200_peer_allreduce_f32; calls of the three functions
  *   may be mixed on one state if every rank makes the same calls in the same order.
+ *   planes    NULL, or (with norm_out) the scratch of the int8 tensor-core projection that consumes norm_out
+ *             (tlaloc_b200_int8_gemm_scratch_bytes(rows, cols, 0) bytes, 16-byte aligned, cols a multiple of 16): the
+ *             normalised rows are also written as that projection's activation planes (TLALOC_B200_GEMM_X_PLANES)
  * cols a multiple of 4 up to 8192.  world == 1 is legal (out = residual + partial).
  */
 int tlaloc_b200_peer_sum_rows_f32(void* const* bases, size_t partial_offset, size_t flag_offset, uint32_t* state,
                                   const float* residual, float* out, void* norm_out, const float* gain, float eps,
-                                  int32_t rank, int32_t world, int32_t rows, int32_t cols, void* stream);
+                                  int32_t rank, int32_t world, int32_t rows, int32_t cols, void* planes, void* stream);
 
 /* ------------------------------------------------------------------ XLA typed-FFI registration */
 

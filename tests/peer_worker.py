@@ -16,6 +16,7 @@ def rank_input(shape, rank, round_):
 
 
 def main():
+    from tlaloc_b200 import ops
     from tlaloc_b200.peer import PeerBuffers
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -110,8 +111,19 @@ def main():
         twin.tensors[which].copy_(torch.from_numpy(rank_input(shapes[1], rank, round_)))
         if use_res:
             res.copy_(torch.from_numpy(rank_input(shapes[1], 99, round_)))
-        twin.sum_rows_(which, res if use_res else None, out, gain if rep != 2 else None, 1e-5, norm_out=normed)
+        planes = torch.zeros((ops.int8_gemm_scratch_bytes(shapes[1][0], shapes[1][1], 0) + 3) // 4, device=dev) if rep == 3 else None
+        twin.sum_rows_(which, res if use_res else None, out, gain if rep != 2 else None, 1e-5, norm_out=normed, planes=planes)
         check_one_shot(round_, which, use_res, gain if rep != 2 else None)
+        if planes is not None:
+            # the planes the kernel left for the int8 tensor-core projection are what that projection's own quantizer
+            # writes for the same bf16 rows (it is launched by a projection call without x_planes)
+            rows_, cols_ = shapes[1]
+            other = torch.zeros_like(planes)
+            codes = torch.zeros((cols_, 256), dtype=torch.int8, device=dev)
+            ops.int8_gemm(normed, codes, None, scratch=other, i8_mma=True)
+            torch.cuda.synchronize(dev)
+            used = (2 * rows_ * cols_ + 4 * rows_) // 4
+            assert torch.equal(planes[:used].view(torch.int32), other[:used].view(torch.int32))
     # in place on the residual stream, replayed from a graph: h += sum(partial 0); h += sum(partial 1); ten times
     hbuf = torch.zeros(shapes[1], device=dev)
     srcs = [torch.empty(shapes[1], device=dev) for _ in range(2)]

@@ -376,3 +376,38 @@ def test_int8_tensor_core_kernel_rows_with_infinity_or_nan_come_out_nan_and_leav
     b = ops().int8_gemm(dev(xf), dev(codes), dev(scales), i8_mma=True)
     torch.cuda.synchronize()
     assert torch.equal(a, b) and not a[5].any()
+
+
+@pytest.mark.parametrize("rows,n", [(128, 8192), (40, 512), (17, 16384), (64, 4096)])
+def test_rmsnorm_writes_the_planes_the_projections_quantizer_would(rows, n):
+    """tlaloc_b200_rmsnorm_planes leaves, beside the bf16 rows, the activation planes of the int8 tensor-core projection
+    that consumes them: bit for bit what that projection's own quantizer launch writes for the same rows (hi, lo and the
+    row steps), so the projection called with x_planes gives the same bits with one launch less.  16384 columns take the
+    two-launch fallback (the row does not fit the registers)."""
+    from tlaloc_b200 import _native as N
+
+    rng = np.random.default_rng(rows + n)
+    x = rng.standard_normal((rows, n)).astype(np.float32) * 3.0
+    x[:, ::53] *= 40.0
+    x[1] = 0.0
+    gain = rng.uniform(0.5, 1.5, size=n).astype(np.float32)
+    k, nn = n, 512
+    codes = rng.integers(-127, 128, size=(k, nn), dtype=np.int8)
+    scales = (rng.uniform(0.001, 0.02, size=nn) / 64.0).astype(np.float32)
+    o = ops()
+    nbytes = o.int8_gemm_scratch_bytes(rows, n, 0)
+    scr_a = torch.zeros((nbytes + 3) // 4, dtype=torch.float32, device=DEV)
+    scr_b = torch.zeros_like(scr_a)
+    plain = o.rmsnorm(dev(x), dev(gain), 1e-5, out_dtype=torch.bfloat16)
+    hn = o.rmsnorm(dev(x), dev(gain), 1e-5, planes=scr_a)
+    assert torch.equal(hn, plain)
+    before = N.lib().tlaloc_b200_launch_count()
+    y_a = o.int8_gemm(hn, dev(codes), dev(scales), scratch=scr_a, i8_mma=True, x_planes=True)
+    assert N.lib().tlaloc_b200_launch_count() - before == 1
+    y_b = o.int8_gemm(hn, dev(codes), dev(scales), scratch=scr_b, i8_mma=True)  # quantizer + projection
+    torch.cuda.synchronize()
+    used = (2 * rows * n + 4 * rows) // 4
+    assert torch.equal(scr_a[:used].view(torch.int32), scr_b[:used].view(torch.int32))
+    assert torch.equal(y_a, y_b)
+    want = oracle.proj_int8(hn.float().cpu().numpy(), codes, scales, threads=8)
+    close(y_a.cpu().numpy(), want)

@@ -12,7 +12,7 @@ from . import build as _build
 
 F32, BF16, S8, S32, F8E4M3FN = 11, 16, 2, 4, 20
 OK, INVALID_ARGUMENT, UNSUPPORTED, INTERNAL = 0, -1, -2, -3
-GEMM_EXACT, GEMM_X_F32_EXACT, GEMM_WEIGHTS_CONST, GEMM_I8_MMA = 1, 2, 4, 8
+GEMM_EXACT, GEMM_X_F32_EXACT, GEMM_WEIGHTS_CONST, GEMM_I8_MMA, GEMM_X_PLANES = 1, 2, 4, 8, 16
 
 _lib = None
 
@@ -41,6 +41,7 @@ _SIGNATURES = {
     "tlaloc_b200_dense_gemm_exact": (ctypes.c_int, [_vp, _i32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_embedding": (ctypes.c_int, [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_rmsnorm": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp]),
+    "tlaloc_b200_rmsnorm_planes": (ctypes.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp]),
     "tlaloc_b200_rope_kv_write": (ctypes.c_int, [_vp] * 8 + [_i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_swiglu": (ctypes.c_int, [_vp, _vp, _i32, _vp, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_argmax": (ctypes.c_int, [_vp, _vp, _i32, _i32, _vp]),
@@ -51,7 +52,7 @@ _SIGNATURES = {
     "tlaloc_b200_peer_allreduce_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _vp, _i32, _i32, _sz, _vp]),
     "tlaloc_b200_peer_allreduce_rmsnorm_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _sz, _vp, _vp, _f32, _i32, _i32,
                                                               _i32, _i32, _vp]),
-    "tlaloc_b200_peer_sum_rows_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _vp, _vp, _vp, _vp, _vp, _f32, _i32, _i32, _i32, _i32, _vp]),
+    "tlaloc_b200_peer_sum_rows_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _vp, _vp, _vp, _vp, _vp, _f32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "TlalocRegisterKernels": (ctypes.c_char_p, [_vp]),
     "tlaloc_b200_ffi_handler": (_vp, [ctypes.c_char_p]),
 }

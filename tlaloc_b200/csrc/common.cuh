@@ -157,8 +157,48 @@ bool Int8GemmI8Applies(const void* codes, int m, int k, int n);
 size_t Int8GemmI8ScratchBytes(int m, int k);
 cudaError_t LaunchInt8GemmI8(const void* x, int x_dtype, const int8_t* codes, const float* scales, const float* residual,
                              void* y, int y_dtype, void* scratch, int m, int k, int n, cudaStream_t st, int* launches,
-                             bool weights_const, bool swiglu);
+                             bool weights_const, bool swiglu, bool have_planes);
+// The quantizer alone: the planes of x [m, k] into `planes` (Int8GemmI8ScratchBytes(m, k) bytes).
+cudaError_t LaunchQuantizeRowsI8(const void* x, int x_dtype, void* planes, int m, int k, cudaStream_t st);
 int ReadI8Status();
+
+// The activation planes of the int8 tensor-core projection: row m of x as q = rint(x / s[m]) = 256 hi + lo with s[m] the
+// smallest power of two that keeps |q| <= 127 * 256.  Layout in the projection's scratch for an [m, k] activation:
+// hi int8 [m, k], lo int8 [m, k], s f32 [m].  Any kernel that produces a projection's input may write them itself
+// (RMSNorm, the one-barrier sum over ranks) and the projection is then called with TLALOC_B200_GEMM_X_PLANES.
+constexpr int kI8QMax = 127 * 256;
+// 1 / s for a row whose largest magnitude is amax (bad: the row holds an infinity or a NaN); *step = s, or NaN for a bad row.
+__device__ __forceinline__ float I8RowInvStep(float amax, bool bad, float* step)
+{
+  int e = 0;
+  if (amax > 0.f) {
+    int p;
+    frexpf(amax, &p);  // amax = f 2^p, f in [0.5, 1)
+    e = min(max(p - 15, -126), 126);
+    if (ldexpf(amax, -e) > static_cast<float>(kI8QMax)) ++e;
+  }
+  *step = bad ? __int_as_float(0x7fc00000) : ldexpf(1.f, e);
+  return bad ? 0.f : ldexpf(1.f, -e);
+}
+__device__ __forceinline__ void I8Split(float v, float inv, int& hi, int& lo)
+{
+  int q = __float2int_rn(v * inv);  // inv is 0 for a bad row: q = 0 (or the NaN conversion's 0)
+  q = min(max(q, -kI8QMax), kI8QMax);
+  hi = (q + 128) >> 8;
+  lo = q - (hi << 8);
+}
+// Four consecutive values as one word of each plane.
+__device__ __forceinline__ void I8Split4(float a, float b, float c, float d, float inv, uint32_t& hi_word, uint32_t& lo_word)
+{
+  int h0, l0, h1, l1, h2, l2, h3, l3;
+  I8Split(a, inv, h0, l0);
+  I8Split(b, inv, h1, l1);
+  I8Split(c, inv, h2, l2);
+  I8Split(d, inv, h3, l3);
+  hi_word = (h0 & 255u) | ((h1 & 255u) << 8) | ((h2 & 255u) << 16) | (static_cast<uint32_t>(h3) << 24);
+  lo_word = (l0 & 255u) | ((l1 & 255u) << 8) | ((l2 & 255u) << 16) | (static_cast<uint32_t>(l3) << 24);
+}
+__device__ __forceinline__ float Bf16Value(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 inline bool Aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 

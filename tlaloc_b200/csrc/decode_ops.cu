@@ -35,8 +35,25 @@ __device__ __forceinline__ float BlockSum(float v, float* red)
 // multiplies kept separate, as the interpreter evaluates the graph's nodes (DxirInterpreter.kt:567-572,1791-1807).
 // Rows of up to 8192 values (a multiple of 4) are read once with 16-byte loads, all in flight together, and kept
 // in registers for the second pass; other rows take the two-pass loop.
-template <typename OT>
-__global__ void __launch_bounds__(256) RmsNormKernel(const float* x, const float* gain, OT* out, int n, float eps)
+__device__ __forceinline__ float BlockMax(float v, float* red)
+{
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = red[0];
+  for (int w = 1; w < nw; ++w) r = fmaxf(r, red[w]);
+  return r;
+}
+
+// PLANES: the row is also written as the int8 tensor-core projection's activation planes (of the bf16-rounded result,
+// which is what the projection would quantize): hi and lo int8 [rows, n] and the row step; only on the register path
+// (the host launches the quantizer separately otherwise).
+template <typename OT, bool PLANES>
+__global__ void __launch_bounds__(256) RmsNormKernel(const float* x, const float* gain, OT* out, int n, float eps, int8_t* hi,
+                                                     int8_t* lo, float* steps)
 {
   GridDependencySync();
   __shared__ float red[8];
@@ -55,6 +72,8 @@ __global__ void __launch_bounds__(256) RmsNormKernel(const float* x, const float
     for (int i = 0; i < 8; ++i) ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, ss))));
     ss = BlockSum(ss, red);
     const float rsq = static_cast<float>(1.0 / sqrt(static_cast<double>(ss / static_cast<float>(n) + eps)));
+    float amax = 0.f;
+    bool bad = false;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int j = threadIdx.x + i * 256;
@@ -67,6 +86,31 @@ __global__ void __launch_bounds__(256) RmsNormKernel(const float* x, const float
         o[4 * j + 1] = FromF32<OT>(r1);
         o[4 * j + 2] = FromF32<OT>(r2);
         o[4 * j + 3] = FromF32<OT>(r3);
+        if constexpr (PLANES) {
+          v[i] = make_float4(Bf16Value(r0), Bf16Value(r1), Bf16Value(r2), Bf16Value(r3));
+          const float m4 = fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
+          bad = bad || !(m4 <= 3.4e38f);
+          amax = fmaxf(amax, m4);
+        }
+      }
+    }
+    if constexpr (PLANES) {
+      amax = BlockMax(amax, red);
+      const bool row_bad = __syncthreads_or(bad ? 1 : 0) != 0;
+      float step;
+      const float inv = I8RowInvStep(amax, row_bad, &step);
+      if (threadIdx.x == 0) steps[blockIdx.x] = step;
+      uint32_t* hrow = reinterpret_cast<uint32_t*>(hi + static_cast<size_t>(blockIdx.x) * n);
+      uint32_t* lrow = reinterpret_cast<uint32_t*>(lo + static_cast<size_t>(blockIdx.x) * n);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int j = threadIdx.x + i * 256;
+        if (j < n4) {
+          uint32_t hw, lw;
+          I8Split4(v[i].x, v[i].y, v[i].z, v[i].w, inv, hw, lw);
+          hrow[j] = hw;
+          lrow[j] = lw;
+        }
       }
     }
     return;
@@ -284,11 +328,41 @@ extern "C" int tlaloc_b200_rmsnorm(const float* x, const float* gain, void* out,
             ? LaunchChained(RmsNormOrderFaithfulKernel<float>, rows, 256, 0, st, x, gain, static_cast<float*>(out), n, eps)
             : LaunchChained(RmsNormOrderFaithfulKernel<__nv_bfloat16>, rows, 256, 0, st, x, gain, static_cast<__nv_bfloat16*>(out), n, eps);
   } else if (out_dtype == TLALOC_B200_F32) {
-    e = LaunchChained(RmsNormKernel<float>, rows, 256, 0, st, x, gain, static_cast<float*>(out), n, eps);
+    e = LaunchChained(RmsNormKernel<float, false>, rows, 256, 0, st, x, gain, static_cast<float*>(out), n, eps, nullptr, nullptr, nullptr);
   } else {
-    e = LaunchChained(RmsNormKernel<__nv_bfloat16>, rows, 256, 0, st, x, gain, static_cast<__nv_bfloat16*>(out), n, eps);
+    e = LaunchChained(RmsNormKernel<__nv_bfloat16, false>, rows, 256, 0, st, x, gain, static_cast<__nv_bfloat16*>(out), n, eps, nullptr,
+                      nullptr, nullptr);
   }
   if (e != cudaSuccess) return CudaFail("RMSNORM launch", e);
+  CountLaunches(1);
+  return kOk;
+}
+
+extern "C" int tlaloc_b200_rmsnorm_planes(const float* x, const float* gain, void* out, void* planes, int32_t rows, int32_t n,
+                                          float eps, void* stream)
+{
+  const char* op = "RMSNORM_PLANES";
+  if (!x || !out || !planes) return Fail(kInvalid, "%s: a required device pointer is null", op);
+  if (rows < 0 || n < 1) return Fail(kInvalid, "%s: bad sizes", op);
+  if (rows == 0) return kOk;
+  if (!Aligned16(planes) || n % 16 != 0) return Fail(kInvalid, "%s: the planes must be 16-byte aligned and n a multiple of 16", op);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // One launch when the row stays in registers; otherwise (long or unaligned rows, parity mode) the norm, then the
+  // projection's own quantizer on its bf16 result.
+  if (OrderFaithful() || n > 8192 || !Aligned16(x) || !Aligned16(gain)) {
+    const int status = tlaloc_b200_rmsnorm(x, gain, out, TLALOC_B200_BF16, rows, n, eps, stream);
+    if (status != kOk) return status;
+    const cudaError_t qe = LaunchQuantizeRowsI8(out, TLALOC_B200_BF16, planes, rows, n, st);
+    if (qe != cudaSuccess) return CudaFail("RMSNORM_PLANES quantizer launch", qe);
+    CountLaunches(1);
+    return kOk;
+  }
+  int8_t* hi = static_cast<int8_t*>(planes);
+  int8_t* lo = hi + static_cast<size_t>(rows) * n;
+  float* steps = reinterpret_cast<float*>(lo + static_cast<size_t>(rows) * n);
+  const cudaError_t e = LaunchChained(RmsNormKernel<__nv_bfloat16, true>, rows, 256, 0, st, x, gain, static_cast<__nv_bfloat16*>(out), n,
+                                      eps, hi, lo, steps);
+  if (e != cudaSuccess) return CudaFail("RMSNORM_PLANES launch", e);
   CountLaunches(1);
   return kOk;
 }

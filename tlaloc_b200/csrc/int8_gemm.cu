@@ -485,7 +485,7 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
   if (UseI8(codes, scratch, scratch_bytes, m, k, n, flags)) {
     int launches = 0;
     e = LaunchInt8GemmI8(x, x_dtype, codes, scales, residual, y, y_dtype, scratch, m, k, n, st, &launches,
-                         (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0, false);
+                         (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0, false, (flags & TLALOC_B200_GEMM_X_PLANES) != 0);
     if (e != cudaSuccess) return CudaFail("INT8_PROJ int8 tensor-core launch", e);
     CountLaunches(launches);
     return kOk;
@@ -598,7 +598,7 @@ extern "C" int tlaloc_b200_int8_gemm_swiglu(const void* x, int32_t x_dtype, cons
   if (UseI8(codes, scratch, scratch_bytes, m, k, n, flags)) {
     int launches = 0;
     e = LaunchInt8GemmI8(x, x_dtype, codes, scales, nullptr, y, y_dtype, scratch, m, k, n, st, &launches,
-                         (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0, true);
+                         (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0, true, (flags & TLALOC_B200_GEMM_X_PLANES) != 0);
     if (e != cudaSuccess) return CudaFail("INT8_PROJ_SWIGLU int8 tensor-core launch", e);
     CountLaunches(launches);
     return kOk;

@@ -47,7 +47,6 @@ constexpr int kI8ScaleOffset = kI8BarOffset + 128;
 constexpr int kI8SmemBytes = kI8ScaleOffset + kTcBN * 4 + 1024;  // slack to align to 1024
 constexpr int kI8Workers = 512;                   // the epilogue's threads
 constexpr int kI8Threads = kI8Workers + 64;       // plus the MMA warp and the producer warp
-constexpr int kI8QMax = 127 * 256;                // largest |256 hi + lo| that keeps hi within int8
 static_assert(kI8PipeBytes >= kI8TileBytes, "the tile aliases the ring");
 
 __device__ int g_i8_status = 0;  // nonzero after an mbarrier wait timed out (sticky until read)
@@ -116,24 +115,16 @@ __global__ void __launch_bounds__(256) QuantizeRowsI8Kernel(const XT* __restrict
     amax = fmaxf(amax, s_max[w]);
     row_bad |= s_bad[w];
   }
-  // s = 2^e, the smallest power of two with amax / s <= 127 * 256
-  int e = 0;
-  if (amax > 0.f) {
-    int p;
-    frexpf(amax, &p);  // amax = f 2^p, f in [0.5, 1)
-    e = min(max(p - 15, -126), 126);
-    if (ldexpf(amax, -e) > static_cast<float>(kI8QMax)) ++e;
-  }
-  const float inv = ldexpf(1.f, -e);
-  if (tid == 0) row_scale[m] = row_bad ? __int_as_float(0x7fc00000) : ldexpf(1.f, e);
+  float step;
+  const float inv = I8RowInvStep(amax, row_bad != 0, &step);
+  if (tid == 0) row_scale[m] = step;
   int8_t* hrow = hi + static_cast<size_t>(m) * K;
   int8_t* lrow = lo + static_cast<size_t>(m) * K;
   auto split = [&](float v, int8_t& h, int8_t& l) {
-    int q = row_bad ? 0 : __float2int_rn(v * inv);
-    q = min(max(q, -kI8QMax), kI8QMax);
-    const int hq = (q + 128) >> 8;
+    int hq, lq;
+    I8Split(v, inv, hq, lq);
     h = static_cast<int8_t>(hq);
-    l = static_cast<int8_t>(q - (hq << 8));
+    l = static_cast<int8_t>(lq);
   };
   if (vec) {
     for (int i = tid * kVec; i < K; i += 256 * kVec) {
@@ -475,19 +466,18 @@ bool Int8GemmI8Applies(const void* codes, int m, int k, int n)
 // Int8GemmI8ScratchBytes(m, k) bytes) receives the activation planes and the row steps.
 cudaError_t LaunchInt8GemmI8(const void* x, int x_dtype, const int8_t* codes, const float* scales, const float* residual,
                              void* y, int y_dtype, void* scratch, int m, int k, int n, cudaStream_t st, int* launches,
-                             bool weights_const, bool swiglu)
+                             bool weights_const, bool swiglu, bool have_planes)
 {
   cudaError_t e = PrepareI8();
   if (e != cudaSuccess) return e;
   int8_t* hi = static_cast<int8_t*>(scratch);
   int8_t* lo = hi + static_cast<size_t>(m) * k;
   float* row_scale = reinterpret_cast<float*>(lo + static_cast<size_t>(m) * k);
-  e = x_dtype == TLALOC_B200_F32
-          ? LaunchChained(QuantizeRowsI8Kernel<float>, static_cast<unsigned>(m), 256, 0, st, static_cast<const float*>(x), hi, lo, row_scale, k)
-          : LaunchChained(QuantizeRowsI8Kernel<__nv_bfloat16>, static_cast<unsigned>(m), 256, 0, st,
-                          static_cast<const __nv_bfloat16*>(x), hi, lo, row_scale, k);
-  if (e != cudaSuccess) return e;
-  ++*launches;
+  if (!have_planes) {
+    e = LaunchQuantizeRowsI8(x, x_dtype, scratch, m, k, st);
+    if (e != cudaSuccess) return e;
+    ++*launches;
+  }
   CUtensorMap mw, mh, ml;
   if (!ByteMatrixMap(&mw, codes, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(n)) ||
       !ByteMatrixMap(&mh, hi, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k)) ||
@@ -511,6 +501,17 @@ cudaError_t LaunchInt8GemmI8(const void* x, int x_dtype, const int8_t* codes, co
   if (e != cudaSuccess) return e;
   ++*launches;
   return cudaSuccess;
+}
+
+cudaError_t LaunchQuantizeRowsI8(const void* x, int x_dtype, void* planes, int m, int k, cudaStream_t st)
+{
+  int8_t* hi = static_cast<int8_t*>(planes);
+  int8_t* lo = hi + static_cast<size_t>(m) * k;
+  float* row_scale = reinterpret_cast<float*>(lo + static_cast<size_t>(m) * k);
+  return x_dtype == TLALOC_B200_F32
+             ? LaunchChained(QuantizeRowsI8Kernel<float>, static_cast<unsigned>(m), 256, 0, st, static_cast<const float*>(x), hi, lo, row_scale, k)
+             : LaunchChained(QuantizeRowsI8Kernel<__nv_bfloat16>, static_cast<unsigned>(m), 256, 0, st,
+                             static_cast<const __nv_bfloat16*>(x), hi, lo, row_scale, k);
 }
 
 int ReadI8Status()

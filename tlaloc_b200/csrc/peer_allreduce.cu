@@ -164,6 +164,20 @@ struct PeerNormTable
 constexpr int kNormParts = 4;  // CTAs that share a row: a cluster, so the row's sum of squares meets in shared memory
 constexpr int kNormVec = 4;    // float4 per thread per row: cols <= 4 * kNormParts * kNormVec * 512
 
+__device__ __forceinline__ float BlockMax512(float v, float* red)
+{
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // red may still be read by the sum before
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < kThreads / 32 ? red[lane] : 0.f;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+  return __shfl_sync(0xffffffffu, t, 0);
+}
+
 __device__ __forceinline__ float BlockSum512(float v, float* red)
 {
 #pragma unroll
@@ -305,7 +319,7 @@ struct PeerSumTable
 template <int W>
 __global__ void __launch_bounds__(kThreads, 1)
 PeerSumRowsKernel(PeerSumTable t, uint32_t* state, const float* residual, float* out, __nv_bfloat16* norm_out, const float* gain,
-                  float eps, int rank, int world_rt, int rows, int cols)
+                  float eps, int rank, int world_rt, int rows, int cols, int8_t* plane_hi, int8_t* plane_lo, float* plane_steps)
 {
   GridDependencySync();
   const int world = W > 0 ? W : world_rt;
@@ -354,6 +368,8 @@ PeerSumRowsKernel(PeerSumTable t, uint32_t* state, const float* residual, float*
       }
     }
     if (norm_out != nullptr) {
+      float amax = 0.f;
+      bool bad = false;
       const float total = BlockSum512(ss, red);
       const float rsq = static_cast<float>(1.0 / sqrt(static_cast<double>(total / static_cast<float>(cols) + eps)));
 #pragma unroll
@@ -369,6 +385,30 @@ PeerSumRowsKernel(PeerSumTable t, uint32_t* state, const float* residual, float*
           packed.x = *reinterpret_cast<const uint32_t*>(&lo);
           packed.y = *reinterpret_cast<const uint32_t*>(&hi);
           *reinterpret_cast<uint2*>(norm_out + base + 4 * c) = packed;
+          if (plane_hi != nullptr) {  // the bf16 values, for the planes below (the f32 sums are already stored)
+            sum[i] = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+            const float m4 = fmaxf(fmaxf(fabsf(sum[i].x), fabsf(sum[i].y)), fmaxf(fabsf(sum[i].z), fabsf(sum[i].w)));
+            bad = bad || !(m4 <= 3.4e38f);
+            amax = fmaxf(amax, m4);
+          }
+        }
+      }
+      if (plane_hi != nullptr) {
+        // the normalised row also as the int8 tensor-core projection's activation planes
+        amax = BlockMax512(amax, red);
+        const bool row_bad = __syncthreads_or(bad ? 1 : 0) != 0;
+        float step;
+        const float inv = I8RowInvStep(amax, row_bad, &step);
+        if (tid == 0) plane_steps[row] = step;
+#pragma unroll
+        for (int i = 0; i < kNormVec; ++i) {
+          const int c = tid + i * kThreads;
+          if (c < row4) {
+            uint32_t hw, lw;
+            I8Split4(sum[i].x, sum[i].y, sum[i].z, sum[i].w, inv, hw, lw);
+            reinterpret_cast<uint32_t*>(plane_hi + base)[c] = hw;
+            reinterpret_cast<uint32_t*>(plane_lo + base)[c] = lw;
+          }
         }
       }
     }
@@ -462,7 +502,7 @@ int LaunchPeerAllReduceNorm(void* const* bases, size_t data_offset, size_t norm_
 
 int LaunchPeerSumRows(void* const* bases, size_t partial_offset, size_t flag_offset, uint32_t* state, const float* residual,
                       float* out, void* norm_out, const float* gain, float eps, int rank, int world, int rows, int cols,
-                      cudaStream_t st)
+                      void* planes, cudaStream_t st)
 {
   const char* op = "peer_sum_rows";
   if (world < 1 || world > kMaxRanks) return Fail(kInvalid, "%s: world %d outside [1, %d]", op, world, kMaxRanks);
@@ -480,14 +520,20 @@ int LaunchPeerSumRows(void* const* bases, size_t partial_offset, size_t flag_off
     t.partial[q] = reinterpret_cast<const float*>(static_cast<const char*>(bases[q]) + partial_offset);
     t.flags[q] = reinterpret_cast<uint32_t*>(static_cast<char*>(bases[q]) + flag_offset);
   }
+  if (planes != nullptr && (norm_out == nullptr || !Aligned16(planes) || cols % 16 != 0)) {
+    return Fail(kInvalid, "%s: planes need norm_out, 16-byte alignment and cols a multiple of 16", op);
+  }
   const int grid = rows < 148 ? rows : 148;
   __nv_bfloat16* nout = static_cast<__nv_bfloat16*>(norm_out);
+  int8_t* phi = static_cast<int8_t*>(planes);
+  int8_t* plo = phi != nullptr ? phi + static_cast<size_t>(rows) * cols : nullptr;
+  float* pst = phi != nullptr ? reinterpret_cast<float*>(plo + static_cast<size_t>(rows) * cols) : nullptr;
   cudaError_t e;
   switch (world) {
-    case 2: e = LaunchChained(PeerSumRowsKernel<2>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols); break;
-    case 4: e = LaunchChained(PeerSumRowsKernel<4>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols); break;
-    case 8: e = LaunchChained(PeerSumRowsKernel<8>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols); break;
-    default: e = LaunchChained(PeerSumRowsKernel<0>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols); break;
+    case 2: e = LaunchChained(PeerSumRowsKernel<2>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols, phi, plo, pst); break;
+    case 4: e = LaunchChained(PeerSumRowsKernel<4>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols, phi, plo, pst); break;
+    case 8: e = LaunchChained(PeerSumRowsKernel<8>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols, phi, plo, pst); break;
+    default: e = LaunchChained(PeerSumRowsKernel<0>, grid, kThreads, 0, st, t, state, residual, out, nout, gain, eps, rank, world, rows, cols, phi, plo, pst); break;
   }
   if (e != cudaSuccess) return CudaFail("peer_sum_rows launch", e);
   CountLaunches(1);
@@ -556,8 +602,8 @@ extern "C" int tlaloc_b200_peer_allreduce_rmsnorm_f32(void* const* bases, size_t
 
 extern "C" int tlaloc_b200_peer_sum_rows_f32(void* const* bases, size_t partial_offset, size_t flag_offset, uint32_t* state,
                                              const float* residual, float* out, void* norm_out, const float* gain, float eps,
-                                             int32_t rank, int32_t world, int32_t rows, int32_t cols, void* stream)
+                                             int32_t rank, int32_t world, int32_t rows, int32_t cols, void* planes, void* stream)
 {
   return LaunchPeerSumRows(bases, partial_offset, flag_offset, state, residual, out, norm_out, gain, eps, rank, world, rows, cols,
-                           static_cast<cudaStream_t>(stream));
+                           planes, static_cast<cudaStream_t>(stream));
 }

@@ -138,6 +138,9 @@ class Decoder:
         self.i8_mma = 17 <= B <= 128 and not self.exact
         kmax = max(d, self.hq * hd, self.f)
         self.proj_scratch = torch.empty((ops.int8_gemm_scratch_bytes(B, kmax, 0) + 3) // 4, **f32) if self.i8_mma else None
+        # The kernels that produce the normalised rows (RMSNorm, the one-barrier sum over ranks) write those planes
+        # themselves, so q|k|v and gate|up need no quantizer launch of their own ($TLALOC_B200_NORM_PLANES=0: they do).
+        self.norm_planes = self.i8_mma and d % 16 == 0 and d <= 8192 and os.environ.get("TLALOC_B200_NORM_PLANES", "1") != "0"
         self.logits = torch.empty((B, cfg.vocab // world), **f32)
         self.next_ids = torch.zeros((B,), **i32)
         self.best = torch.empty((B,), **f32)
@@ -236,22 +239,28 @@ class Decoder:
         res_rank = self.rank == 0  # under tensor parallelism the residual enters the all-reduced sum once
         q3, k3, v3 = self._qkv_views()
         fused = self.fuse_norm  # the sum over ranks also produces the next RMSNorm's output
+        pl = self.proj_scratch if self.norm_planes else None  # RMSNorm leaves hn's int8 planes there for the projection
+        how = dict(weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
         for l, lw in enumerate(self.layers):
+            xp = False  # hn's planes are in the scratch (only when this rank's own RMSNorm kernel produced hn)
             if l == 0 or not fused:
-                ops.rmsnorm(h, lw["ln1"], cfg.rms_eps, out=self.hn)
-            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
+                ops.rmsnorm(h, lw["ln1"], cfg.rms_eps, out=self.hn, planes=pl)
+                xp = pl is not None
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, x_planes=xp, **how)
             ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
                               self.value_pools[l], q_out=self.q_rot)
             ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
                                 scale=cfg.scale, out=self.att, scratch=self.att_scratch)
-            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], residual=h if res_rank else None, out=h2, **how)
             if fused:
                 self.peer.all_reduce_norm_(1, lw["ln2"], cfg.rms_eps)
+                xp = False
             else:
                 self._all_reduce(h2)
-                ops.rmsnorm(h2, lw["ln2"], cfg.rms_eps, out=self.hn)
-            self.gate_up_proj(lw)
-            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
+                ops.rmsnorm(h2, lw["ln2"], cfg.rms_eps, out=self.hn, planes=pl)
+                xp = pl is not None
+            self.gate_up_proj(lw, x_planes=xp)
+            ops.int8_gemm(self.act, *lw["down"], residual=h2 if res_rank else None, out=h, **how)
             if fused:
                 nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
                 self.peer.all_reduce_norm_(0, nxt, cfg.rms_eps)
@@ -270,19 +279,22 @@ class Decoder:
         ops.embedding(self.embed, self.token_ids, out=self.h)
         h, (p_o, p_down) = self.h, self.peer.tensors
         q3, k3, v3 = self._qkv_views()
-        ops.rmsnorm(h, self.layers[0]["ln1"], cfg.rms_eps, out=self.hn)
+        pl = self.proj_scratch if self.norm_planes else None  # the kernels that write hn also leave its int8 planes there
+        xp = pl is not None
+        how = dict(weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
+        ops.rmsnorm(h, self.layers[0]["ln1"], cfg.rms_eps, out=self.hn, planes=pl)
         for l, lw in enumerate(self.layers):
-            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, x_planes=xp, **how)
             ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
                               self.value_pools[l], q_out=self.q_rot)
             ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
                                 scale=cfg.scale, out=self.att, scratch=self.att_scratch)
-            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], out=p_o, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
-            self.peer.sum_rows_(0, h, h, lw["ln2"], cfg.rms_eps, norm_out=self.hn)
-            self.gate_up_proj(lw)
-            ops.int8_gemm(self.act, *lw["down"], out=p_down, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], out=p_o, **how)
+            self.peer.sum_rows_(0, h, h, lw["ln2"], cfg.rms_eps, norm_out=self.hn, planes=pl)
+            self.gate_up_proj(lw, x_planes=xp)
+            ops.int8_gemm(self.act, *lw["down"], out=p_down, **how)
             nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
-            self.peer.sum_rows_(1, h, h, nxt, cfg.rms_eps, norm_out=self.hn)
+            self.peer.sum_rows_(1, h, h, nxt, cfg.rms_eps, norm_out=self.hn, planes=pl)
         self._head_and_greedy()
 
     def _qkv_views(self):
@@ -299,13 +311,15 @@ class Decoder:
         if self.world > 1:
             self._merge_greedy()
 
-    def gate_up_proj(self, lw) -> None:
+    def gate_up_proj(self, lw, x_planes: bool = False) -> None:
         """The MLP's first half for one layer: normalised rows `hn` -> `act` = silu(gate) * up, as one projection with
         SwiGLU in its epilogue where the shape allows, else the fused gate|up projection and the SwiGLU kernel."""
         if self.fuse_swiglu:
-            ops.int8_gemm_swiglu(self.hn, *lw["gate_up"], out=self.act, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
+            ops.int8_gemm_swiglu(self.hn, *lw["gate_up"], out=self.act, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma,
+                                 x_planes=x_planes)
         else:
-            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
+            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma,
+                          x_planes=x_planes)
             ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
 
     def _merge_greedy(self) -> None:

@@ -107,11 +107,12 @@ def kv_cache_write(pool, new_kv, slot_mapping):
 
 
 def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.float32, exact=False, x_f32_exact=False,
-              scratch=None, weights_const=False, i8_mma=False):
+              scratch=None, weights_const=False, i8_mma=False, x_planes=False):
     """y = (cast(x) @ cast(codes)) * scales (+ residual): x [M, K], codes int8 [K, N] (in, out), scales f32 [N].
     `weights_const`: no kernel queued just before this call writes codes or scales (true of a loaded model).
     `i8_mma`: 17 to 128 rows take the int8 tensor-core kernel (codes straight to the tensor core, activations as 16-bit
-    fixed point per row, exact int32 sums) instead of the bf16 one (f32 accumulation of exact products)."""
+    fixed point per row, exact int32 sums) instead of the bf16 one (f32 accumulation of exact products).
+    `x_planes`: `scratch` already holds x's activation planes (rmsnorm(..., planes=scratch) wrote them)."""
     _dev(x, codes, scales, residual)
     M, K = x.shape
     K2, Nn = codes.shape
@@ -127,7 +128,8 @@ def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.floa
                               device=x.device)
     _out("INT8_PROJ scratch", scratch, None, torch.float32, x)
     flags = ((N.GEMM_EXACT if exact else 0) | (N.GEMM_X_F32_EXACT if x_f32_exact else 0)
-             | (N.GEMM_WEIGHTS_CONST if weights_const else 0) | (N.GEMM_I8_MMA if i8_mma else 0))
+             | (N.GEMM_WEIGHTS_CONST if weights_const else 0) | (N.GEMM_I8_MMA if i8_mma else 0)
+             | (N.GEMM_X_PLANES if x_planes else 0))
     N.check(N.lib().tlaloc_b200_int8_gemm(_ptr(x), _dt(x), _ptr(codes), _ptr(scales), _ptr(residual), _ptr(out), _dt(out),
                                           _ptr(scratch), 0 if scratch is None else scratch.numel() * 4, M, K, Nn, flags,
                                           _stream(x)))
@@ -135,7 +137,7 @@ def int8_gemm(x, codes, scales, *, residual=None, out=None, out_dtype=torch.floa
 
 
 def int8_gemm_swiglu(x, codes, scales, *, out=None, out_dtype=torch.bfloat16, exact=False, scratch=None, weights_const=False,
-                     i8_mma=False):
+                     i8_mma=False, x_planes=False):
     """silu(x @ gate) * (x @ up) with gate and up interleaved in `codes` [K, 2F] in column blocks of 128 + 128
     (sharding.interleave_gate_up); returns [M, F]."""
     _dev(x, codes, scales)
@@ -150,7 +152,8 @@ def int8_gemm_swiglu(x, codes, scales, *, out=None, out_dtype=torch.bfloat16, ex
     if scratch is None and not exact and (x.dtype == torch.float32 or (i8_mma and 17 <= M <= 128)):
         scratch = torch.empty((N.lib().tlaloc_b200_int8_gemm_scratch_bytes(M, K, Nn) + 3) // 4, dtype=torch.float32, device=x.device)
     _out("INT8_PROJ_SWIGLU scratch", scratch, None, torch.float32, x)
-    flags = (N.GEMM_EXACT if exact else 0) | (N.GEMM_WEIGHTS_CONST if weights_const else 0) | (N.GEMM_I8_MMA if i8_mma else 0)
+    flags = ((N.GEMM_EXACT if exact else 0) | (N.GEMM_WEIGHTS_CONST if weights_const else 0) | (N.GEMM_I8_MMA if i8_mma else 0)
+             | (N.GEMM_X_PLANES if x_planes else 0))
     N.check(N.lib().tlaloc_b200_int8_gemm_swiglu(_ptr(x), _dt(x), _ptr(codes), _ptr(scales), _ptr(out), _dt(out), _ptr(scratch),
                                                  0 if scratch is None else scratch.numel() * 4, M, K, Nn, flags, _stream(x)))
     return out
@@ -181,12 +184,21 @@ def embedding(table, ids, *, out=None):
     return out
 
 
-def rmsnorm(x, gain, eps, *, out=None, out_dtype=torch.float32):
+def rmsnorm(x, gain, eps, *, out=None, out_dtype=torch.float32, planes=None):
+    """x * rsqrt(mean(x^2) + eps) * gain.  `planes` (an f32 scratch of int8_gemm_scratch_bytes(rows, n, 0) bytes; out must
+    be bf16, n a multiple of 16) also receives the normalised rows as the activation planes of the int8 tensor-core
+    projection that reads `out`: call that projection with the same scratch and x_planes=True."""
     _dev(x, gain)
     rows, n = x.shape
     if out is None:
-        out = torch.empty((rows, n), dtype=out_dtype, device=x.device)
+        out = torch.empty((rows, n), dtype=torch.bfloat16 if planes is not None else out_dtype, device=x.device)
     _out("RMSNORM out", out, (rows, n), (torch.float32, torch.bfloat16), x)
+    if planes is not None:
+        _out("RMSNORM planes", planes, None, torch.float32, x)
+        if out.dtype != torch.bfloat16 or planes.numel() * 4 < int8_gemm_scratch_bytes(rows, n, 0):
+            raise ValueError("RMSNORM: planes need a bf16 out and int8_gemm_scratch_bytes(rows, n, 0) bytes")
+        N.check(N.lib().tlaloc_b200_rmsnorm_planes(_ptr(x), _ptr(gain), _ptr(out), _ptr(planes), rows, n, float(eps), _stream(x)))
+        return out
     N.check(N.lib().tlaloc_b200_rmsnorm(_ptr(x), _ptr(gain), _ptr(out), _dt(out), rows, n, float(eps), _stream(x)))
     return out
 

@@ -105,9 +105,11 @@ class PeerBuffers:
             torch.cuda.current_stream(self.device).cuda_stream))
         return t, self.norm_out
 
-    def sum_rows_(self, index: int, residual, out, gain, eps: float, norm_out=None):
+    def sum_rows_(self, index: int, residual, out, gain, eps: float, norm_out=None, planes=None):
         """The one-barrier form: out = residual + sum over ranks of tensor `index` (every rank's partial, added in rank
-        order) into LOCAL `out` (f32, may be `residual` itself), and RMSNorm(out) * gain as bf16 into local `norm_out`.
+        order) into LOCAL `out` (f32, may be `residual` itself), and RMSNorm(out) * gain as bf16 into local `norm_out`;
+        `planes` (the scratch of the int8 tensor-core projection that reads norm_out) also receives the normalised rows
+        as that projection's activation planes.
         The caller must not overwrite tensor `index` again before one more sum_rows_ (on another tensor) has run."""
         t = self.tensors[index]
         if t.dim() != 2 or tuple(out.shape) != tuple(t.shape) or out.dtype != torch.float32 or not out.is_contiguous():
@@ -118,7 +120,7 @@ class PeerBuffers:
             self._bases, self.offsets[index], self.flag_offset, self.state.data_ptr(),
             None if residual is None else residual.data_ptr(), out.data_ptr(), None if norm_out is None else norm_out.data_ptr(),
             None if gain is None else gain.data_ptr(), float(eps), self.rank, self.world, t.shape[0], t.shape[1],
-            torch.cuda.current_stream(self.device).cuda_stream))
+            None if planes is None else planes.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream))
         return out
 
     def can_sum_rows(self, index: int) -> bool:

@@ -388,7 +388,6 @@ def test_rmsnorm_writes_the_planes_the_projections_quantizer_would(rows, n):
 
     rng = np.random.default_rng(rows + n)
     x = rng.standard_normal((rows, n)).astype(np.float32) * 3.0
-    x[:, ::53] *= 40.0
     x[1] = 0.0
     gain = rng.uniform(0.5, 1.5, size=n).astype(np.float32)
     k, nn = n, 512

@@ -250,10 +250,11 @@ class StepBench:
         dec = self.dec
         if not dec.i8_mma:
             return {"note": "this batch size does not use the int8 form"}
-        dec.i8_mma = False
+        planes = dec.norm_planes
+        dec.i8_mma, dec.norm_planes = False, False
         dec.capture()
         value, ms_step, _ = self.time_value(local_gpu)
-        dec.i8_mma = True
+        dec.i8_mma, dec.norm_planes = True, planes
         dec.capture()
         return {"value": value, "unit": UNIT, "ms_per_step": ms_step}
 

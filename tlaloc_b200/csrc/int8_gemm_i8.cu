@@ -15,8 +15,9 @@
 // rounding of the inputs.  A row holding an infinity or a NaN gets s = NaN, so its whole output row is NaN.
 //
 // Formulation: D[m, n] = sum_k X[m, k] W[k, n], activation rows = the MMA's M (TMEM lanes), 256 weight columns = its N.
-// A CTA owns 256 columns and one slice of K, walked in blocks of 128 rows through a three-stage ring:
-//   producer thread  one lane; per block four TMA loads (hi strip, lo strip: K-major 128-byte-swizzled [128 rows][128 k];
+// A CTA owns 256 columns and one slice of K, walked in blocks of 128 rows through a ring of three stages (65 to 128
+// activation rows; four stages for up to 64 rows, five for up to 32, whose strips are smaller):
+//   producer thread  one lane; per block four TMA loads (hi strip, lo strip: K-major 128-byte-swizzled [rows][128 k];
 //                    the block's codes as two MN-major 128-byte-swizzled boxes [128 k][128 n]: W's rows are contiguous
 //                    along N, which is MN-major, so nothing is transposed) onto the stage's mbarrier;
 //   MMA thread       one lane; per block 4 K-steps x {hi, lo} of 128 x 256 x 32, then a commit that hands the stage back;
@@ -35,19 +36,29 @@ namespace {
 
 using namespace tc;
 
-constexpr int kI8BK = 128;                        // k rows per block
-constexpr int kI8Stages = 3;
-constexpr int kI8StripBytes = 128 * kI8BK;        // one plane of the activation strip: 128 rows x 128 k
-constexpr int kI8AtomBytes = kI8BK * 128;         // 128 k rows x 128 columns of codes
-constexpr int kI8StageBytes = 2 * kI8StripBytes + 2 * kI8AtomBytes;
-constexpr int kI8PipeBytes = kI8Stages * kI8StageBytes;
-constexpr int kI8TileBytes = 128 * kTcTileStride * 4;  // the epilogue's f32 tile; aliases the ring
-constexpr int kI8BarOffset = kI8PipeBytes > kI8TileBytes ? kI8PipeBytes : (kI8TileBytes + 15) / 16 * 16;
-constexpr int kI8ScaleOffset = kI8BarOffset + 128;
-constexpr int kI8SmemBytes = kI8ScaleOffset + kTcBN * 4 + 1024;  // slack to align to 1024
-constexpr int kI8Workers = 512;                   // the epilogue's threads
-constexpr int kI8Threads = kI8Workers + 64;       // plus the MMA warp and the producer warp
-static_assert(kI8PipeBytes >= kI8TileBytes, "the tile aliases the ring");
+constexpr int kI8BK = 128;                 // k rows per block
+constexpr int kI8AtomBytes = kI8BK * 128;  // 128 k rows x 128 columns of codes
+constexpr int kI8Workers = 512;            // the epilogue's threads
+constexpr int kI8Threads = kI8Workers + 64;  // plus the MMA warp and the producer warp
+
+// Shared memory for launches of up to MROWS activation rows (32, 64 or 128): the ring of stages, each [hi strip][lo
+// strip][two atoms of codes], then the mbarriers, the TMEM base, the abort word and the tile's scales.  The strips hold
+// MROWS rows; the MMA always reads 128 (the rows past MROWS are whatever follows in the stage, and only reach
+// accumulator lanes that are never read), so fewer rows leave room for more stages: 3 of 64 KB, 4 of 48 KB, 5 of 40 KB.
+template <int MROWS>
+struct I8Layout {
+  static constexpr int kStripBytes = MROWS * kI8BK;
+  static constexpr int kStageBytes = 2 * kStripBytes + 2 * kI8AtomBytes;
+  static constexpr int kStages = MROWS > 64 ? 3 : MROWS > 32 ? 4 : 5;
+  static constexpr int kPipeBytes = kStages * kStageBytes;
+  static constexpr int kTileBytes = MROWS * kTcTileStride * 4;  // the epilogue's f32 tile; aliases the ring
+  static constexpr int kBarOffset = kPipeBytes;
+  static constexpr int kScaleOffset = kBarOffset + 128;
+  static constexpr int kSmemBytes = kScaleOffset + kTcBN * 4 + 1024;  // slack to align to 1024
+  static_assert(kPipeBytes >= kTileBytes, "the tile aliases the ring");
+  static_assert(kStripBytes % 1024 == 0 && kStageBytes % 1024 == 0, "operand tiles start on 1024-byte boundaries");
+  static_assert(16 * kStages <= 96, "the barriers sit below the TMEM slot");
+};
 
 __device__ int g_i8_status = 0;  // nonzero after an mbarrier wait timed out (sticky until read)
 
@@ -175,11 +186,14 @@ __device__ __forceinline__ void TmaLoad2d(uint32_t dst, const CUtensorMap* map, 
       : "memory");
 }
 
-template <typename YT>
+template <int MROWS, typename YT>
 __global__ void __launch_bounds__(kI8Threads, 1)
     Int8GemmI8Kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_hi,
                      const __grid_constant__ CUtensorMap map_lo, I8Params p)
 {
+  using L = I8Layout<MROWS>;
+  constexpr int kI8Stages = L::kStages, kI8StripBytes = L::kStripBytes, kI8StageBytes = L::kStageBytes;
+  constexpr int kI8BarOffset = L::kBarOffset, kI8ScaleOffset = L::kScaleOffset;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (SmemAddr(smem_raw) + 1023u) & ~1023u;  // the swizzle is a function of address bits 4..9
   unsigned char* smem = smem_raw + (smem_base - SmemAddr(smem_raw));
@@ -190,8 +204,8 @@ __global__ void __launch_bounds__(kI8Threads, 1)
   const int nblocks = ke > kb0 ? (ke - kb0 + kI8BK - 1) / kI8BK : 0;
   // full[i]: the four boxes of the block in stage i have landed; empty[i]: its MMAs have completed.
   const uint32_t full0 = smem_base + kI8BarOffset, empty0 = full0 + 8 * kI8Stages;
-  const uint32_t tmem_slot_addr = smem_base + kI8BarOffset + 64;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kI8BarOffset + 64);
+  const uint32_t tmem_slot_addr = smem_base + kI8BarOffset + 96;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kI8BarOffset + 96);
   volatile uint32_t* abort_word = tmem_slot + 1;  // raised by the first wait that gives up
   float* s_scales = reinterpret_cast<float*>(smem + kI8ScaleOffset);
 
@@ -292,7 +306,7 @@ __global__ void __launch_bounds__(kI8Threads, 1)
   float* tile = reinterpret_cast<float*>(smem);
   const EpilogueOut out{p.residual, p.y, p.M, p.N, p.swiglu};
   const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0;
-  if (worker) {
+  if (worker && (warp & 3) * 32 < MROWS) {
     const int lg = warp & 3, wq = warp >> 2;
     const int m = lg * 32 + lane;
     const float rs = m < p.M ? __ldg(p.row_scale + m) : 0.f;
@@ -323,7 +337,7 @@ __global__ void __launch_bounds__(kI8Threads, 1)
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   if (nranks == 1) {
     __syncthreads();
-    if (worker) EpilogueRows<128, YT>(tile, s_scales, out, col0, 0, tid, vec_ok);
+    if (worker) EpilogueRows<MROWS, YT>(tile, s_scales, out, col0, 0, tid, vec_ok);
     __syncthreads();
   } else {
     cluster.sync();
@@ -354,22 +368,22 @@ EncodeTiledFn EncodeTiled()
   return fn;
 }
 
-// A [rows][inner] byte matrix with rows `pitch` bytes apart, read in boxes of 128 bytes x 128 rows, 128-byte swizzle,
-// zeros outside.
-bool ByteMatrixMap(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch)
+// A [rows][inner] byte matrix with rows `pitch` bytes apart, read in boxes of 128 bytes x box_rows rows, 128-byte
+// swizzle, zeros outside.
+bool ByteMatrixMap(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch, uint32_t box_rows)
 {
   EncodeTiledFn encode = EncodeTiled();
   if (encode == nullptr) return false;
   const cuuint64_t dims[2] = {inner, rows};
   const cuuint64_t strides[1] = {pitch};
-  const cuuint32_t box[2] = {128, 128};
+  const cuuint32_t box[2] = {128, box_rows};
   const cuuint32_t elem[2] = {1, 1};
   return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int g_i8_slots[kMaxDevices][9];  // resident CTAs when launched as clusters of ks
+int g_i8_slots[kMaxDevices][9];  // resident CTAs when launched as clusters of ks (one CTA per SM whatever the row class)
 
 void FillI8Slots(int device)
 {
@@ -377,7 +391,7 @@ void FillI8Slots(int device)
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(148, ks, 1);
     cfg.blockDim = dim3(kI8Threads, 1, 1);
-    cfg.dynamicSmemBytes = kI8SmemBytes;
+    cfg.dynamicSmemBytes = I8Layout<128>::kSmemBytes;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
@@ -386,7 +400,7 @@ void FillI8Slots(int device)
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, Int8GemmI8Kernel<float>, &cfg) != cudaSuccess || clusters <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, Int8GemmI8Kernel<128, float>, &cfg) != cudaSuccess || clusters <= 0) {
       cudaGetLastError();
       clusters = (ks <= 2 ? 148 : ks <= 4 ? 128 : 112) / ks;  // a cautious guess when the query is not available
     }
@@ -398,8 +412,17 @@ cudaError_t PrepareI8()
 {
   static OncePerDevice once;
   return once.Run([](int device) {
-    cudaError_t e = cudaFuncSetAttribute(Int8GemmI8Kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kI8SmemBytes);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(Int8GemmI8Kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kI8SmemBytes);
+    cudaError_t e = cudaSuccess;
+#define TLALOC_I8_OPT_IN(MROWS, YT)                                                                                     \
+  if (e == cudaSuccess)                                                                                                 \
+    e = cudaFuncSetAttribute(Int8GemmI8Kernel<MROWS, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize, I8Layout<MROWS>::kSmemBytes)
+    TLALOC_I8_OPT_IN(32, float);
+    TLALOC_I8_OPT_IN(32, __nv_bfloat16);
+    TLALOC_I8_OPT_IN(64, float);
+    TLALOC_I8_OPT_IN(64, __nv_bfloat16);
+    TLALOC_I8_OPT_IN(128, float);
+    TLALOC_I8_OPT_IN(128, __nv_bfloat16);
+#undef TLALOC_I8_OPT_IN
     if (e == cudaSuccess) FillI8Slots(device);
     return e;
   });
@@ -435,18 +458,26 @@ int ChooseI8Slices(int k, int n)
   return best;
 }
 
-template <typename YT>
+template <int MROWS, typename YT>
 cudaError_t LaunchI8(const CUtensorMap& mw, const CUtensorMap& mh, const CUtensorMap& ml, const I8Params& p, cudaStream_t stream)
 {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + kTcBN - 1) / kTcBN, p.ks, 1);
   cfg.blockDim = dim3(kI8Threads, 1, 1);
-  cfg.dynamicSmemBytes = kI8SmemBytes;
+  cfg.dynamicSmemBytes = I8Layout<MROWS>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   cfg.numAttrs = ChainAttributes(attr, p.ks);
   cfg.attrs = attr;
-  return cudaLaunchKernelEx(&cfg, Int8GemmI8Kernel<YT>, mw, mh, ml, p);
+  return cudaLaunchKernelEx(&cfg, Int8GemmI8Kernel<MROWS, YT>, mw, mh, ml, p);
+}
+
+template <typename YT>
+cudaError_t LaunchI8Rows(const CUtensorMap& mw, const CUtensorMap& mh, const CUtensorMap& ml, const I8Params& p, cudaStream_t stream)
+{
+  if (p.M <= 32) return LaunchI8<32, YT>(mw, mh, ml, p, stream);
+  if (p.M <= 64) return LaunchI8<64, YT>(mw, mh, ml, p, stream);
+  return LaunchI8<128, YT>(mw, mh, ml, p, stream);
 }
 
 }  // namespace
@@ -479,9 +510,10 @@ cudaError_t LaunchInt8GemmI8(const void* x, int x_dtype, const int8_t* codes, co
     ++*launches;
   }
   CUtensorMap mw, mh, ml;
-  if (!ByteMatrixMap(&mw, codes, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(n)) ||
-      !ByteMatrixMap(&mh, hi, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k)) ||
-      !ByteMatrixMap(&ml, lo, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k))) {
+  const uint32_t strip_rows = m <= 32 ? 32 : m <= 64 ? 64 : 128;  // the row class of the launch: I8Layout<MROWS>
+  if (!ByteMatrixMap(&mw, codes, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(n), 128) ||
+      !ByteMatrixMap(&mh, hi, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k), strip_rows) ||
+      !ByteMatrixMap(&ml, lo, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k), strip_rows)) {
     return cudaErrorInvalidValue;
   }
   I8Params p;
@@ -497,7 +529,7 @@ cudaError_t LaunchInt8GemmI8(const void* x, int x_dtype, const int8_t* codes, co
   p.Kc = (nb + p.ks - 1) / p.ks * kI8BK;
   p.weights_const = weights_const ? 1 : 0;
   p.swiglu = swiglu ? 1 : 0;
-  e = y_dtype == TLALOC_B200_F32 ? LaunchI8<float>(mw, mh, ml, p, st) : LaunchI8<__nv_bfloat16>(mw, mh, ml, p, st);
+  e = y_dtype == TLALOC_B200_F32 ? LaunchI8Rows<float>(mw, mh, ml, p, st) : LaunchI8Rows<__nv_bfloat16>(mw, mh, ml, p, st);
   if (e != cudaSuccess) return e;
   ++*launches;
   return cudaSuccess;

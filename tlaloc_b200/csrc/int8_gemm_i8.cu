@@ -194,6 +194,7 @@ __global__ void __launch_bounds__(kI8Threads, 1)
   using L = I8Layout<MROWS>;
   constexpr int kI8Stages = L::kStages, kI8StripBytes = L::kStripBytes, kI8StageBytes = L::kStageBytes;
   constexpr int kI8BarOffset = L::kBarOffset, kI8ScaleOffset = L::kScaleOffset;
+  constexpr bool kStacked = MROWS <= 64;  // both planes in one accumulator's lanes (see the MMA thread)
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (SmemAddr(smem_raw) + 1023u) & ~1023u;  // the swizzle is a function of address bits 4..9
   unsigned char* smem = smem_raw + (smem_base - SmemAddr(smem_raw));
@@ -264,8 +265,10 @@ __global__ void __launch_bounds__(kI8Threads, 1)
     }
     __syncwarp();
   } else if (warp == kI8Workers / 32) {
-    // The MMA thread: per block, 4 K-steps of 32; the hi plane into accumulator columns 0..255, the lo plane into
-    // 256..511, both against the same codes.
+    // The MMA thread: per block, 4 K-steps of 32.  65 to 128 rows: the hi plane into accumulator columns 0..255, the lo
+    // plane into 256..511, both against the same codes.  Up to 64 rows: the stage's two strips, which lie one after the
+    // other, ARE one 128-row A operand (lanes [0, MROWS) the hi plane, [MROWS, 2 MROWS) the lo plane), so one MMA per
+    // K-step serves both planes and the codes are fetched from shared memory once.
     if (lane == 0) {
       constexpr uint32_t idesc = InstrDescI8();
       const uint64_t hi0 = SmemDesc(smem_base, 16, 1024), lo0 = SmemDesc(smem_base + kI8StripBytes, 16, 1024);
@@ -280,7 +283,7 @@ __global__ void __launch_bounds__(kI8Threads, 1)
           const uint32_t acc = (b > 0 || ks > 0) ? 1u : 0u;
           const uint64_t wd = w0 + stage + static_cast<uint64_t>((ks * 32 * 128) >> 4);
           TcMmaI8(tmem_base, hi0 + stage + static_cast<uint64_t>((ks * 32) >> 4), wd, idesc, acc);
-          TcMmaI8(tmem_base + kTcBN, lo0 + stage + static_cast<uint64_t>((ks * 32) >> 4), wd, idesc, acc);
+          if constexpr (!kStacked) TcMmaI8(tmem_base + kTcBN, lo0 + stage + static_cast<uint64_t>((ks * 32) >> 4), wd, idesc, acc);
         }
         TcCommit(empty0 + 8 * s);
       }
@@ -306,7 +309,44 @@ __global__ void __launch_bounds__(kI8Threads, 1)
   float* tile = reinterpret_cast<float*>(smem);
   const EpilogueOut out{p.residual, p.y, p.M, p.N, p.swiglu};
   const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0;
-  if (worker && (warp & 3) * 32 < MROWS) {
+  if constexpr (kStacked) {
+    // Lanes [0, MROWS) hold the hi sums of rows 0.., lanes [MROWS, 2 MROWS) the lo sums of the same rows: the warps on
+    // the lo lanes write lo * s[row] to the tile first, then the warps on the hi lanes add 256 hi * s[row] (s is a power
+    // of two, so this rounds exactly like (256 hi + lo) * s).
+    constexpr int kQuarters = MROWS / 32;  // lane quarters per plane
+    const int lg = warp & 3, wq = warp >> 2;
+    const int m = (lg % kQuarters) * 32 + lane;
+    const float rs = (worker && m < p.M) ? __ldg(p.row_scale + m) : 0.f;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const bool mine = worker && (pass == 0 ? (lg >= kQuarters && lg < 2 * kQuarters) : lg < kQuarters);
+      if (mine) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t a[32];
+          if (nblocks > 0) {
+            TcLd32(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + wq * 64 + h * 32, a);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) a[e] = 0u;
+          }
+          float4* dst = reinterpret_cast<float4*>(tile + m * kTcTileStride + wq * 64 + h * 32);
+          const float w = pass == 0 ? rs : 256.f * rs;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float4 v = pass == 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : dst[c];
+            v.x = fmaf(static_cast<float>(static_cast<int>(a[4 * c])), w, v.x);
+            v.y = fmaf(static_cast<float>(static_cast<int>(a[4 * c + 1])), w, v.y);
+            v.z = fmaf(static_cast<float>(static_cast<int>(a[4 * c + 2])), w, v.z);
+            v.w = fmaf(static_cast<float>(static_cast<int>(a[4 * c + 3])), w, v.w);
+            dst[c] = v;
+          }
+        }
+      }
+      if (pass == 0) __syncthreads();
+    }
+  } else if (worker && (warp & 3) * 32 < MROWS) {
     const int lg = warp & 3, wq = warp >> 2;
     const int m = lg * 32 + lane;
     const float rs = m < p.M ? __ldg(p.row_scale + m) : 0.f;

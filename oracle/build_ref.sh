@@ -1,8 +1,8 @@
 #!/bin/bash
 # Builds the reference's own CUDA paged-attention kernel (triton/kernels/paged_attention.cu with its vendored XLA
 # FFI headers) for sm_100a, straight from the reference checkout, into oracle/_ref/ (git-ignored).  Test
-# infrastructure: the result is the "reference itself, run here" leg of the parity tests and the same-box baseline
-# kernel of `bench.py --workload paged_attn`.  Usage: oracle/build_ref.sh [reference checkout, default /root/reference]
+# infrastructure: the result is the "reference itself, run here" leg of the parity tests and of their same-GPU timing
+# (tests/test_reference_kernel_gpu.py).  Usage: oracle/build_ref.sh [path of the reference checkout]
 set -euo pipefail
 REF="${1:-/root/reference}"
 HERE="$(cd "$(dirname "$0")" && pwd)"

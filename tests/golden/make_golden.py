@@ -2,7 +2,7 @@
 
 Run in a container that has the reference mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the reference checkout>
 
 reference_decode.json: the reference's own known-answer file for its decode
 seam (triton/examples/reference/reference_decode.json, produced by its DXIR

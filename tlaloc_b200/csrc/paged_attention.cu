@@ -51,7 +51,6 @@ struct PaParams {
   int group, rpt, NQ;
   int window, keep_chunks, keep_chunk;
   int bs_shift;  // log2(bs) when bs is a power of two, else -1
-  int kv_fast;   // tensor-core kernels: blockIdx.x is the KV head and blockIdx.y the slice (else the other way round)
   float scale;
 };
 
@@ -319,7 +318,7 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
   unsigned char* stages = smem;
   int* tab = reinterpret_cast<int*>(smem + L::kTabOffset);
 
-  const int s = p.kv_fast ? blockIdx.y : blockIdx.x, kv = p.kv_fast ? blockIdx.x : blockIdx.y, tb = blockIdx.z;
+  const int s = blockIdx.x, kv = blockIdx.y, tb = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gid = lane >> 2, tig = lane & 3;
   const int ctx = p.M * p.bs;
@@ -643,7 +642,7 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
   unsigned char* stages = smem;
   int* tab = reinterpret_cast<int*>(smem + L::kTabOffset);
 
-  const int s = p.kv_fast ? blockIdx.y : blockIdx.x, kv = p.kv_fast ? blockIdx.x : blockIdx.y, tb = blockIdx.z;
+  const int s = blockIdx.x, kv = blockIdx.y, tb = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gid = lane >> 2, tig = lane & 3;
   const int ctx = p.M * p.bs;
@@ -1184,7 +1183,7 @@ template <typename QT, int D, int NS>
 cudaError_t LaunchMmaNs(const PaParams& p, cudaStream_t stream)
 {
   const size_t smem = MmaLayout<D, NS>::Bytes(p.slice / p.bs + 2);
-  const dim3 grid(p.kv_fast ? p.Hkv : p.S, p.kv_fast ? p.S : p.Hkv, p.Tb);
+  const dim3 grid(p.S, p.Hkv, p.Tb);
   if (p.NQ <= 8) return LaunchChained(PaSliceMma<QT, D, NS, 1>, grid, kMmaThreads, smem, stream, p);
   return LaunchChained(PaSliceMma<QT, D, NS, 2>, grid, kMmaThreads, smem, stream, p);
 }
@@ -1217,7 +1216,7 @@ template <typename QT, int D>
 cudaError_t LaunchMmaF8(const PaParams& p, cudaStream_t stream)
 {
   const size_t smem = MmaLayoutF8<D, kF8Stages>::Bytes(p.slice / p.bs + 2);
-  const dim3 grid(p.kv_fast ? p.Hkv : p.S, p.kv_fast ? p.S : p.Hkv, p.Tb);
+  const dim3 grid(p.S, p.Hkv, p.Tb);
   if (p.NQ <= 8) return LaunchChained(PaSliceMmaF8<QT, D, kF8Stages, 1>, grid, kMmaThreads, smem, stream, p);
   return LaunchChained(PaSliceMmaF8<QT, D, kF8Stages, 2>, grid, kMmaThreads, smem, stream, p);
 }
@@ -1362,7 +1361,6 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
   p.keep_chunk = keep ? ctx / keep_chunks : 1;
   p.bs_shift = (block_size & (block_size - 1)) == 0 ? __builtin_ctz(block_size) : -1;
   p.scale = scale;
-  p.kv_fast = 0;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (OrderFaithful()) {  // parity mode: the interpreter's walk, straight into out (no slices, no scratch use)
@@ -1402,11 +1400,6 @@ extern "C" int tlaloc_b200_paged_attention(const void* query, int32_t q_dtype, c
   }
   p.slice = slice;
   p.S = (ctx + slice - 1) / slice;
-  static const bool kv_fast = [] {
-    const char* v = std::getenv("TLALOC_B200_PA_KV_FAST");
-    return v != nullptr && v[0] == '1';
-  }();
-  p.kv_fast = mma && kv_fast ? 1 : 0;
 
   cudaError_t e = cudaSuccess;
   if (mma) {

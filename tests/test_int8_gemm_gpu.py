@@ -410,3 +410,34 @@ def test_rmsnorm_writes_the_planes_the_projections_quantizer_would(rows, n):
     assert torch.equal(y_a, y_b)
     want = oracle.proj_int8(hn.float().cpu().numpy(), codes, scales, threads=8)
     close(y_a.cpu().numpy(), want)
+
+
+def test_activation_planes_match_their_definition():
+    """The quantizer's output against a numpy restatement of its rule: s = the smallest power of two with max|x| / s <=
+    127 * 256, q = rint(x / s) (ties to even), hi = floor((q + 128) / 256), lo = q - 256 hi; bit for bit, on rows with
+    outlier channels, a zero row, a tiny row and a row whose largest magnitude sits just below a power of two."""
+    rng = np.random.default_rng(77)
+    m, k = 48, 2048
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[:, ::61] *= 50.0
+    x[2] = 0.0
+    x[3] *= 1e-30
+    x[4, 7] = np.float32(255.0 / 256.0 * 64.0)  # 0.99609375 * 2^6: the step must move up one power of two
+    x[4, 8:] *= 0.01
+    x = oracle.snap_bf16(x)
+    o = ops()
+    scr = torch.zeros((o.int8_gemm_scratch_bytes(m, k, 0) + 3) // 4, dtype=torch.float32, device=DEV)
+    o.int8_gemm(dev(x, torch.bfloat16), torch.zeros((k, 256), dtype=torch.int8, device=DEV), None, scratch=scr, i8_mma=True)
+    torch.cuda.synchronize()
+    raw = scr.view(torch.int8)
+    hi = raw[:m * k].view(m, k).cpu().numpy().astype(np.int64)
+    lo = raw[m * k:2 * m * k].view(m, k).cpu().numpy().astype(np.int64)
+    steps = scr[(2 * m * k) // 4:(2 * m * k) // 4 + m].cpu().numpy().astype(np.float64)
+    want_steps = _row_steps(x)
+    want_steps[3] = max(want_steps[3], 2.0 ** -126)  # the step's exponent stops at the smallest normal f32
+    assert np.array_equal(steps, want_steps)
+    q = np.rint(x.astype(np.float64) / want_steps[:, None]).astype(np.int64)
+    want_hi = (q + 128) >> 8
+    assert np.array_equal(hi, want_hi) and np.array_equal(lo, q - 256 * want_hi)
+    assert np.abs(hi).max() <= 127 and lo.min() >= -128 and lo.max() <= 127
+    assert np.array_equal((256 * hi + lo)[4, 7] * steps[4], np.float64(x[4, 7]))  # exact where the row's bits allow

@@ -1198,27 +1198,55 @@ cudaError_t LaunchMma(const PaParams& p, cudaStream_t stream)
   }
 }
 
-constexpr int kF8Stages = 4;  // half the bytes per group: twice the groups in flight for the same shared memory
+constexpr int kF8Stages = 3;  // 48 KB per CTA: four CTAs per SM (83 vs 89 us on the operator configuration with four stages and three CTAs)
 
-template <typename QT, int D>
-cudaError_t PrepareMmaF8()
+// Stages per warp of the f8 kernel ($TLALOC_B200_PA_F8_STAGES = 3 or 4; two would not hold a warp's partial record).
+int MmaF8Stages()
 {
-  cudaError_t e = cudaFuncSetAttribute(PaSliceMmaF8<QT, D, kF8Stages, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(MmaLayoutF8<D, kF8Stages>::Bytes(kMaxTabEntries)));
+  static const int v = [] {
+    const char* e = std::getenv("TLALOC_B200_PA_F8_STAGES");
+    const int x = e != nullptr ? std::atoi(e) : 0;
+    return x >= 3 && x <= 4 ? x : kF8Stages;
+  }();
+  return v;
+}
+
+template <typename QT, int D, int NS>
+cudaError_t PrepareMmaF8Ns()
+{
+  cudaError_t e = cudaFuncSetAttribute(PaSliceMmaF8<QT, D, NS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(MmaLayoutF8<D, NS>::Bytes(kMaxTabEntries)));
   if (e == cudaSuccess) {
-    e = cudaFuncSetAttribute(PaSliceMmaF8<QT, D, kF8Stages, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(MmaLayoutF8<D, kF8Stages>::Bytes(kMaxTabEntries)));
+    e = cudaFuncSetAttribute(PaSliceMmaF8<QT, D, NS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(MmaLayoutF8<D, NS>::Bytes(kMaxTabEntries)));
   }
   return e;
 }
 
 template <typename QT, int D>
+cudaError_t PrepareMmaF8()
+{
+  cudaError_t e = PrepareMmaF8Ns<QT, D, 3>();
+  if (e == cudaSuccess) e = PrepareMmaF8Ns<QT, D, 4>();
+  return e;
+}
+
+template <typename QT, int D, int NS>
+cudaError_t LaunchMmaF8Ns(const PaParams& p, cudaStream_t stream)
+{
+  const size_t smem = MmaLayoutF8<D, NS>::Bytes(p.slice / p.bs + 2);
+  const dim3 grid(p.S, p.Hkv, p.Tb);
+  if (p.NQ <= 8) return LaunchChained(PaSliceMmaF8<QT, D, NS, 1>, grid, kMmaThreads, smem, stream, p);
+  return LaunchChained(PaSliceMmaF8<QT, D, NS, 2>, grid, kMmaThreads, smem, stream, p);
+}
+
+template <typename QT, int D>
 cudaError_t LaunchMmaF8(const PaParams& p, cudaStream_t stream)
 {
-  const size_t smem = MmaLayoutF8<D, kF8Stages>::Bytes(p.slice / p.bs + 2);
-  const dim3 grid(p.S, p.Hkv, p.Tb);
-  if (p.NQ <= 8) return LaunchChained(PaSliceMmaF8<QT, D, kF8Stages, 1>, grid, kMmaThreads, smem, stream, p);
-  return LaunchChained(PaSliceMmaF8<QT, D, kF8Stages, 2>, grid, kMmaThreads, smem, stream, p);
+  switch (MmaF8Stages()) {
+    case 3: return LaunchMmaF8Ns<QT, D, 3>(p, stream);
+    default: return LaunchMmaF8Ns<QT, D, 4>(p, stream);
+  }
 }
 
 template <typename QT, typename KVT>

@@ -626,7 +626,6 @@ struct MmaLayoutF8 {
   static constexpr int kStageBytes = 2 * kTileBytes;
   static constexpr int kWarpBytes = NS * kStageBytes;
   static constexpr int kTabOffset = kMmaWarps * kWarpBytes;
-  static_assert(kWarpBytes >= static_cast<int>(sizeof(float)) * kMmaQ * (D + 2), "a warp's stages hold its partial record");
   static size_t Bytes(int tab_entries) { return kTabOffset + sizeof(int) * static_cast<size_t>(tab_entries); }
 };
 
@@ -636,6 +635,7 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
   GridDependencySync();
   constexpr bool QLO = sizeof(QT) == 4;  // a bf16 query is exact in f16 (within its range): no low part to carry
   using L = MmaLayoutF8<D, NS>;
+  static_assert(L::kWarpBytes >= static_cast<int>(sizeof(float)) * (2 * kMmaQ + 8 * NT * D), "a warp's stages hold its partial record");
   constexpr int CPR = L::kRowBytes / 16;  // 16-byte chunks per row: 8 (D = 128) or 4 (D = 64)
   constexpr int KS = D / 16;              // k-steps of K Q^T, m-tiles of V^T P^T: one per chunk
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -1200,7 +1200,7 @@ cudaError_t LaunchMma(const PaParams& p, cudaStream_t stream)
 
 constexpr int kF8Stages = 3;  // 48 KB per CTA: four CTAs per SM (83 vs 89 us on the operator configuration with four stages and three CTAs)
 
-// Stages per warp of the f8 kernel ($TLALOC_B200_PA_F8_STAGES = 3 or 4; two would not hold a warp's partial record).
+// Stages per warp of the f8 kernel ($TLALOC_B200_PA_F8_STAGES = 3 or 4; two would not hold a 16-query partial record).
 int MmaF8Stages()
 {
   static const int v = [] {

@@ -265,12 +265,12 @@ int tlaloc_b200_rmsnorm(const float* x, const float* gain, void* out, int32_t ou
 /*
  * The same with a BF16 out, and the normalised rows also written as the activation planes of the int8 tensor-core
  * projection (see tlaloc_b200_int8_gemm): `planes` is that projection's scratch for an [rows, n] activation
- * (tlaloc_b200_int8_gemm_scratch_bytes(rows, n, 0) bytes, 16-byte aligned; n a multiple of 16).  The projection that
+ * (planes_bytes >= tlaloc_b200_int8_gemm_scratch_bytes(rows, n, 0), 16-byte aligned; n a multiple of 16).  The projection that
  * consumes `out` is then called with the same scratch and TLALOC_B200_GEMM_X_PLANES and skips its own quantizer launch.
  * The planes are exactly what that launch would have written.
  */
-int tlaloc_b200_rmsnorm_planes(const float* x, const float* gain, void* out, void* planes, int32_t rows, int32_t n, float eps,
-                               void* stream);
+int tlaloc_b200_rmsnorm_planes(const float* x, const float* gain, void* out, void* planes, size_t planes_bytes, int32_t rows,
+                               int32_t n, float eps, void* stream);
 
 /*
  * RoPE (HfDecoderGraph.kt:792-818, HF rotate_half with the duplicated cos/sin tables of
@@ -351,13 +351,14 @@ int tlaloc_b200_peer_allreduce_rmsnorm_f32(void* const* bases, size_t data_offse
  *   flag words (world of them at flag_offset) and state as tlaloc_b200_peer_allreduce_f32; calls of the three functions
  *   may be mixed on one state if every rank makes the same calls in the same order.
  *   planes    NULL, or (with norm_out) the scratch of the int8 tensor-core projection that consumes norm_out
- *             (tlaloc_b200_int8_gemm_scratch_bytes(rows, cols, 0) bytes, 16-byte aligned, cols a multiple of 16): the
+ *             (planes_bytes >= tlaloc_b200_int8_gemm_scratch_bytes(rows, cols, 0), 16-byte aligned, cols a multiple of 16): the
  *             normalised rows are also written as that projection's activation planes (TLALOC_B200_GEMM_X_PLANES)
  * cols a multiple of 4 up to 8192.  world == 1 is legal (out = residual + partial).
  */
 int tlaloc_b200_peer_sum_rows_f32(void* const* bases, size_t partial_offset, size_t flag_offset, uint32_t* state,
                                   const float* residual, float* out, void* norm_out, const float* gain, float eps,
-                                  int32_t rank, int32_t world, int32_t rows, int32_t cols, void* planes, void* stream);
+                                  int32_t rank, int32_t world, int32_t rows, int32_t cols, void* planes, size_t planes_bytes,
+                                  void* stream);
 
 /* ------------------------------------------------------------------ XLA typed-FFI registration */
 

@@ -188,12 +188,12 @@ class TlalocB200Ffm private constructor(arena: Arena, library: Path) {
             JAVA_INT, ADDRESS, JAVA_LONG, JAVA_LONG, ADDRESS,   // bases, partial_offset, flag_offset, state
             ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_FLOAT,     // residual, out, norm_out, gain, eps
             JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT,             // rank, world, rows, cols
-            ADDRESS, ADDRESS,                                   // planes (or null), stream
+            ADDRESS, JAVA_LONG, ADDRESS,                        // planes (or null), planes_bytes, stream
         ),
     )
     private val rmsnormPlanes = handle(
         "tlaloc_b200_rmsnorm_planes",
-        FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_INT, JAVA_INT, JAVA_FLOAT, ADDRESS),
+        FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_LONG, JAVA_INT, JAVA_INT, JAVA_FLOAT, ADDRESS),
     )
     private val registerKernels = handle("TlalocRegisterKernels", FunctionDescriptor.of(ADDRESS, ADDRESS))
     private val ffiHandler = handle("tlaloc_b200_ffi_handler", FunctionDescriptor.of(ADDRESS, ADDRESS))
@@ -347,21 +347,21 @@ class TlalocB200Ffm private constructor(arena: Arena, library: Path) {
     @Suppress("LongParameterList")
     fun peerSumRowsF32(
         arena: Arena, bases: LongArray, partialOffset: Long, flagOffset: Long, state: Long, residual: Long, out: Long, normOut: Long,
-        gain: Long, eps: Float, rank: Int, rows: Int, cols: Int, planes: Long, stream: Long,
+        gain: Long, eps: Float, rank: Int, rows: Int, cols: Int, planes: Long, planesBytes: Long, stream: Long,
     ) {
         val table = arena.allocate(ADDRESS, bases.size.toLong())
         bases.forEachIndexed { i, b -> table.setAtIndex(ADDRESS, i.toLong(), ptr(b)) }
         check(
             peerSumRows.invokeExact(
                 table, partialOffset, flagOffset, ptr(state), ptr(residual), ptr(out), ptr(normOut), ptr(gain), eps, rank, bases.size, rows, cols,
-                ptr(planes), ptr(stream),
+                ptr(planes), planesBytes, ptr(stream),
             ) as Int,
         )
     }
 
     /** RMSNorm with a bf16 result that also writes the int8 tensor-core projection's activation planes (GEMM_X_PLANES). */
-    fun rmsnormPlanes(x: Long, gain: Long, out: Long, planes: Long, rows: Int, n: Int, eps: Float, stream: Long) =
-        check(rmsnormPlanes.invokeExact(ptr(x), ptr(gain), ptr(out), ptr(planes), rows, n, eps, ptr(stream)) as Int)
+    fun rmsnormPlanes(x: Long, gain: Long, out: Long, planes: Long, planesBytes: Long, rows: Int, n: Int, eps: Float, stream: Long) =
+        check(rmsnormPlanes.invokeExact(ptr(x), ptr(gain), ptr(out), ptr(planes), planesBytes, rows, n, eps, ptr(stream)) as Int)
 
     /** TlalocRegisterKernels(PJRT_Api*): null on success, else the library's message. */
     fun registerKernels(pjrtApi: MemorySegment): String? {

@@ -41,7 +41,7 @@ _SIGNATURES = {
     "tlaloc_b200_dense_gemm_exact": (ctypes.c_int, [_vp, _i32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_embedding": (ctypes.c_int, [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_rmsnorm": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp]),
-    "tlaloc_b200_rmsnorm_planes": (ctypes.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp]),
+    "tlaloc_b200_rmsnorm_planes": (ctypes.c_int, [_vp, _vp, _vp, _vp, _sz, _i32, _i32, _f32, _vp]),
     "tlaloc_b200_rope_kv_write": (ctypes.c_int, [_vp] * 8 + [_i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_swiglu": (ctypes.c_int, [_vp, _vp, _i32, _vp, _i32, _i32, _i32, _vp]),
     "tlaloc_b200_argmax": (ctypes.c_int, [_vp, _vp, _i32, _i32, _vp]),
@@ -52,7 +52,7 @@ _SIGNATURES = {
     "tlaloc_b200_peer_allreduce_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _vp, _i32, _i32, _sz, _vp]),
     "tlaloc_b200_peer_allreduce_rmsnorm_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _sz, _vp, _vp, _f32, _i32, _i32,
                                                               _i32, _i32, _vp]),
-    "tlaloc_b200_peer_sum_rows_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _vp, _vp, _vp, _vp, _vp, _f32, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "tlaloc_b200_peer_sum_rows_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _vp, _vp, _vp, _vp, _vp, _f32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "TlalocRegisterKernels": (ctypes.c_char_p, [_vp]),
     "tlaloc_b200_ffi_handler": (_vp, [ctypes.c_char_p]),
 }

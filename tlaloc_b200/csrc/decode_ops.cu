@@ -338,14 +338,17 @@ extern "C" int tlaloc_b200_rmsnorm(const float* x, const float* gain, void* out,
   return kOk;
 }
 
-extern "C" int tlaloc_b200_rmsnorm_planes(const float* x, const float* gain, void* out, void* planes, int32_t rows, int32_t n,
-                                          float eps, void* stream)
+extern "C" int tlaloc_b200_rmsnorm_planes(const float* x, const float* gain, void* out, void* planes, size_t planes_bytes,
+                                          int32_t rows, int32_t n, float eps, void* stream)
 {
   const char* op = "RMSNORM_PLANES";
   if (!x || !out || !planes) return Fail(kInvalid, "%s: a required device pointer is null", op);
   if (rows < 0 || n < 1) return Fail(kInvalid, "%s: bad sizes", op);
   if (rows == 0) return kOk;
   if (!Aligned16(planes) || n % 16 != 0) return Fail(kInvalid, "%s: the planes must be 16-byte aligned and n a multiple of 16", op);
+  if (planes_bytes < Int8GemmI8ScratchBytes(rows, n)) {
+    return Fail(kInvalid, "%s: the planes of %d x %d need %zu bytes, got %zu", op, rows, n, Int8GemmI8ScratchBytes(rows, n), planes_bytes);
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // One launch when the row stays in registers; otherwise (long or unaligned rows, parity mode) the norm, then the
   // projection's own quantizer on its bf16 result.

@@ -502,7 +502,7 @@ int LaunchPeerAllReduceNorm(void* const* bases, size_t data_offset, size_t norm_
 
 int LaunchPeerSumRows(void* const* bases, size_t partial_offset, size_t flag_offset, uint32_t* state, const float* residual,
                       float* out, void* norm_out, const float* gain, float eps, int rank, int world, int rows, int cols,
-                      void* planes, cudaStream_t st)
+                      void* planes, size_t planes_bytes, cudaStream_t st)
 {
   const char* op = "peer_sum_rows";
   if (world < 1 || world > kMaxRanks) return Fail(kInvalid, "%s: world %d outside [1, %d]", op, world, kMaxRanks);
@@ -520,8 +520,9 @@ int LaunchPeerSumRows(void* const* bases, size_t partial_offset, size_t flag_off
     t.partial[q] = reinterpret_cast<const float*>(static_cast<const char*>(bases[q]) + partial_offset);
     t.flags[q] = reinterpret_cast<uint32_t*>(static_cast<char*>(bases[q]) + flag_offset);
   }
-  if (planes != nullptr && (norm_out == nullptr || !Aligned16(planes) || cols % 16 != 0)) {
-    return Fail(kInvalid, "%s: planes need norm_out, 16-byte alignment and cols a multiple of 16", op);
+  if (planes != nullptr && (norm_out == nullptr || !Aligned16(planes) || cols % 16 != 0 || planes_bytes < Int8GemmI8ScratchBytes(rows, cols))) {
+    return Fail(kInvalid, "%s: planes need norm_out, 16-byte alignment, cols a multiple of 16 and %zu bytes (got %zu)", op,
+                Int8GemmI8ScratchBytes(rows, cols), planes_bytes);
   }
   const int grid = rows < 148 ? rows : 148;
   __nv_bfloat16* nout = static_cast<__nv_bfloat16*>(norm_out);
@@ -602,8 +603,9 @@ extern "C" int tlaloc_b200_peer_allreduce_rmsnorm_f32(void* const* bases, size_t
 
 extern "C" int tlaloc_b200_peer_sum_rows_f32(void* const* bases, size_t partial_offset, size_t flag_offset, uint32_t* state,
                                              const float* residual, float* out, void* norm_out, const float* gain, float eps,
-                                             int32_t rank, int32_t world, int32_t rows, int32_t cols, void* planes, void* stream)
+                                             int32_t rank, int32_t world, int32_t rows, int32_t cols, void* planes,
+                                             size_t planes_bytes, void* stream)
 {
   return LaunchPeerSumRows(bases, partial_offset, flag_offset, state, residual, out, norm_out, gain, eps, rank, world, rows, cols,
-                           planes, static_cast<cudaStream_t>(stream));
+                           planes, planes_bytes, static_cast<cudaStream_t>(stream));
 }

@@ -197,7 +197,7 @@ def rmsnorm(x, gain, eps, *, out=None, out_dtype=torch.float32, planes=None):
         _out("RMSNORM planes", planes, None, torch.float32, x)
         if out.dtype != torch.bfloat16 or planes.numel() * 4 < int8_gemm_scratch_bytes(rows, n, 0):
             raise ValueError("RMSNORM: planes need a bf16 out and int8_gemm_scratch_bytes(rows, n, 0) bytes")
-        N.check(N.lib().tlaloc_b200_rmsnorm_planes(_ptr(x), _ptr(gain), _ptr(out), _ptr(planes), rows, n, float(eps), _stream(x)))
+        N.check(N.lib().tlaloc_b200_rmsnorm_planes(_ptr(x), _ptr(gain), _ptr(out), _ptr(planes), planes.numel() * 4, rows, n, float(eps), _stream(x)))
         return out
     N.check(N.lib().tlaloc_b200_rmsnorm(_ptr(x), _ptr(gain), _ptr(out), _dt(out), rows, n, float(eps), _stream(x)))
     return out

@@ -120,7 +120,8 @@ class PeerBuffers:
             self._bases, self.offsets[index], self.flag_offset, self.state.data_ptr(),
             None if residual is None else residual.data_ptr(), out.data_ptr(), None if norm_out is None else norm_out.data_ptr(),
             None if gain is None else gain.data_ptr(), float(eps), self.rank, self.world, t.shape[0], t.shape[1],
-            None if planes is None else planes.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream))
+            None if planes is None else planes.data_ptr(), 0 if planes is None else planes.numel() * planes.element_size(),
+            torch.cuda.current_stream(self.device).cuda_stream))
         return out
 
     def can_sum_rows(self, index: int) -> bool:

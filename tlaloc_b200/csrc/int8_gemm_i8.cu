@@ -2,7 +2,7 @@
 // y = (cast(x) @ cast(codes)) * scale (HfDecoderGraph.proj, ir/.../inference/HfDecoderGraph.kt:625-655).
 //
 // The bf16 form of this projection (int8_gemm_tc.cu) spends its time turning codes into bf16 on the ALUs and pushing them
-// through shared memory twice.  Here the codes go global -> shared memory by TMA and are read by tcgen05.mma.kind::i8
+// through shared memory twice.  (Opt-in: TLALOC_B200_GEMM_I8_MMA; the caller accepts the activation format below.)  Here the codes go global -> shared memory by TMA and are read by tcgen05.mma.kind::i8
 // as they are; it is the ACTIVATIONS that change form.  A row of x (bf16; an f32 x is rounded to bf16 first, as the
 // bf16 kernel does) is written as
 //     x[m, k] ~ (256 hi[m, k] + lo[m, k]) * s[m],   s[m] a power of two, hi in [-127, 127], lo in [-128, 127]
@@ -10,7 +10,8 @@
 // magnitude is represented EXACTLY (a bf16 has 8 significant bits), smaller ones are rounded to the nearest multiple of
 // s[m], an absolute error of at most 2^-16 of the row's largest magnitude.  Then
 //     y[m, n] = (256 sum_k hi w + sum_k lo w) * s[m] * scale[n]
-// with both sums exact in int32 (|sum| <= 127 * 127 * K), two MMAs per K step into two TMEM accumulators.  Integer-valued
+// with both sums exact in int32 (|sum| <= 128 * 127 * K), two MMAs per K step into two TMEM accumulators (up to 64
+// rows: one MMA whose 128 lanes carry both planes).  Integer-valued
 // activations come out exact; for others the difference from the f32-accumulating bf16 kernel is far below bf16's own
 // rounding of the inputs.  A row holding an infinity or a NaN gets s = NaN, so its whole output row is NaN.
 //
@@ -20,7 +21,9 @@
 //   producer thread  one lane; per block four TMA loads (hi strip, lo strip: K-major 128-byte-swizzled [rows][128 k];
 //                    the block's codes as two MN-major 128-byte-swizzled boxes [128 k][128 n]: W's rows are contiguous
 //                    along N, which is MN-major, so nothing is transposed) onto the stage's mbarrier;
-//   MMA thread       one lane; per block 4 K-steps x {hi, lo} of 128 x 256 x 32, then a commit that hands the stage back;
+//   MMA thread       one lane; per block 4 K-steps x {hi, lo} of 128 x 256 x 32 (up to 64 rows: the two strips, which
+//                    lie one after the other, are ONE 128-row A operand, so one MMA per K-step serves both planes and
+//                    the codes leave shared memory once), then a commit that hands the stage back;
 //   sixteen warps    sleep at the CTA barrier until the last MMA has completed, then run the epilogue shared with the
 //                    bf16 kernel (tile in shared memory, scale / residual / SwiGLU, cluster sum over the K slices).
 // Rows past M and k past K are outside the tensor maps and arrive as zeros.  Every mbarrier wait is bounded.

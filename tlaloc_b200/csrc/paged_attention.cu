@@ -602,11 +602,16 @@ __device__ __forceinline__ void MmaF16(float (&c)[4], const uint32_t (&a)[4], ui
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// Two e4m3fn bytes (the low and the high byte of `pair`) as an f16 pair, exactly.
-__device__ __forceinline__ uint32_t E4m3x2ToF16x2(uint32_t pair)
+// The four e4m3fn bytes of a word as two f16 pairs (bytes 0, 1 and bytes 2, 3), exactly; the halves of the word are
+// named as 16-bit registers, with no shift or mask of their own.
+__device__ __forceinline__ void E4m3x4ToF16x2x2(uint32_t word, uint32_t& low_pair, uint32_t& high_pair)
 {
-  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(pair & 0xFFFFu), __NV_E4M3);
-  return static_cast<uint32_t>(h.x) | (static_cast<uint32_t>(h.y) << 16);
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}\n"
+      : "=r"(low_pair), "=r"(high_pair)
+      : "r"(word));
 }
 // Two floats as f16 hi parts (lower index in the low half) and the f16 of what is left.
 __device__ __forceinline__ void SplitPackF16(float x, float y, uint32_t& hi, uint32_t& lo)
@@ -789,7 +794,9 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
       for (int half = 0; half < 2; ++half) {
         const int kk = 2 * j + half;
         const uint32_t lo_rows = r[2 * half], hi_rows = r[2 * half + 1];
-        const uint32_t a[4] = {E4m3x2ToF16x2(lo_rows), E4m3x2ToF16x2(hi_rows), E4m3x2ToF16x2(lo_rows >> 16), E4m3x2ToF16x2(hi_rows >> 16)};
+        uint32_t a[4];
+        E4m3x4ToF16x2x2(lo_rows, a[0], a[2]);
+        E4m3x4ToF16x2x2(hi_rows, a[1], a[3]);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           MmaF16(sacc[nt], a, qh[nt][kk][0], qh[nt][kk][1]);
@@ -850,7 +857,9 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
         const int mt = 2 * j + half;
         // bytes {p0 c0, p0 c1, p1 c0, p1 c1} -> {p0 c0, p1 c0 | p0 c1, p1 c1}: the two positions of each channel side by side
         const uint32_t lo_pos = __byte_perm(r[2 * half], 0u, 0x3120), hi_pos = __byte_perm(r[2 * half + 1], 0u, 0x3120);
-        const uint32_t a[4] = {E4m3x2ToF16x2(lo_pos), E4m3x2ToF16x2(lo_pos >> 16), E4m3x2ToF16x2(hi_pos), E4m3x2ToF16x2(hi_pos >> 16)};
+        uint32_t a[4];
+        E4m3x4ToF16x2x2(lo_pos, a[0], a[1]);
+        E4m3x4ToF16x2x2(hi_pos, a[2], a[3]);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           MmaF16(o[nt][mt], a, pb_hi[nt][0], pb_hi[nt][1]);

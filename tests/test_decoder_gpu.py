@@ -125,25 +125,28 @@ def test_tiny_decoder_64_greedy_steps_match_the_oracle(kv_dtype, head_quant, exa
 
 
 def test_batch_of_40_with_swiglu_in_the_projection_epilogue_matches_the_oracle():
-    """17 to 128 rows and an FFN width that tiles in blocks of 128: the engine runs the int8 tensor-core projection and
-    folds SwiGLU into the gate|up projection's epilogue (weights interleaved at load).  Against the oracle's step."""
+    """17 to 128 rows and an FFN width that tiles in blocks of 128: the engine runs the int8 tensor-core projection (the
+    activation planes written by the RMSNorm kernel) and folds SwiGLU into the gate|up projection's epilogue (weights
+    interleaved at load).  64 greedy steps, teacher-forced on the oracle's tokens: logits within the bar at every step,
+    and a different token only where the oracle itself ranks the two candidates closer than the runs' logits differ."""
     from tlaloc_b200 import decoder as D
     from tlaloc_b200 import sharding
 
     dims = dict(num_layers=2, d_model=256, num_heads=4, num_kv_heads=2, head_dim=64, ffn=512, vocab=512)
     shape = oracle.DecoderShape(**dims, kv_dtype="bf16", head_quant=True)
     w = oracle.make_weights(shape, seed=7)
-    cfg = D.DecoderConfig(**dims, kv_dtype=torch.bfloat16, head_quant=True, max_positions=64)
-    B, bs, M = 40, 16, 2
+    cfg = D.DecoderConfig(**dims, kv_dtype=torch.bfloat16, head_quant=True, max_positions=80)
+    B, bs, M = 40, 16, 5
     rng = np.random.default_rng(3)
     tables = (1 + rng.permutation(B * M)).reshape(B, M).astype(np.int32)
     dec = D.Decoder(cfg, B, 1 + B * M, M)
-    assert dec.fuse_swiglu
+    assert dec.fuse_swiglu and dec.i8_mma and dec.norm_planes
     dec.load_host_weights(w)
     kp = [np.zeros((1 + B * M, bs, 2, 64), np.float32) for _ in range(2)]
     vp = [np.zeros_like(a) for a in kp]
     ids = rng.integers(0, 512, size=B).astype(np.int32)
-    for step in range(6):
+    swaps = 0
+    for step in range(64):
         pos = np.full(B, step, np.int32)
         slots = sharding.slot_mapping(tables, pos, bs)
         dec.set_inputs(ids, pos, tables, pos + 1, slots)
@@ -157,4 +160,6 @@ def test_batch_of_40_with_swiglu_in_the_projection_epilogue_matches_the_oracle()
         # a different token only where the oracle's own logits rank the two closer than the runs' logits differ
         for i in np.nonzero(nxt != ids)[0]:
             assert float(want[i, ids[i]] - want[i, nxt[i]]) <= 2.0 * float(err[i].max()), (step, i)
-        assert np.mean(nxt == ids) >= 0.9
+            swaps += 1
+    print(f"near-tie swaps: {swaps} of {64 * B}")
+    assert swaps <= 0.03 * 64 * B

@@ -162,4 +162,4 @@ def test_batch_of_40_with_swiglu_in_the_projection_epilogue_matches_the_oracle()
             assert float(want[i, ids[i]] - want[i, nxt[i]]) <= 2.0 * float(err[i].max()), (step, i)
             swaps += 1
     print(f"near-tie swaps: {swaps} of {64 * B}")
-    assert swaps <= 0.10 * 64 * B
+    assert swaps <= 0.015 * 64 * B  # observed: 13 of 2560

@@ -153,6 +153,7 @@ cudaError_t LaunchInt8GemmTc(const __nv_bfloat16* x, const int8_t* codes, const 
 int ReadTcStatus();
 // The same projection with the codes fed to the tensor core as int8 and the activations as two int8 planes
 // (int8_gemm_i8.cu); m <= 128 rows per call.
+cudaError_t PrepareInt8GemmI8Kernels();
 bool Int8GemmI8Applies(const void* codes, int m, int k, int n);
 size_t Int8GemmI8ScratchBytes(int m, int k);
 cudaError_t LaunchInt8GemmI8(const void* x, int x_dtype, const int8_t* codes, const float* scales, const float* residual,

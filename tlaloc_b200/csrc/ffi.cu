@@ -312,6 +312,7 @@ extern "C" int tlaloc_b200_init(void)
   cudaError_t e = PreparePagedAttentionKernels();
   if (e == cudaSuccess) e = PrepareInt8GemmKernels();
   if (e == cudaSuccess) e = PrepareInt8GemmTcKernels();
+  if (e == cudaSuccess) e = PrepareInt8GemmI8Kernels();
   if (e != cudaSuccess) return CudaFail("kernel set-up", e);
   return kOk;
 }

@@ -525,6 +525,12 @@ cudaError_t LaunchI8Rows(const CUtensorMap& mw, const CUtensorMap& mh, const CUt
 
 }  // namespace
 
+cudaError_t PrepareInt8GemmI8Kernels()
+{
+  EncodeTiled();  // resolves the driver entry point now rather than inside a later stream capture
+  return PrepareI8();
+}
+
 size_t Int8GemmI8ScratchBytes(int m, int k) { return 2 * static_cast<size_t>(m) * k + 4 * static_cast<size_t>(m); }
 
 bool Int8GemmI8Applies(const void* codes, int m, int k, int n)

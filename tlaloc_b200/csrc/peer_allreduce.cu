@@ -195,7 +195,8 @@ __device__ __forceinline__ float BlockSum512(float v, float* red)
 // Grid (row CTAs, kNormParts), clusters (1, kNormParts, 1): blockIdx.y is the part of the row this CTA holds.
 template <int W>
 __global__ void __launch_bounds__(kThreads, 1)
-PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, float eps, int rank, int world_rt, int rows, int cols)
+PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, float eps, int rank, int world_rt, int rows, int cols,
+                        float* own_rows)
 {
   GridDependencySync();
   namespace cg = cooperative_groups;
@@ -237,6 +238,10 @@ PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, flo
         for (int q = 0; q < kMaxRanks; ++q)
           if (q < world) v[q] = LoadPeer(t.data[q] + base + 4 * (c_lo + c));
         float4 a = v[0];
+        if (own_rows != nullptr) {  // the residual stream of this rank's rows comes first, then the partials in rank order
+          const float4 r = *reinterpret_cast<const float4*>(own_rows + static_cast<size_t>(row - r_lo) * cols + 4 * (c_lo + c));
+          a.x += r.x; a.y += r.y; a.z += r.z; a.w += r.w;
+        }
 #pragma unroll
         for (int q = 1; q < kMaxRanks; ++q)
           if (q < world) { a.x += v[q].x; a.y += v[q].y; a.z += v[q].z; a.w += v[q].w; }
@@ -267,11 +272,19 @@ PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, flo
         uint2 packed;
         packed.x = *reinterpret_cast<const uint32_t*>(&lo);
         packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        if (own_rows != nullptr) {
+          // the sums stay here, in this rank's rows of the residual stream; only the normalised row travels
+          *reinterpret_cast<float4*>(own_rows + static_cast<size_t>(row - r_lo) * cols + 4 * cc) = a;
 #pragma unroll
-        for (int q = 0; q < kMaxRanks; ++q) {
-          if (q < world) {
-            *reinterpret_cast<float4*>(t.data[q] + base + 4 * cc) = a;
-            *reinterpret_cast<uint2*>(t.norm[q] + base + 4 * cc) = packed;
+          for (int q = 0; q < kMaxRanks; ++q)
+            if (q < world) *reinterpret_cast<uint2*>(t.norm[q] + base + 4 * cc) = packed;
+        } else {
+#pragma unroll
+          for (int q = 0; q < kMaxRanks; ++q) {
+            if (q < world) {
+              *reinterpret_cast<float4*>(t.data[q] + base + 4 * cc) = a;
+              *reinterpret_cast<uint2*>(t.norm[q] + base + 4 * cc) = packed;
+            }
           }
         }
       }
@@ -460,8 +473,9 @@ int LaunchPeerAllReduce(void* const* bases, size_t data_offset, size_t flag_offs
 }
 
 int LaunchPeerAllReduceNorm(void* const* bases, size_t data_offset, size_t norm_offset, size_t flag_offset, uint32_t* state,
-                            const float* gain, float eps, int rank, int world, int rows, int cols, cudaStream_t st)
+                            const float* gain, float eps, int rank, int world, int rows, int cols, float* own_rows, cudaStream_t st)
 {
+  if (own_rows != nullptr && !Aligned16(own_rows)) return Fail(kInvalid, "peer_reduce_rmsnorm_rows: own_rows must be 16-byte aligned");
   if (world < 2 || world > kMaxRanks) return Fail(kInvalid, "peer_allreduce_rmsnorm: world %d outside [2, %d]", world, kMaxRanks);
   if (rank < 0 || rank >= world) return Fail(kInvalid, "peer_allreduce_rmsnorm: rank %d outside [0, %d)", rank, world);
   if (!bases || !state) return Fail(kInvalid, "peer_allreduce_rmsnorm: null base table or state");
@@ -490,10 +504,10 @@ int LaunchPeerAllReduceNorm(void* const* bases, size_t data_offset, size_t norm_
   cfg.attrs = attrs;
   cudaError_t e;
   switch (world) {
-    case 2: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<2>, t, state, gain, eps, rank, world, rows, cols); break;
-    case 4: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<4>, t, state, gain, eps, rank, world, rows, cols); break;
-    case 8: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<8>, t, state, gain, eps, rank, world, rows, cols); break;
-    default: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<0>, t, state, gain, eps, rank, world, rows, cols); break;
+    case 2: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<2>, t, state, gain, eps, rank, world, rows, cols, own_rows); break;
+    case 4: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<4>, t, state, gain, eps, rank, world, rows, cols, own_rows); break;
+    case 8: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<8>, t, state, gain, eps, rank, world, rows, cols, own_rows); break;
+    default: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<0>, t, state, gain, eps, rank, world, rows, cols, own_rows); break;
   }
   if (e != cudaSuccess) return CudaFail("peer_allreduce_rmsnorm launch", e);
   CountLaunches(1);
@@ -598,7 +612,17 @@ extern "C" int tlaloc_b200_peer_allreduce_rmsnorm_f32(void* const* bases, size_t
                                                       int32_t rank, int32_t world, int32_t rows, int32_t cols, void* stream)
 {
   return LaunchPeerAllReduceNorm(bases, data_offset, norm_offset, flag_offset, state, gain, eps, rank, world, rows, cols,
-                                 static_cast<cudaStream_t>(stream));
+                                 nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tlaloc_b200_peer_reduce_rmsnorm_rows_f32(void* const* bases, size_t data_offset, size_t norm_offset,
+                                                        size_t flag_offset, uint32_t* state, float* own_rows, const float* gain,
+                                                        float eps, int32_t rank, int32_t world, int32_t rows, int32_t cols,
+                                                        void* stream)
+{
+  if (!own_rows) return Fail(kInvalid, "peer_reduce_rmsnorm_rows: own_rows is null");
+  return LaunchPeerAllReduceNorm(bases, data_offset, norm_offset, flag_offset, state, gain, eps, rank, world, rows, cols,
+                                 own_rows, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int tlaloc_b200_peer_sum_rows_f32(void* const* bases, size_t partial_offset, size_t flag_offset, uint32_t* state,

@@ -127,6 +127,13 @@ class Decoder:
         self.fuse_norm = (self.peer is not None and not self.one_shot and self.peer.can_fuse_norm(0)
                           and os.environ.get("TLALOC_B200_TP_FUSE_NORM", "1") != "0")
         self.hn = self.peer.norm_out if self.fuse_norm else torch.empty((B, d), **bf)
+        # With the norm folded into the exchange, the f32 residual stream need not travel at all: each rank keeps its
+        # own rows of it, the projections hand over bare partial sums, and only the normalised bf16 rows are gathered
+        # ($TLALOC_B200_TP_ROWS=0: every rank keeps the whole stream, summed in place).
+        self.rows_residual = self.fuse_norm and os.environ.get("TLALOC_B200_TP_ROWS", "1") != "0"
+        if self.rows_residual:
+            self.row_lo, self.row_hi = B * rank // world, B * (rank + 1) // world
+            self.h_rows = torch.empty((self.row_hi - self.row_lo, d), **f32)
         self.qkv = torch.empty((B, nqkv), **f32)
         self.q_rot = torch.empty((B, self.hq, hd), **f32)
         self.att = torch.empty((B, self.hq, hd), **bf)
@@ -232,6 +239,8 @@ class Decoder:
     def _launch_step(self) -> None:
         if self.one_shot:
             return self._launch_step_one_shot()
+        if self.rows_residual:
+            return self._launch_step_rows()
         cfg, B = self.cfg, self.batch
         hd, hq, hk = cfg.head_dim, self.hq, self.hk
         ops.embedding(self.embed, self.token_ids, out=self.h)
@@ -268,6 +277,33 @@ class Decoder:
                 self._all_reduce(h)
         if not fused:
             ops.rmsnorm(h, self.final_norm, cfg.rms_eps, out=self.hn)
+        self._head_and_greedy()
+
+    def _launch_step_rows(self) -> None:
+        """The tensor-parallel step with the residual stream distributed by rows: o_proj and down_proj write bare partial
+        sums into the two peer buffers; the exchange kernel adds this rank's rows of the residual stream and every
+        rank's partial, keeps the sums in `h_rows` and gathers only the next RMSNorm's bf16 output."""
+        cfg, B = self.cfg, self.batch
+        hd, hq = cfg.head_dim, self.hq
+        p_down, p_o = self.peer.tensors
+        ops.embedding(self.embed, self.token_ids, out=p_down)  # the whole embedding on every rank: its norm is local
+        self.h_rows.copy_(p_down[self.row_lo:self.row_hi])
+        q3, k3, v3 = self._qkv_views()
+        how = dict(weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
+        pl = self.proj_scratch if self.norm_planes else None
+        ops.rmsnorm(p_down, self.layers[0]["ln1"], cfg.rms_eps, out=self.hn, planes=pl)
+        for l, lw in enumerate(self.layers):
+            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, x_planes=pl is not None and l == 0, **how)
+            ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
+                              self.value_pools[l], q_out=self.q_rot)
+            ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
+                                scale=cfg.scale, out=self.att, scratch=self.att_scratch)
+            ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], out=p_o, **how)
+            self.peer.reduce_norm_rows_(1, self.h_rows, lw["ln2"], cfg.rms_eps)
+            self.gate_up_proj(lw)
+            ops.int8_gemm(self.act, *lw["down"], out=p_down, **how)
+            nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
+            self.peer.reduce_norm_rows_(0, self.h_rows, nxt, cfg.rms_eps)
         self._head_and_greedy()
 
     def _launch_step_one_shot(self) -> None:

@@ -105,6 +105,20 @@ class PeerBuffers:
             torch.cuda.current_stream(self.device).cuda_stream))
         return t, self.norm_out
 
+    def reduce_norm_rows_(self, index: int, own_rows, gain, eps: float):
+        """Tensor `index` holds this rank's PARTIAL result.  Adds this rank's rows of the residual stream (`own_rows`,
+        local f32 [rows / world, cols], updated in place) and every rank's partial for those rows, and leaves
+        RMSNorm(sum) * gain of ALL rows as bf16 in `norm_out` on every rank.  The f32 sums never travel."""
+        t = self.tensors[index]
+        if (own_rows.dtype != torch.float32 or not own_rows.is_contiguous() or own_rows.dim() != 2
+                or own_rows.shape[0] * self.world != t.shape[0] or own_rows.shape[1] != t.shape[1]):
+            raise ValueError("reduce_norm_rows_: own_rows must be contiguous f32 [rows / world, cols]")
+        N.check(N.lib().tlaloc_b200_peer_reduce_rmsnorm_rows_f32(
+            self._bases, self.offsets[index], self.norm_offset, self.flag_offset, self.state.data_ptr(), own_rows.data_ptr(),
+            None if gain is None else gain.data_ptr(), float(eps), self.rank, self.world, t.shape[0], t.shape[1],
+            torch.cuda.current_stream(self.device).cuda_stream))
+        return self.norm_out
+
     def sum_rows_(self, index: int, residual, out, gain, eps: float, norm_out=None, planes=None):
         """The one-barrier form: out = residual + sum over ranks of tensor `index` (every rank's partial, added in rank
         order) into LOCAL `out` (f32, may be `residual` itself), and RMSNorm(out) * gain as bf16 into local `norm_out`;

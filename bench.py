@@ -825,6 +825,8 @@ def run_peer_sum(args) -> dict:
         row = {"shape": list(shp), "bytes": 4 * shp[0] * shp[1], "peer_us": timed(lambda: peer.all_reduce_(0))}
         if peer.can_fuse_norm(0):
             row["peer_with_rmsnorm_us"] = timed(lambda: peer.all_reduce_norm_(0, gain, 1e-5))
+            own = torch.zeros((shp[0] // world, shp[1]), device=dev)
+            row["rows_residual_with_rmsnorm_us"] = timed(lambda: peer.reduce_norm_rows_(0, own, gain, 1e-5))
         if peer.can_sum_rows(0):
             two = PeerBuffers([shp, shp], rank=rank, world=world, group=group, device=dev)
             hbuf = torch.zeros(shp, device=dev)

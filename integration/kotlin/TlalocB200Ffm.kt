@@ -182,6 +182,14 @@ class TlalocB200Ffm private constructor(arena: Arena, library: Path) {
             JAVA_INT, ADDRESS, JAVA_LONG, JAVA_LONG, JAVA_LONG, ADDRESS, ADDRESS, JAVA_FLOAT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS,
         ),
     )
+    private val peerReduceNormRows = handle(
+        "tlaloc_b200_peer_reduce_rmsnorm_rows_f32",
+        FunctionDescriptor.of(
+            JAVA_INT, ADDRESS, JAVA_LONG, JAVA_LONG, JAVA_LONG, ADDRESS,   // bases, data_offset, norm_offset, flag_offset, state
+            ADDRESS, ADDRESS, JAVA_FLOAT,                                  // own_rows, gain, eps
+            JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS,               // rank, world, rows, cols, stream
+        ),
+    )
     private val peerSumRows = handle(
         "tlaloc_b200_peer_sum_rows_f32",
         FunctionDescriptor.of(
@@ -341,6 +349,21 @@ class TlalocB200Ffm private constructor(arena: Arena, library: Path) {
         val table = arena.allocate(ADDRESS, bases.size.toLong())
         bases.forEachIndexed { i, b -> table.setAtIndex(ADDRESS, i.toLong(), ptr(b)) }
         check(peerAllReduceNorm.invokeExact(table, dataOffset, normOffset, flagOffset, ptr(state), ptr(gain), eps, rank, bases.size, rows, cols, ptr(stream)) as Int)
+    }
+
+    /** The exchange with the residual stream distributed by rows: ownRows += the ranks' partials; bf16 RMSNorm rows to every rank. */
+    @Suppress("LongParameterList")
+    fun peerReduceRmsnormRowsF32(
+        arena: Arena, bases: LongArray, dataOffset: Long, normOffset: Long, flagOffset: Long, state: Long, ownRows: Long, gain: Long,
+        eps: Float, rank: Int, rows: Int, cols: Int, stream: Long,
+    ) {
+        val table = arena.allocate(ADDRESS, bases.size.toLong())
+        bases.forEachIndexed { i, b -> table.setAtIndex(ADDRESS, i.toLong(), ptr(b)) }
+        check(
+            peerReduceNormRows.invokeExact(
+                table, dataOffset, normOffset, flagOffset, ptr(state), ptr(ownRows), ptr(gain), eps, rank, bases.size, rows, cols, ptr(stream),
+            ) as Int,
+        )
     }
 
     /** The one-barrier sum: out = residual + the ranks' partials at partialOffset, and the RMSNorm of it, all local. */

@@ -82,6 +82,32 @@ def main():
     assert peer.status() == 0
     calls = 3 * len(shapes) + 2 + 2 + 3 * 20
     assert int(peer.state[0].item()) == calls
+    # The residual stream distributed by rows: tensor 1 holds bare partials; each rank adds its own rows of the residual
+    # stream (rank 0's partial first, then the residual, then the other partials, as the kernel does), keeps the sums
+    # locally and every rank receives only the normalised bf16 rows.
+    if peer.can_fuse_norm(1):
+        rows_, cols_ = shapes[1]
+        lo, hi = rows_ * rank // world, rows_ * (rank + 1) // world
+        gain_r = torch.from_numpy(np.random.default_rng(5).uniform(0.5, 1.5, size=cols_).astype(np.float32)).to(dev)
+        for rep in range(2):
+            round_ += 1
+            res_all = rank_input(shapes[1], 77, round_)
+            own = torch.from_numpy(res_all[lo:hi].copy()).to(dev)
+            peer.tensors[1].copy_(torch.from_numpy(rank_input(shapes[1], rank, round_)))
+            normed_all = peer.reduce_norm_rows_(1, own, gain_r, 1e-5)
+            torch.cuda.synchronize(dev)
+            torch.distributed.barrier()
+            acc = rank_input(shapes[1], 0, round_) + res_all
+            for q in range(1, world):
+                acc = acc + rank_input(shapes[1], q, round_)
+            assert np.array_equal(own.cpu().numpy(), acc[lo:hi]), rep
+            w64 = acc.astype(np.float64)
+            ref = w64 / np.sqrt((w64 * w64).mean(axis=1, keepdims=True) + 1e-5) * gain_r.cpu().numpy().astype(np.float64)[None, :]
+            got = normed_all.float().cpu().numpy().astype(np.float64)
+            assert np.all(np.abs(got - ref) <= np.abs(ref) * 2.0 ** -7 + 1e-6), float(np.abs(got - ref).max())
+            torch.distributed.barrier()
+        calls += 2
+        assert peer.status() == 0 and int(peer.state[0].item()) == calls
     # The one-barrier form: out = residual + the ranks' partials in rank order, kept locally, with the RMSNorm.  Two
     # partial buffers in turn (tensors 1 and a twin), eagerly and from a CUDA graph.
     twin = PeerBuffers([shapes[1], shapes[1]], rank=rank, world=world, group=torch.distributed.group.WORLD, device=dev)

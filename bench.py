@@ -599,6 +599,8 @@ def run_ours(args) -> dict:
     }
     if world > 1:
         line["config"]["rank_sum"] = ("peer-memory kernel, one barrier (every rank sums all partials)" if dec.one_shot
+                                      else "peer-memory kernel, residual stream distributed by rows (reduce-scatter of the partials, "
+                                           "all-gather of the bf16 normalised rows)" if getattr(dec, "rows_residual", False)
                                       else "peer-memory kernel, reduce-scatter + all-gather" if dec.peer is not None else "nccl")
         line["exchange_status"] = dec.exchange_status()  # 0: no bounded wait of the exchange kernel ever gave up
         line["tp_parity"] = parity

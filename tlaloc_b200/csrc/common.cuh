@@ -76,7 +76,9 @@ void CountLaunches(int n);
 // the programmatic-serialization attribute and starts with GridDependencySync(): the kernel may be scheduled (and run
 // whatever comes before that call: shared-memory carve-up, mbarrier and TMEM setup) while its predecessor drains, and
 // the call then waits until the predecessor grid has COMPLETED and its writes are visible.  So no global memory is
-// read or written before it, and correctness is exactly that of plain stream order.  The trigger for the kernel's
+// read or written before it, and correctness is exactly that of plain stream order.  The one exception, taken only
+// when the caller states that the weights are constant (TLALOC_B200_GEMM_WEIGHTS_CONST): the projection kernels fetch
+// their first stages of codes ahead of the call, since no kernel in flight can be writing them.  The trigger for the kernel's
 // own successors is issued right after the wait, never before it, so at most one kernel is ever waiting behind a
 // running one.  A launch without the attribute (another library's kernel, $TLALOC_B200_PDL=0) makes the call a no-op.
 __device__ __forceinline__ void GridDependencySync()

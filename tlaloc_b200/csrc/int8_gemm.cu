@@ -35,6 +35,7 @@ struct GemmParams {
   int M, K, N;
   int Kc;  // K per CTA (a multiple of kGvStageK * kGvWarps)
   int ks;  // K slices (cluster size along y)
+  int weights_const;  // no kernel still in flight writes codes or scales: the first weight stages are fetched before the dependency wait
 };
 
 constexpr int kGvThreads = 128;
@@ -107,7 +108,7 @@ struct GvLayout {
 template <int NT, typename YT>
 __global__ void __launch_bounds__(kGvThreads) Int8GemvKernel(GemmParams p)
 {
-  GridDependencySync();
+  if (!p.weights_const) GridDependencySync();
   using L = GvLayout<NT>;
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -136,7 +137,8 @@ __global__ void __launch_bounds__(kGvThreads) Int8GemvKernel(GemmParams p)
   const uint32_t xdst = kGvWBytes + xm * (kGvStageK * 2) + ((xpiece ^ ((xm >> 1) & 3)) << 4);
   const __nv_bfloat16* x_lane = p.x + static_cast<size_t>(xm) * p.K + kb + warp * kGvStageK + xpiece * 8;
 
-  auto issue = [&](int it) {
+  // A stage's copies in two parts: the weights, which with weights_const depend on no earlier kernel, and the activations.
+  auto issue_w = [&](int it) {
     const int k0 = kb + (warp + kGvWarps * it) * kGvStageK;
     const uint32_t dst = my_pipe_addr + (it % kGvStages) * L::kStageBytes;
     const int8_t* src = w_lane + it * w_stage;
@@ -147,6 +149,18 @@ __global__ void __launch_bounds__(kGvThreads) Int8GemvKernel(GemmParams p)
         CpAsync16(dst + wdst_even + i * (4 * kGvCols), src + i * w_row4, bytes);
         CpAsync16(dst + wdst_odd + i * (4 * kGvCols), src + (i + 1) * w_row4, bytes);
       }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const bool valid = col_ok && k0 + l3 + 4 * i < ke;
+        CpAsync16(dst + ((i & 1) ? wdst_odd - 4 * kGvCols : wdst_even) + i * (4 * kGvCols), valid ? src + i * w_row4 : p.w, valid ? 16 : 0);
+      }
+    }
+  };
+  auto issue_x = [&](int it) {
+    const int k0 = kb + (warp + kGvWarps * it) * kGvStageK;
+    const uint32_t dst = my_pipe_addr + (it % kGvStages) * L::kStageBytes;
+    if (k0 + kGvStageK <= ke) {
 #pragma unroll
       for (int i = 0; i < NT; ++i) {
         const bool valid = xm + 8 * i < p.M;
@@ -155,11 +169,6 @@ __global__ void __launch_bounds__(kGvThreads) Int8GemvKernel(GemmParams p)
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const bool valid = col_ok && k0 + l3 + 4 * i < ke;
-        CpAsync16(dst + ((i & 1) ? wdst_odd - 4 * kGvCols : wdst_even) + i * (4 * kGvCols), valid ? src + i * w_row4 : p.w, valid ? 16 : 0);
-      }
-#pragma unroll
       for (int i = 0; i < NT; ++i) {
         const bool valid = xm + 8 * i < p.M && k0 + xpiece * 8 < ke;
         CpAsync16(dst + xdst + i * (8 * kGvStageK * 2),
@@ -167,10 +176,26 @@ __global__ void __launch_bounds__(kGvThreads) Int8GemvKernel(GemmParams p)
       }
     }
   };
+  auto issue = [&](int it) {
+    issue_w(it);
+    issue_x(it);
+  };
 
-  for (int it = 0; it < kGvStages - 1; ++it) {
-    if (it < my_n) issue(it);
-    CpAsyncCommit();
+  if (p.weights_const) {
+    // The weights of the first stages are on their way while the previous kernel drains; the first commit group then
+    // holds all of them together with the first stage's activations.
+    for (int it = 0; it < kGvStages - 1; ++it)
+      if (it < my_n) issue_w(it);
+    GridDependencySync();
+    for (int it = 0; it < kGvStages - 1; ++it) {
+      if (it < my_n) issue_x(it);
+      CpAsyncCommit();
+    }
+  } else {
+    for (int it = 0; it < kGvStages - 1; ++it) {
+      if (it < my_n) issue(it);
+      CpAsyncCommit();
+    }
   }
 
   // acc[j][nt]: output columns col0 + gid*16 + 2j (c0, c1) and + 2j + 1 (c2, c3), activation rows nt*8 + 2tig, + 1.
@@ -523,6 +548,7 @@ extern "C" int tlaloc_b200_int8_gemm(const void* x, int32_t x_dtype, const int8_
   p.K = k;
   p.N = n;
   p.ks = ChooseSlices(k, n);
+  p.weights_const = (flags & TLALOC_B200_GEMM_WEIGHTS_CONST) != 0 ? 1 : 0;
   const int per = (k + p.ks - 1) / p.ks;
   const int unit = kGvStageK * kGvWarps;
   p.Kc = (per + unit - 1) / unit * unit;

@@ -14,6 +14,8 @@
 
 #include "../../include/tlaloc_b200.h"
 
+struct CUtensorMap_st;  // the driver API's tensor map (cuda.h), named here without including it
+
 namespace tlaloc_b200 {
 
 // Status codes of the C ABI (include/tlaloc_b200.h).
@@ -164,6 +166,8 @@ cudaError_t LaunchInt8GemmI8(const void* x, int x_dtype, const int8_t* codes, co
 // The quantizer alone: the planes of x [m, k] into `planes` (Int8GemmI8ScratchBytes(m, k) bytes).
 cudaError_t LaunchQuantizeRowsI8(const void* x, int x_dtype, void* planes, int m, int k, cudaStream_t st);
 int ReadI8Status();
+bool EncodeKvPoolMap(::CUtensorMap_st* map, const void* base, int head_dim, int kv_heads, unsigned long long positions);
+int ReadPaStatus();
 
 // The activation planes of the int8 tensor-core projection: row m of x as q = rint(x / s[m]) = 256 hi + lo with s[m] the
 // smallest power of two that keeps |q| <= 127 * 256.  Layout in the projection's scratch for an [m, k] activation:

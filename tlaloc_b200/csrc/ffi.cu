@@ -298,8 +298,8 @@ extern "C" long long tlaloc_b200_launch_count(void) { return g_launches.load(std
 
 extern "C" int tlaloc_b200_device_status(void)
 {
-  const int a = ReadTcStatus(), b = ReadI8Status();
-  return a < 0 || b < 0 ? -1 : (a | b);
+  const int a = ReadTcStatus(), b = ReadI8Status(), c = ReadPaStatus();
+  return a < 0 || b < 0 || c < 0 ? -1 : (a | b | c);
 }
 
 extern "C" int tlaloc_b200_set_order_faithful(int on)

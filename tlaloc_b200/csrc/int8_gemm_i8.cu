@@ -525,6 +525,20 @@ cudaError_t LaunchI8Rows(const CUtensorMap& mw, const CUtensorMap& mh, const CUt
 
 }  // namespace
 
+// A [positions][kv_heads][head_dim] bf16 pool read in boxes of 16 positions x 64 channels of one head, 128-byte swizzle.
+bool EncodeKvPoolMap(::CUtensorMap_st* map, const void* base, int head_dim, int kv_heads, unsigned long long positions)
+{
+  EncodeTiledFn encode = EncodeTiled();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(kv_heads), positions};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2, static_cast<cuuint64_t>(head_dim) * 2 * kv_heads};
+  const cuuint32_t box[3] = {64, 1, 16};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 cudaError_t PrepareInt8GemmI8Kernels()
 {
   EncodeTiled();  // resolves the driver entry point now rather than inside a later stream capture

@@ -28,9 +28,11 @@
 //   PaSliceGeneric  any D <= 256, any block size, f32 or bf16 pools, keep masks, up to
 //                   any number of queries (in passes of 8): plain fp32 FMA, warp per
 //                   position for the scores and thread per head dimension for the values.
+#include <cuda.h>
 #include <mutex>
 
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace tlaloc_b200 {
 namespace {
@@ -306,8 +308,25 @@ struct MmaLayout {
 };
 
 // QT: the query's element type (an f32 query is carried as hi + lo bf16 parts); NT: n-tiles of 8 queries.
-template <typename QT, int D, int NS, int NT>
-__global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
+// TMA: the K and V tiles arrive as boxes of a tensor map over the pool (one lane issues them, an mbarrier per warp and
+// stage counts their bytes) instead of 16-byte cp.async copies issued by every lane; the tile then lies in shared memory
+// as 128-byte rows (one 2 KB sub-tile per 64 channels) under the 128-byte swizzle.  Needs a group of 16 positions to
+// lie inside one block (block size a power of two >= 16).
+__device__ int g_pa_status;  // 1: a wait for a K/V tile ran out (the launch's result is then not valid)
+
+__device__ __forceinline__ void TmaLoad3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar)
+{
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void PaMbarExpectTx(uint32_t bar, uint32_t bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+template <typename QT, int D, int NS, int NT, bool TMA>
+__device__ __forceinline__ void PaSliceMmaBody(const PaParams& p, const CUtensorMap* map_k, const CUtensorMap* map_v)
 {
   GridDependencySync();
   constexpr bool QLO = sizeof(QT) == 4;
@@ -317,6 +336,8 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* stages = smem;
   int* tab = reinterpret_cast<int*>(smem + L::kTabOffset);
+  __shared__ __align__(8) unsigned long long tile_bars[kMmaWarps * NS];
+  __shared__ uint32_t abort_word;
 
   const int s = blockIdx.x, kv = blockIdx.y, tb = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -386,6 +407,13 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
       }
     }
   }
+  if (TMA) {
+    if (threadIdx.x == 0) abort_word = 0;
+    if ((threadIdx.x & 31) == 0) {
+      for (int st = 0; st < NS; ++st) tc::MbarInit(SmemAddr(&tile_bars[(threadIdx.x >> 5) * NS + st]), 1);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+  }
   __syncthreads();  // tab is staged
 
   const __nv_bfloat16* kc = static_cast<const __nv_bfloat16*>(p.kc);
@@ -398,9 +426,24 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
 
   // One group of 16 positions: each lane copies 16-byte chunks of the K and V rows; a row's chunk c lands at
   // chunk c ^ (row & 7) so that the ldmatrix reads below are conflict-free.  Rows at or past c1 are zero-filled.
+  const uint32_t my_bars = SmemAddr(&tile_bars[warp * NS]);
   auto issue = [&](int it) {
     const int t_base = t_begin + ((warp + kMmaWarps * it) << 4);
     const uint32_t dst_base = my_stages_addr + (it % NS) * L::kStageBytes;
+    if (TMA) {
+      if (lane == 0) {
+        const int blk = tab[(t_base >> p.bs_shift) - b0];
+        const int pos = (blk << p.bs_shift) + (t_base & (p.bs - 1));  // the group's first position in the pool
+        const uint32_t bar = my_bars + 8 * (it % NS);
+        PaMbarExpectTx(bar, L::kStageBytes);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          TmaLoad3d(dst_base + h * 2048, map_k, 64 * h, kv, pos, bar);
+          TmaLoad3d(dst_base + L::kTileBytes + h * 2048, map_v, 64 * h, kv, pos, bar);
+        }
+      }
+      return;
+    }
     size_t group_off = 0;
     if (one_block_per_group) {
       const int blk = tab[(t_base >> p.bs_shift) - b0];
@@ -430,7 +473,7 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
 
   for (int it = 0; it < NS - 1; ++it) {
     if (it < my_n) issue(it);
-    CpAsyncCommit();
+    if (!TMA) CpAsyncCommit();
   }
 
   float o[NT][KS][4];
@@ -447,26 +490,64 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
   const int row_v = (lane & 7) + (lane >> 4) * 8;        // V^T as A: matrices 2, 3 are positions 8..15; 1, 3 the next 8 dims
 
   for (int it = 0; it < my_n; ++it) {
-    if (it + NS - 1 < my_n) issue(it + NS - 1);
-    CpAsyncCommit();
-    CpAsyncWait<NS - 1>();
-    __syncwarp();
     const int t_base = t_begin + ((warp + kMmaWarps * it) << 4);
     const uint32_t k_addr = my_stages_addr + (it % NS) * L::kStageBytes;
     const uint32_t v_addr = k_addr + L::kTileBytes;
+    if (TMA) {
+      if (it + NS - 1 < my_n) issue(it + NS - 1);
+      if (!tc::MbarWait(my_bars + 8 * (it % NS), (it / NS) & 1, &abort_word)) {
+        g_pa_status = 1;
+        break;
+      }
+      if (t_base + 16 > c1) {
+        // The box brought whole rows of the block; positions at or past the live end weigh nothing, but their V rows
+        // may hold anything (0 x NaN): zero them.  A row is 128 bytes of each sub-tile whatever the swizzle.
+        const int r0 = c1 - t_base;
+        for (int idx = lane; idx < (16 - r0) * (D / 64) * 8; idx += 32) {
+          const int r = r0 + idx / ((D / 64) * 8), rem = idx % ((D / 64) * 8);
+          *reinterpret_cast<uint4*>(my_stages + (it % NS) * L::kStageBytes + L::kTileBytes + (rem >> 3) * 2048 + r * 128 + (rem & 7) * 16) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // before a later box lands in the same space
+        __syncwarp();
+      }
+    } else {
+      if (it + NS - 1 < my_n) issue(it + NS - 1);
+      CpAsyncCommit();
+      CpAsyncWait<NS - 1>();
+      __syncwarp();
+    }
 
-    float sacc[NT][4];
+    // Four accumulation chains per score tile, added at the end: a quarter of the dependent MMAs in a row.
+    float sch[4][NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) sch[c][nt][0] = sch[c][nt][1] = sch[c][nt][2] = sch[c][nt][3] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < KS; ++kk) {
       uint32_t a[4];
-      LdMatrixX4(a, k_addr + row_k * L::kRowBytes + (((2 * kk + (lane >> 4)) ^ (row_k & 7)) << 4));
+      if (TMA) {
+        const int ci = 2 * kk + (lane >> 4);
+        LdMatrixX4(a, k_addr + (ci >> 3) * 2048 + row_k * 128 + (((ci & 7) ^ (row_k & 7)) << 4));
+      } else {
+        LdMatrixX4(a, k_addr + row_k * L::kRowBytes + (((2 * kk + (lane >> 4)) ^ (row_k & 7)) << 4));
+      }
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        MmaBf16(sacc[nt], a, qh[nt][kk][0], qh[nt][kk][1]);
-        if (QLO) MmaBf16(sacc[nt], a, ql[nt][kk][0], ql[nt][kk][1]);
+        if (QLO) {
+          MmaBf16(sch[2 * (kk & 1)][nt], a, qh[nt][kk][0], qh[nt][kk][1]);
+          MmaBf16(sch[2 * (kk & 1) + 1][nt], a, ql[nt][kk][0], ql[nt][kk][1]);
+        } else {
+          MmaBf16(sch[kk & 3][nt], a, qh[nt][kk][0], qh[nt][kk][1]);
+        }
       }
+    }
+    float sacc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int x = 0; x < 4; ++x) sacc[nt][x] = (sch[0][nt][x] + sch[1][nt][x]) + (sch[2][nt][x] + sch[3][nt][x]);
     }
     // sacc[nt]: [0], [1] = position t_base + gid against queries 2tig, 2tig + 1; [2], [3] = position t_base + gid + 8.
     uint32_t pb_hi[NT][2], pb_lo[NT][2];
@@ -517,7 +598,12 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
 #pragma unroll
     for (int mt = 0; mt < KS; ++mt) {
       uint32_t a[4];
-      LdMatrixX4Trans(a, v_addr + row_v * L::kRowBytes + (((2 * mt + ((lane >> 3) & 1)) ^ (row_v & 7)) << 4));
+      if (TMA) {
+        const int ci = 2 * mt + ((lane >> 3) & 1);
+        LdMatrixX4Trans(a, v_addr + (ci >> 3) * 2048 + row_v * 128 + (((ci & 7) ^ (row_v & 7)) << 4));
+      } else {
+        LdMatrixX4Trans(a, v_addr + row_v * L::kRowBytes + (((2 * mt + ((lane >> 3) & 1)) ^ (row_v & 7)) << 4));
+      }
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         MmaBf16(o[nt][mt], a, pb_hi[nt][0], pb_hi[nt][1]);
@@ -526,7 +612,7 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
     }
     __syncwarp();  // the stage is free for the copy the next iteration issues
   }
-  CpAsyncWait<0>();
+  if (!TMA) CpAsyncWait<0>();
   __syncwarp();
 
   // Each warp leaves {m, l, o} of its positions in its own stage space; the CTA then merges the four.
@@ -578,6 +664,19 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
       rec[1] = l;
     }
   }
+}
+
+template <typename QT, int D, int NS, int NT>
+__global__ void __launch_bounds__(kMmaThreads) PaSliceMma(PaParams p)
+{
+  PaSliceMmaBody<QT, D, NS, NT, false>(p, nullptr, nullptr);
+}
+
+template <typename QT, int D, int NT>
+__global__ void __launch_bounds__(kMmaThreads)
+    PaSliceTma(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, PaParams p)
+{
+  PaSliceMmaBody<QT, D, 2, NT, true>(p, &map_k, &map_v);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -783,9 +882,12 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
     const uint32_t k_addr = my_stages_addr + (it % NS) * L::kStageBytes;
     const uint32_t v_addr = k_addr + L::kTileBytes;
 
-    float sacc[NT][4];
+    // Four accumulation chains per score tile, added at the end: a quarter of the dependent MMAs in a row.
+    float sch[4][NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) sch[c][nt][0] = sch[c][nt][1] = sch[c][nt][2] = sch[c][nt][3] = 0.f;
 #pragma unroll
     for (int j = 0; j < KS / 2; ++j) {
       uint32_t r[4];
@@ -799,10 +901,20 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
         E4m3x4ToF16x2x2(hi_rows, a[1], a[3]);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          MmaF16(sacc[nt], a, qh[nt][kk][0], qh[nt][kk][1]);
-          if (QLO) MmaF16(sacc[nt], a, ql[nt][kk][0], ql[nt][kk][1]);
+          if (QLO) {
+            MmaF16(sch[2 * half][nt], a, qh[nt][kk][0], qh[nt][kk][1]);
+            MmaF16(sch[2 * half + 1][nt], a, ql[nt][kk][0], ql[nt][kk][1]);
+          } else {
+            MmaF16(sch[kk & 3][nt], a, qh[nt][kk][0], qh[nt][kk][1]);
+          }
         }
       }
+    }
+    float sacc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int x = 0; x < 4; ++x) sacc[nt][x] = (sch[0][nt][x] + sch[1][nt][x]) + (sch[2][nt][x] + sch[3][nt][x]);
     }
     uint32_t pb_hi[NT][2], pb_lo[NT][2];
 #pragma unroll
@@ -1197,9 +1309,54 @@ cudaError_t LaunchMmaNs(const PaParams& p, cudaStream_t stream)
   return LaunchChained(PaSliceMma<QT, D, NS, 2>, grid, kMmaThreads, smem, stream, p);
 }
 
+// The TMA-fed form of the bf16 kernel ($TLALOC_B200_PA_TMA=0 keeps the cp.async form).
+bool MmaTmaEnabled()
+{
+  static const bool v = [] {
+    const char* e = std::getenv("TLALOC_B200_PA_TMA");
+    return e == nullptr || e[0] != '0';
+  }();
+  return v;
+}
+
+template <typename QT, int D>
+cudaError_t PrepareTma()
+{
+  cudaError_t e = cudaFuncSetAttribute(PaSliceTma<QT, D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(MmaLayout<D, 2>::Bytes(kMaxTabEntries)));
+  if (e == cudaSuccess) {
+    e = cudaFuncSetAttribute(PaSliceTma<QT, D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(MmaLayout<D, 2>::Bytes(kMaxTabEntries)));
+  }
+  return e;
+}
+
+// False when the launch does not qualify (the caller then takes the cp.async form).
+template <typename QT, int D>
+bool LaunchTma(const PaParams& p, cudaStream_t stream, cudaError_t* err)
+{
+  if (!MmaTmaEnabled() || MmaStages() != 2 || p.bs_shift < 4) return false;
+  CUtensorMap map_k, map_v;
+  const unsigned long long positions = static_cast<unsigned long long>(p.P) * p.bs;
+  if (!EncodeKvPoolMap(&map_k, p.kc, D, p.Hkv, positions) || !EncodeKvPoolMap(&map_v, p.vc, D, p.Hkv, positions)) return false;
+  const size_t smem = MmaLayout<D, 2>::Bytes(p.slice / p.bs + 2);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.S, p.Hkv, p.Tb);
+  cfg.blockDim = dim3(kMmaThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  cfg.numAttrs = ChainAttributes(attrs);
+  cfg.attrs = attrs;
+  *err = p.NQ <= 8 ? cudaLaunchKernelEx(&cfg, PaSliceTma<QT, D, 1>, map_k, map_v, p) : cudaLaunchKernelEx(&cfg, PaSliceTma<QT, D, 2>, map_k, map_v, p);
+  return true;
+}
+
 template <typename QT, int D>
 cudaError_t LaunchMma(const PaParams& p, cudaStream_t stream)
 {
+  cudaError_t tma_err = cudaSuccess;
+  if (LaunchTma<QT, D>(p, stream, &tma_err)) return tma_err;
   switch (MmaStages()) {
     case 3: return LaunchMmaNs<QT, D, 3>(p, stream);
     case 4: return LaunchMmaNs<QT, D, 4>(p, stream);
@@ -1296,12 +1453,27 @@ cudaError_t PreparePagedAttentionKernels()
     if (e == cudaSuccess) e = PrepareMma<__nv_bfloat16, 128>();
     if (e == cudaSuccess) e = PrepareMma<float, 64>();
     if (e == cudaSuccess) e = PrepareMma<float, 128>();
+    if (e == cudaSuccess) e = PrepareTma<__nv_bfloat16, 64>();
+    if (e == cudaSuccess) e = PrepareTma<__nv_bfloat16, 128>();
+    if (e == cudaSuccess) e = PrepareTma<float, 64>();
+    if (e == cudaSuccess) e = PrepareTma<float, 128>();
     if (e == cudaSuccess) e = PrepareMmaF8<__nv_bfloat16, 64>();
     if (e == cudaSuccess) e = PrepareMmaF8<__nv_bfloat16, 128>();
     if (e == cudaSuccess) e = PrepareMmaF8<float, 64>();
     if (e == cudaSuccess) e = PrepareMmaF8<float, 128>();
     return e;
   });
+}
+
+int ReadPaStatus()
+{
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_pa_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_pa_status, &zero, sizeof(int));
+  }
+  return v;
 }
 
 }  // namespace tlaloc_b200

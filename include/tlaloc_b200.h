@@ -58,9 +58,9 @@ const char* tlaloc_b200_last_error(void);
 int tlaloc_b200_init(void);
 
 /*
- * Device-side health: 1 if a bounded wait inside a kernel (an mbarrier poll of the tensor-core projection) has
- * given up since the last call, 0 if none has, -1 on a CUDA error.  Synchronises with the device: a test and
- * debugging aid, not for the per-step path.  A kernel whose wait gave up has freed its resources and returned;
+ * Device-side health: 1 if a bounded wait inside a kernel (an mbarrier poll of a tensor-core projection or of the
+ * paged-attention kernel's K/V tiles) has given up since the last call, 0 if none has, -1 on a CUDA error.
+ * Synchronises with the device: a test and debugging aid, not for the per-step path.  A kernel whose wait gave up has freed its resources and returned;
  * its output is undefined.
  */
 int tlaloc_b200_device_status(void);

@@ -231,6 +231,38 @@ def test_llama_shapes_ragged_lengths_permuted_tables(heads, kv_heads, dim, q_dty
         assert np.abs(other - want).max() <= (tol_of(want) if q_dtype == torch.float32 else 2e-3 + 4e-3 * np.abs(want).max())
 
 
+@pytest.mark.parametrize("bs", [8, 16, 32])
+@pytest.mark.parametrize("dim", [64, 128])
+def test_dead_slots_holding_nan_never_reach_the_output(bs, dim):
+    """Slots at or past a row's length hold NaN in both pools (what an unwritten block may hold): the output is, bit
+    for bit, that of clean pools.  Block sizes 16 and 32 take the TMA-fed kernel, which copies whole 16-position
+    groups and must blank the V rows past the end itself; 8 takes the cp.async form, which never copies them."""
+    rng = np.random.default_rng(100 + bs + dim)
+    lens = [1, 5, 16, 17, 31, 33, 250, 1023, 1025, 700]
+    B, width = len(lens), 1040 // bs + 1
+    nb = B * width
+    q = rng.standard_normal((B, 16, dim)).astype(np.float32)
+    k = as_bf16(rng.standard_normal((nb, bs, 2, dim)).astype(np.float32))
+    v = as_bf16(rng.standard_normal((nb, bs, 2, dim)).astype(np.float32))
+    tab = rng.permutation(nb).reshape(B, width).astype(np.int32)  # every block belongs to one row
+    lens = np.asarray(lens, np.int32)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(dim)))
+    want = oracle.paged_attention(q, k, v, tab, lens, scale, threads=8)
+    clean = run(q, k, v, tab, lens, scale, kv_dtype=torch.bfloat16)
+    assert np.abs(clean - want).max() <= tol_of(want)
+    kp, vp = k.copy(), v.copy()
+    live = np.zeros((nb, bs), bool)
+    for r in range(B):
+        for t in range(lens[r]):
+            live[tab[r, t // bs], t % bs] = True
+    kp[~live], vp[~live] = np.float32("nan"), np.float32("nan")
+    got = run(q, kp, vp, tab, lens, scale, kv_dtype=torch.bfloat16)
+    assert np.isfinite(got).all() and np.array_equal(got, clean)
+    from tlaloc_b200 import _native as N
+
+    assert N.lib().tlaloc_b200_device_status() == 0  # no wait for a tile ran out
+
+
 def test_tensor_core_kernel_window_shared_tables_and_lse():
     rng = np.random.default_rng(9)
     heads, kv_heads, dim, bs, width, nb = 16, 4, 128, 16, 128, 300

@@ -600,7 +600,9 @@ def run_ours(args) -> dict:
     if world > 1:
         line["config"]["rank_sum"] = ("peer-memory kernel, one barrier (every rank sums all partials)" if dec.one_shot
                                       else "peer-memory kernel, residual stream distributed by rows (reduce-scatter of the partials, "
-                                           "all-gather of the bf16 normalised rows)" if getattr(dec, "rows_residual", False)
+                                           + ("all-gather of the normalised rows as the next projection's int8 planes)"
+                                              if getattr(dec, "rows_planes", False) else "all-gather of the bf16 normalised rows)")
+                                      if getattr(dec, "rows_residual", False)
                                       else "peer-memory kernel, reduce-scatter + all-gather" if dec.peer is not None else "nccl")
         line["exchange_status"] = dec.exchange_status()  # 0: no bounded wait of the exchange kernel ever gave up
         line["tp_parity"] = parity
@@ -829,6 +831,7 @@ def run_peer_sum(args) -> dict:
             row["peer_with_rmsnorm_us"] = timed(lambda: peer.all_reduce_norm_(0, gain, 1e-5))
             own = torch.zeros((shp[0] // world, shp[1]), device=dev)
             row["rows_residual_with_rmsnorm_us"] = timed(lambda: peer.reduce_norm_rows_(0, own, gain, 1e-5))
+            row["rows_residual_with_rmsnorm_planes_us"] = timed(lambda: peer.reduce_norm_rows_(0, own, gain, 1e-5, planes=True))
         if peer.can_sum_rows(0):
             two = PeerBuffers([shp, shp], rank=rank, world=world, group=group, device=dev)
             hbuf = torch.zeros(shp, device=dev)

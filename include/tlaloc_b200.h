@@ -347,10 +347,16 @@ int tlaloc_b200_peer_allreduce_rmsnorm_f32(void* const* bases, size_t data_offse
  * writes only the bf16 normalised rows into every rank's buffer at norm_offset.  Per rank 2 bytes per element leave
  * instead of 6: at 8 ranks the exchange moves 5.25 MB per rank instead of 8.75 MB for a 128 x 8192 matrix.
  * Arguments and limits as tlaloc_b200_peer_allreduce_rmsnorm_f32; own_rows 16-byte aligned.
+ * planes != 0: the normalised rows travel as the activation planes of the int8 tensor-core projection that reads them
+ * (tlaloc_b200_int8_gemm with TLALOC_B200_GEMM_I8_MMA | TLALOC_B200_GEMM_X_PLANES and the region as its scratch)
+ * instead of bf16: every rank's region at norm_offset then holds [rows][cols] hi bytes, [rows][cols] lo bytes and
+ * [rows] f32 steps, bit for bit what that projection's own quantizer makes of the bf16 rows, and must have
+ * tlaloc_b200_int8_gemm_scratch_bytes(rows, cols, 0) bytes.  The same bytes per element leave; the projection's
+ * quantizer launch is saved.
  */
 int tlaloc_b200_peer_reduce_rmsnorm_rows_f32(void* const* bases, size_t data_offset, size_t norm_offset, size_t flag_offset,
                                              uint32_t* state, float* own_rows, const float* gain, float eps, int32_t rank,
-                                             int32_t world, int32_t rows, int32_t cols, void* stream);
+                                             int32_t world, int32_t rows, int32_t cols, int32_t planes, void* stream);
 
 /*
  * The one-barrier form of the same sum, for the decode step: out = residual + sum over ranks of an f32 [rows, cols]

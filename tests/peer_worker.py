@@ -108,6 +108,37 @@ def main():
             torch.distributed.barrier()
         calls += 2
         assert peer.status() == 0 and int(peer.state[0].item()) == calls
+        # The same exchange handing over the int8 tensor-core projection's planes instead of bf16 rows: the region holds,
+        # bit for bit, what that projection's own quantizer makes of the bf16 rows of the run above with the same inputs.
+        round_ += 1
+        res_all = rank_input(shapes[1], 77, round_)
+        mine = torch.from_numpy(rank_input(shapes[1], rank, round_)).to(dev)
+        own = torch.from_numpy(res_all[lo:hi].copy()).to(dev)
+        peer.tensors[1].copy_(mine)
+        rows_bf16 = peer.reduce_norm_rows_(1, own, gain_r, 1e-5).clone()
+        torch.cuda.synchronize(dev)
+        torch.distributed.barrier()
+        sums = own.clone()
+        want_planes = torch.zeros((ops.int8_gemm_scratch_bytes(rows_, cols_, 0) + 3) // 4, device=dev)
+        codes = torch.zeros((cols_, 256), dtype=torch.int8, device=dev)
+        ops.int8_gemm(rows_bf16, codes, None, scratch=want_planes, i8_mma=True)  # runs the quantizer on the bf16 rows
+        own = torch.from_numpy(res_all[lo:hi].copy()).to(dev)
+        peer.tensors[1].copy_(mine)
+        got_planes = peer.reduce_norm_rows_(1, own, gain_r, 1e-5, planes=True)
+        torch.cuda.synchronize(dev)
+        torch.distributed.barrier()
+        used = (2 * rows_ * cols_ + 4 * rows_) // 4
+        assert torch.equal(own, sums)
+        assert torch.equal(got_planes[:used].view(torch.int32), want_planes[:used].view(torch.int32))
+        # ... and the projection reads them from the peer block
+        wq = torch.from_numpy(np.random.default_rng(9).integers(-127, 128, size=(cols_, 256)).astype(np.int8)).to(dev)
+        y_quant = ops.int8_gemm(rows_bf16, wq, None, scratch=want_planes, i8_mma=True)
+        y_peer = ops.int8_gemm(rows_bf16, wq, None, scratch=got_planes, i8_mma=True, x_planes=True)
+        torch.cuda.synchronize(dev)
+        assert torch.equal(y_quant, y_peer)
+        torch.distributed.barrier()
+        calls += 2
+        assert peer.status() == 0 and int(peer.state[0].item()) == calls
     # The one-barrier form: out = residual + the ranks' partials in rank order, kept locally, with the RMSNorm.  Two
     # partial buffers in turn (tensors 1 and a twin), eagerly and from a CUDA graph.
     twin = PeerBuffers([shapes[1], shapes[1]], rank=rank, world=world, group=torch.distributed.group.WORLD, device=dev)

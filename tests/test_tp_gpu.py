@@ -44,6 +44,15 @@ def test_two_gpu_tensor_parallel_decoder_matches_the_oracle(reduce):
 
 
 @two_gpus
+@pytest.mark.parametrize("reduce", ["peer1", "peer2"])
+def test_two_gpu_decoder_on_the_int8_tensor_core_form_matches_the_oracle(reduce):
+    """Batch 32: the layers' projections on the int8 form; with the two-phase sum the residual stream is distributed by
+    rows and the exchange hands the next projection its int8 planes."""
+    outs = run_ranks("tp_worker.py", limit=400.0, TLALOC_B200_TP_REDUCE=reduce, TP_WORKER_BATCH="32")
+    assert "TP2 ok" in outs[0]
+
+
+@two_gpus
 def test_peer_memory_sum_is_exact_and_identical_on_both_ranks():
     outs = run_ranks("peer_worker.py")
     assert "peer sum ok" in outs[0]

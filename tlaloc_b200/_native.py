@@ -53,7 +53,7 @@ _SIGNATURES = {
     "tlaloc_b200_peer_allreduce_rmsnorm_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _sz, _vp, _vp, _f32, _i32, _i32,
                                                               _i32, _i32, _vp]),
     "tlaloc_b200_peer_reduce_rmsnorm_rows_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _sz, _vp, _vp, _vp, _f32, _i32, _i32,
-                                                               _i32, _i32, _vp]),
+                                                               _i32, _i32, _i32, _vp]),
     "tlaloc_b200_peer_sum_rows_f32": (ctypes.c_int, [ctypes.POINTER(_vp), _sz, _sz, _vp, _vp, _vp, _vp, _vp, _f32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "TlalocRegisterKernels": (ctypes.c_char_p, [_vp]),
     "tlaloc_b200_ffi_handler": (_vp, [ctypes.c_char_p]),

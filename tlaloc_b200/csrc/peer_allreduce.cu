@@ -196,7 +196,7 @@ __device__ __forceinline__ float BlockSum512(float v, float* red)
 template <int W>
 __global__ void __launch_bounds__(kThreads, 1)
 PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, float eps, int rank, int world_rt, int rows, int cols,
-                        float* own_rows)
+                        float* own_rows, int planes)
 {
   GridDependencySync();
   namespace cg = cooperative_groups;
@@ -205,6 +205,8 @@ PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, flo
   __shared__ uint32_t s_epoch, s_last, s_dead;
   __shared__ float red[kThreads / 32];
   __shared__ float part[2];  // this CTA's share of a row's sum of squares, double-buffered over rows
+  __shared__ float pmax[2];  // with planes: the largest magnitude of this CTA's share of the normalised row, likewise
+  __shared__ int pbad[2];    // ... and whether it holds an infinity or a NaN
   const int tid = threadIdx.x;
   if (tid == 0) {
     s_epoch = *reinterpret_cast<volatile uint32_t*>(state) + 1u;
@@ -259,6 +261,8 @@ PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, flo
 #pragma unroll
     for (int q = 0; q < kNormParts; ++q) total += cluster.map_shared_rank(part, q)[trip & 1];  // fixed order: same bits in every part
     const float rsq = static_cast<float>(1.0 / sqrt(static_cast<double>(total / static_cast<float>(cols) + eps)));
+    float amax = 0.f;
+    bool bad = false;
 #pragma unroll
     for (int i = 0; i < kNormVec; ++i) {
       const int c = tid + i * kThreads;
@@ -275,15 +279,64 @@ PeerAllReduceNormKernel(PeerNormTable t, uint32_t* state, const float* gain, flo
         if (own_rows != nullptr) {
           // the sums stay here, in this rank's rows of the residual stream; only the normalised row travels
           *reinterpret_cast<float4*>(own_rows + static_cast<size_t>(row - r_lo) * cols + 4 * cc) = a;
+          if (planes) {  // the bf16 values stay in registers until the row's step is known (below)
+            sum[i] = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+            const float m4 = fmaxf(fmaxf(fabsf(sum[i].x), fabsf(sum[i].y)), fmaxf(fabsf(sum[i].z), fabsf(sum[i].w)));
+            bad = bad || !(m4 <= 3.4e38f);
+            amax = fmaxf(amax, m4);
+          } else {
 #pragma unroll
-          for (int q = 0; q < kMaxRanks; ++q)
-            if (q < world) *reinterpret_cast<uint2*>(t.norm[q] + base + 4 * cc) = packed;
+            for (int q = 0; q < kMaxRanks; ++q)
+              if (q < world) *reinterpret_cast<uint2*>(t.norm[q] + base + 4 * cc) = packed;
+          }
         } else {
 #pragma unroll
           for (int q = 0; q < kMaxRanks; ++q) {
             if (q < world) {
               *reinterpret_cast<float4*>(t.data[q] + base + 4 * cc) = a;
               *reinterpret_cast<uint2*>(t.norm[q] + base + 4 * cc) = packed;
+            }
+          }
+        }
+      }
+    }
+    if (planes) {
+      // The normalised row travels as the int8 tensor-core projection's activation planes instead of bf16: the row's
+      // step needs the largest magnitude over all parts of the row, so the parts meet once more.  The receiving
+      // rank's norm region then holds [rows][cols] hi bytes, [rows][cols] lo bytes and [rows] f32 steps.
+      amax = BlockMax512(amax, red);
+      const int cta_bad = __syncthreads_or(bad ? 1 : 0);
+      if (tid == 0) {
+        pmax[trip & 1] = amax;
+        pbad[trip & 1] = cta_bad;
+      }
+      cluster.sync();
+      float row_max = 0.f;
+      int row_bad = 0;
+#pragma unroll
+      for (int q = 0; q < kNormParts; ++q) {
+        row_max = fmaxf(row_max, cluster.map_shared_rank(pmax, q)[trip & 1]);
+        row_bad |= cluster.map_shared_rank(pbad, q)[trip & 1];
+      }
+      float step;
+      const float inv = I8RowInvStep(row_max, row_bad != 0, &step);
+      const size_t plane_bytes = static_cast<size_t>(rows) * cols;
+      if (blockIdx.y == 0 && tid < world) {
+        reinterpret_cast<float*>(reinterpret_cast<char*>(t.norm[tid]) + 2 * plane_bytes)[row] = step;
+      }
+#pragma unroll
+      for (int i = 0; i < kNormVec; ++i) {
+        const int c = tid + i * kThreads;
+        if (c < part4) {
+          uint32_t hw, lw;
+          I8Split4(sum[i].x, sum[i].y, sum[i].z, sum[i].w, inv, hw, lw);
+          const size_t at = base + 4 * static_cast<size_t>(c_lo + c);
+#pragma unroll
+          for (int q = 0; q < kMaxRanks; ++q) {
+            if (q < world) {
+              char* region = reinterpret_cast<char*>(t.norm[q]);
+              *reinterpret_cast<uint32_t*>(region + at) = hw;
+              *reinterpret_cast<uint32_t*>(region + plane_bytes + at) = lw;
             }
           }
         }
@@ -473,8 +526,10 @@ int LaunchPeerAllReduce(void* const* bases, size_t data_offset, size_t flag_offs
 }
 
 int LaunchPeerAllReduceNorm(void* const* bases, size_t data_offset, size_t norm_offset, size_t flag_offset, uint32_t* state,
-                            const float* gain, float eps, int rank, int world, int rows, int cols, float* own_rows, cudaStream_t st)
+                            const float* gain, float eps, int rank, int world, int rows, int cols, float* own_rows, int planes,
+                            cudaStream_t st)
 {
+  if (planes && own_rows == nullptr) return Fail(kInvalid, "peer_allreduce_rmsnorm: planes go with the row-distributed form only");
   if (own_rows != nullptr && !Aligned16(own_rows)) return Fail(kInvalid, "peer_reduce_rmsnorm_rows: own_rows must be 16-byte aligned");
   if (world < 2 || world > kMaxRanks) return Fail(kInvalid, "peer_allreduce_rmsnorm: world %d outside [2, %d]", world, kMaxRanks);
   if (rank < 0 || rank >= world) return Fail(kInvalid, "peer_allreduce_rmsnorm: rank %d outside [0, %d)", rank, world);
@@ -504,10 +559,10 @@ int LaunchPeerAllReduceNorm(void* const* bases, size_t data_offset, size_t norm_
   cfg.attrs = attrs;
   cudaError_t e;
   switch (world) {
-    case 2: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<2>, t, state, gain, eps, rank, world, rows, cols, own_rows); break;
-    case 4: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<4>, t, state, gain, eps, rank, world, rows, cols, own_rows); break;
-    case 8: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<8>, t, state, gain, eps, rank, world, rows, cols, own_rows); break;
-    default: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<0>, t, state, gain, eps, rank, world, rows, cols, own_rows); break;
+    case 2: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<2>, t, state, gain, eps, rank, world, rows, cols, own_rows, planes); break;
+    case 4: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<4>, t, state, gain, eps, rank, world, rows, cols, own_rows, planes); break;
+    case 8: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<8>, t, state, gain, eps, rank, world, rows, cols, own_rows, planes); break;
+    default: e = cudaLaunchKernelEx(&cfg, PeerAllReduceNormKernel<0>, t, state, gain, eps, rank, world, rows, cols, own_rows, planes); break;
   }
   if (e != cudaSuccess) return CudaFail("peer_allreduce_rmsnorm launch", e);
   CountLaunches(1);
@@ -612,17 +667,17 @@ extern "C" int tlaloc_b200_peer_allreduce_rmsnorm_f32(void* const* bases, size_t
                                                       int32_t rank, int32_t world, int32_t rows, int32_t cols, void* stream)
 {
   return LaunchPeerAllReduceNorm(bases, data_offset, norm_offset, flag_offset, state, gain, eps, rank, world, rows, cols,
-                                 nullptr, static_cast<cudaStream_t>(stream));
+                                 nullptr, 0, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int tlaloc_b200_peer_reduce_rmsnorm_rows_f32(void* const* bases, size_t data_offset, size_t norm_offset,
                                                         size_t flag_offset, uint32_t* state, float* own_rows, const float* gain,
                                                         float eps, int32_t rank, int32_t world, int32_t rows, int32_t cols,
-                                                        void* stream)
+                                                        int32_t planes, void* stream)
 {
   if (!own_rows) return Fail(kInvalid, "peer_reduce_rmsnorm_rows: own_rows is null");
   return LaunchPeerAllReduceNorm(bases, data_offset, norm_offset, flag_offset, state, gain, eps, rank, world, rows, cols,
-                                 own_rows, static_cast<cudaStream_t>(stream));
+                                 own_rows, planes != 0 ? 1 : 0, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int tlaloc_b200_peer_sum_rows_f32(void* const* bases, size_t partial_offset, size_t flag_offset, uint32_t* state,

@@ -148,6 +148,10 @@ class Decoder:
         # The kernels that produce the normalised rows (RMSNorm, the one-barrier sum over ranks) write those planes
         # themselves, so q|k|v and gate|up need no quantizer launch of their own ($TLALOC_B200_NORM_PLANES=0: they do).
         self.norm_planes = self.i8_mma and d % 16 == 0 and d <= 8192 and os.environ.get("TLALOC_B200_NORM_PLANES", "1") != "0"
+        # Likewise the row-distributed exchange: the normalised rows travel as those planes instead of bf16 (same bytes).
+        # Only where the projections that read them are sure to take the int8 form: the region then holds no bf16 rows.
+        self.rows_planes = (self.rows_residual and self.norm_planes and nqkv % 16 == 0 and (2 * self.f) % 16 == 0
+                            and os.environ.get("TLALOC_B200_GEMM_I8", "1") != "0" and os.environ.get("TLALOC_B200_TP_PLANES", "1") != "0")
         self.logits = torch.empty((B, cfg.vocab // world), **f32)
         self.next_ids = torch.zeros((B,), **i32)
         self.best = torch.empty((B,), **f32)
@@ -292,18 +296,24 @@ class Decoder:
         how = dict(weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma)
         pl = self.proj_scratch if self.norm_planes else None
         ops.rmsnorm(p_down, self.layers[0]["ln1"], cfg.rms_eps, out=self.hn, planes=pl)
+        rp = self.rows_planes  # the exchange hands the next projection its int8 planes (in the peer block) instead of bf16 rows
+        from_peer = dict(how, scratch=self.peer.norm_planes, x_planes=True)
+        last = len(self.layers) - 1
         for l, lw in enumerate(self.layers):
-            ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, x_planes=pl is not None and l == 0, **how)
+            if l == 0:
+                ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, x_planes=pl is not None, **how)
+            else:
+                ops.int8_gemm(self.hn, *lw["qkv"], out=self.qkv, **(from_peer if rp else how))
             ops.rope_kv_write(q3, k3, v3, self.positions, self.cos, self.sin, self.slot_mapping, self.key_pools[l],
                               self.value_pools[l], q_out=self.q_rot)
             ops.paged_attention(self.q_rot, self.key_pools[l], self.value_pools[l], self.block_tables, self.seq_lens,
                                 scale=cfg.scale, out=self.att, scratch=self.att_scratch)
             ops.int8_gemm(self.att.view(B, hq * hd), *lw["o"], out=p_o, **how)
-            self.peer.reduce_norm_rows_(1, self.h_rows, lw["ln2"], cfg.rms_eps)
-            self.gate_up_proj(lw)
+            self.peer.reduce_norm_rows_(1, self.h_rows, lw["ln2"], cfg.rms_eps, planes=rp)
+            self.gate_up_proj(lw, x_planes=rp, scratch=self.peer.norm_planes if rp else None)
             ops.int8_gemm(self.act, *lw["down"], out=p_down, **how)
-            nxt = self.layers[l + 1]["ln1"] if l + 1 < len(self.layers) else self.final_norm
-            self.peer.reduce_norm_rows_(0, self.h_rows, nxt, cfg.rms_eps)
+            nxt = self.layers[l + 1]["ln1"] if l < last else self.final_norm
+            self.peer.reduce_norm_rows_(0, self.h_rows, nxt, cfg.rms_eps, planes=rp and l < last)  # the head reads bf16 rows
         self._head_and_greedy()
 
     def _launch_step_one_shot(self) -> None:
@@ -347,14 +357,16 @@ class Decoder:
         if self.world > 1:
             self._merge_greedy()
 
-    def gate_up_proj(self, lw, x_planes: bool = False) -> None:
+    def gate_up_proj(self, lw, x_planes: bool = False, scratch=None) -> None:
         """The MLP's first half for one layer: normalised rows `hn` -> `act` = silu(gate) * up, as one projection with
-        SwiGLU in its epilogue where the shape allows, else the fused gate|up projection and the SwiGLU kernel."""
+        SwiGLU in its epilogue where the shape allows, else the fused gate|up projection and the SwiGLU kernel.
+        `scratch`: where the planes of `hn` are (x_planes) or go; the step's shared projection scratch by default."""
+        scratch = self.proj_scratch if scratch is None else scratch
         if self.fuse_swiglu:
-            ops.int8_gemm_swiglu(self.hn, *lw["gate_up"], out=self.act, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma,
+            ops.int8_gemm_swiglu(self.hn, *lw["gate_up"], out=self.act, weights_const=True, scratch=scratch, i8_mma=self.i8_mma,
                                  x_planes=x_planes)
         else:
-            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True, scratch=self.proj_scratch, i8_mma=self.i8_mma,
+            ops.int8_gemm(self.hn, *lw["gate_up"], out=self.gu, weights_const=True, scratch=scratch, i8_mma=self.i8_mma,
                           x_planes=x_planes)
             ops.swiglu(self.gu[:, :self.f], self.gu[:, self.f:], out=self.act)
 

@@ -47,7 +47,9 @@ class PeerBuffers:
         self.norm_offset, self.norm_shape = off, None
         if norm_shape is not None:
             self.norm_shape = tuple(int(v) for v in norm_shape)
-            off += (2 * int(np.prod(self.norm_shape)) + _ALIGN - 1) // _ALIGN * _ALIGN
+            # bf16 rows, or the same rows as two int8 planes and a step per row (reduce_norm_rows_ with planes)
+            self.norm_bytes = (2 * int(np.prod(self.norm_shape)) + 4 * self.norm_shape[0] + _ALIGN - 1) // _ALIGN * _ALIGN
+            off += self.norm_bytes
         self.flag_offset = off
         self.nbytes = off + _ALIGN
         lib = N.lib()
@@ -72,10 +74,11 @@ class PeerBuffers:
             self._opened.append(p.value)
         whole = torch.as_tensor(_DeviceSpan(self._local, self.nbytes // 4), device=self.device)
         self.tensors = [whole[o // 4:o // 4 + int(np.prod(s))].view(*s) for o, s in zip(self.offsets, shapes)]
-        self.norm_out = None
+        self.norm_out = self.norm_planes = None
         if self.norm_shape is not None:
             n = int(np.prod(self.norm_shape))
             self.norm_out = whole[self.norm_offset // 4:self.norm_offset // 4 + (n + 1) // 2].view(torch.bfloat16)[:n].view(*self.norm_shape)
+            self.norm_planes = whole[self.norm_offset // 4:(self.norm_offset + self.norm_bytes) // 4]  # the same region as a scratch
         self.state = torch.zeros((4,), dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         if world > 1:
@@ -105,10 +108,12 @@ class PeerBuffers:
             torch.cuda.current_stream(self.device).cuda_stream))
         return t, self.norm_out
 
-    def reduce_norm_rows_(self, index: int, own_rows, gain, eps: float):
+    def reduce_norm_rows_(self, index: int, own_rows, gain, eps: float, planes: bool = False):
         """Tensor `index` holds this rank's PARTIAL result.  Adds this rank's rows of the residual stream (`own_rows`,
         local f32 [rows / world, cols], updated in place) and every rank's partial for those rows, and leaves
-        RMSNorm(sum) * gain of ALL rows as bf16 in `norm_out` on every rank.  The f32 sums never travel."""
+        RMSNorm(sum) * gain of ALL rows as bf16 in `norm_out` on every rank.  The f32 sums never travel.
+        `planes`: the rows arrive as the int8 tensor-core projection's activation planes instead (`norm_planes`, to be
+        passed as that projection's scratch with x_planes=True); `norm_out` then holds no bf16 rows."""
         t = self.tensors[index]
         if (own_rows.dtype != torch.float32 or not own_rows.is_contiguous() or own_rows.dim() != 2
                 or own_rows.shape[0] * self.world != t.shape[0] or own_rows.shape[1] != t.shape[1]):
@@ -116,8 +121,8 @@ class PeerBuffers:
         N.check(N.lib().tlaloc_b200_peer_reduce_rmsnorm_rows_f32(
             self._bases, self.offsets[index], self.norm_offset, self.flag_offset, self.state.data_ptr(), own_rows.data_ptr(),
             None if gain is None else gain.data_ptr(), float(eps), self.rank, self.world, t.shape[0], t.shape[1],
-            torch.cuda.current_stream(self.device).cuda_stream))
-        return self.norm_out
+            1 if planes else 0, torch.cuda.current_stream(self.device).cuda_stream))
+        return self.norm_planes if planes else self.norm_out
 
     def sum_rows_(self, index: int, residual, out, gain, eps: float, norm_out=None, planes=None):
         """The one-barrier form: out = residual + sum over ranks of tensor `index` (every rank's partial, added in rank

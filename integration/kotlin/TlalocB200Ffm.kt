@@ -187,7 +187,7 @@ class TlalocB200Ffm private constructor(arena: Arena, library: Path) {
         FunctionDescriptor.of(
             JAVA_INT, ADDRESS, JAVA_LONG, JAVA_LONG, JAVA_LONG, ADDRESS,   // bases, data_offset, norm_offset, flag_offset, state
             ADDRESS, ADDRESS, JAVA_FLOAT,                                  // own_rows, gain, eps
-            JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS,               // rank, world, rows, cols, stream
+            JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS,     // rank, world, rows, cols, planes (0 | 1), stream
         ),
     )
     private val peerSumRows = handle(
@@ -351,17 +351,21 @@ class TlalocB200Ffm private constructor(arena: Arena, library: Path) {
         check(peerAllReduceNorm.invokeExact(table, dataOffset, normOffset, flagOffset, ptr(state), ptr(gain), eps, rank, bases.size, rows, cols, ptr(stream)) as Int)
     }
 
-    /** The exchange with the residual stream distributed by rows: ownRows += the ranks' partials; bf16 RMSNorm rows to every rank. */
+    /**
+     * The exchange with the residual stream distributed by rows: ownRows += the ranks' partials; the RMSNorm rows go to
+     * every rank as bf16, or (planes) as the int8 activation planes of the projection that reads them.
+     */
     @Suppress("LongParameterList")
     fun peerReduceRmsnormRowsF32(
         arena: Arena, bases: LongArray, dataOffset: Long, normOffset: Long, flagOffset: Long, state: Long, ownRows: Long, gain: Long,
-        eps: Float, rank: Int, rows: Int, cols: Int, stream: Long,
+        eps: Float, rank: Int, rows: Int, cols: Int, planes: Boolean, stream: Long,
     ) {
         val table = arena.allocate(ADDRESS, bases.size.toLong())
         bases.forEachIndexed { i, b -> table.setAtIndex(ADDRESS, i.toLong(), ptr(b)) }
         check(
             peerReduceNormRows.invokeExact(
-                table, dataOffset, normOffset, flagOffset, ptr(state), ptr(ownRows), ptr(gain), eps, rank, bases.size, rows, cols, ptr(stream),
+                table, dataOffset, normOffset, flagOffset, ptr(state), ptr(ownRows), ptr(gain), eps, rank, bases.size, rows, cols,
+                if (planes) 1 else 0, ptr(stream),
             ) as Int,
         )
     }

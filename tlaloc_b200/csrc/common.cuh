@@ -167,6 +167,7 @@ cudaError_t LaunchInt8GemmI8(const void* x, int x_dtype, const int8_t* codes, co
 cudaError_t LaunchQuantizeRowsI8(const void* x, int x_dtype, void* planes, int m, int k, cudaStream_t st);
 int ReadI8Status();
 bool EncodeKvPoolMap(::CUtensorMap_st* map, const void* base, int head_dim, int kv_heads, unsigned long long positions);
+bool TensorMapEncoderReady();
 int ReadPaStatus();
 
 // The activation planes of the int8 tensor-core projection: row m of x as q = rint(x / s[m]) = 256 hi + lo with s[m] the

@@ -525,6 +525,9 @@ cudaError_t LaunchI8Rows(const CUtensorMap& mw, const CUtensorMap& mh, const CUt
 
 }  // namespace
 
+// Resolves the driver's tensor-map encoder; called from kernel set-up so that no launch has to do it inside a capture.
+bool TensorMapEncoderReady() { return EncodeTiled() != nullptr; }
+
 // A [positions][kv_heads][head_dim] bf16 pool read in boxes of 16 positions x 64 channels of one head, 128-byte swizzle.
 bool EncodeKvPoolMap(::CUtensorMap_st* map, const void* base, int head_dim, int kv_heads, unsigned long long positions)
 {

@@ -1449,6 +1449,7 @@ cudaError_t PreparePagedAttentionKernels()
 {
   static OncePerDevice once;
   return once.Run([](int) {
+    TensorMapEncoderReady();  // without it the bf16 kernel keeps its cp.async form
     cudaError_t e = PrepareMma<__nv_bfloat16, 64>();
     if (e == cudaSuccess) e = PrepareMma<__nv_bfloat16, 128>();
     if (e == cudaSuccess) e = PrepareMma<float, 64>();

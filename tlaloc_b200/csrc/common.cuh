@@ -166,7 +166,7 @@ cudaError_t LaunchInt8GemmI8(const void* x, int x_dtype, const int8_t* codes, co
 // The quantizer alone: the planes of x [m, k] into `planes` (Int8GemmI8ScratchBytes(m, k) bytes).
 cudaError_t LaunchQuantizeRowsI8(const void* x, int x_dtype, void* planes, int m, int k, cudaStream_t st);
 int ReadI8Status();
-bool EncodeKvPoolMap(::CUtensorMap_st* map, const void* base, int head_dim, int kv_heads, unsigned long long positions);
+bool EncodeKvPoolMap(::CUtensorMap_st* map, const void* base, int head_dim, int kv_heads, unsigned long long positions, int elem_bytes);
 bool TensorMapEncoderReady();
 int ReadPaStatus();
 

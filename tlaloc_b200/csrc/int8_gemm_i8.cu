@@ -528,18 +528,21 @@ cudaError_t LaunchI8Rows(const CUtensorMap& mw, const CUtensorMap& mh, const CUt
 // Resolves the driver's tensor-map encoder; called from kernel set-up so that no launch has to do it inside a capture.
 bool TensorMapEncoderReady() { return EncodeTiled() != nullptr; }
 
-// A [positions][kv_heads][head_dim] bf16 pool read in boxes of 16 positions x 64 channels of one head, 128-byte swizzle.
-bool EncodeKvPoolMap(::CUtensorMap_st* map, const void* base, int head_dim, int kv_heads, unsigned long long positions)
+// A [positions][kv_heads][head_dim] pool of 2-byte (bf16) or 1-byte (f8) elements, read in boxes of 16 positions of one
+// head: 64 bf16 channels under the 128-byte swizzle, or a whole row of D bytes under the swizzle of that width.
+bool EncodeKvPoolMap(::CUtensorMap_st* map, const void* base, int head_dim, int kv_heads, unsigned long long positions, int elem_bytes)
 {
   EncodeTiledFn encode = EncodeTiled();
-  if (encode == nullptr) return false;
+  if (encode == nullptr || (elem_bytes != 1 && elem_bytes != 2)) return false;
+  const cuuint64_t row = static_cast<cuuint64_t>(head_dim) * elem_bytes;
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(kv_heads), positions};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2, static_cast<cuuint64_t>(head_dim) * 2 * kv_heads};
-  const cuuint32_t box[3] = {64, 1, 16};
+  const cuuint64_t strides[2] = {row, row * kv_heads};
+  const cuuint32_t box[3] = {elem_bytes == 2 ? 64u : static_cast<cuuint32_t>(head_dim), 1, 16};
   const cuuint32_t elem[3] = {1, 1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const bool wide = elem_bytes == 2 || head_dim >= 128;  // the box's rows are 128 bytes (else 64)
+  return encode(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims,
+                strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 cudaError_t PrepareInt8GemmI8Kernels()

@@ -733,8 +733,11 @@ struct MmaLayoutF8 {
   static size_t Bytes(int tab_entries) { return kTabOffset + sizeof(int) * static_cast<size_t>(tab_entries); }
 };
 
-template <typename QT, int D, int NS, int NT>
-__global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
+// TMA: as in PaSliceMmaBody, the tiles arrive as boxes (16 positions x D bytes of one head) of a byte tensor map over
+// the pool; the map's swizzle (128-byte rows: SWIZZLE_128B, 64-byte rows: SWIZZLE_64B) is the layout the cp.async form
+// builds by hand, so the reads below are the same for both.
+template <typename QT, int D, int NS, int NT, bool TMA>
+__device__ __forceinline__ void PaSliceMmaF8Body(const PaParams& p, const CUtensorMap* map_k, const CUtensorMap* map_v)
 {
   GridDependencySync();
   constexpr bool QLO = sizeof(QT) == 4;  // a bf16 query is exact in f16 (within its range): no low part to carry
@@ -745,6 +748,8 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* stages = smem;
   int* tab = reinterpret_cast<int*>(smem + L::kTabOffset);
+  __shared__ __align__(8) unsigned long long tile_bars[kMmaWarps * NS];
+  __shared__ uint32_t abort_word;
 
   const int s = blockIdx.x, kv = blockIdx.y, tb = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -809,6 +814,13 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
       }
     }
   }
+  if (TMA) {
+    if (threadIdx.x == 0) abort_word = 0;
+    if ((threadIdx.x & 31) == 0) {
+      for (int st = 0; st < NS; ++st) tc::MbarInit(SmemAddr(&tile_bars[(threadIdx.x >> 5) * NS + st]), 1);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+  }
   __syncthreads();  // tab is staged
 
   const unsigned char* kc = static_cast<const unsigned char*>(p.kc);
@@ -823,9 +835,21 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
   // per 128 bytes) swz = (row >> 1) & 3; either way the eight rows an ldmatrix touches fall in eight different 16-byte
   // bank groups.
   auto swz = [](int r) { return CPR == 8 ? (r & 7) : ((r >> 1) & 3); };
+  const uint32_t my_bars = SmemAddr(&tile_bars[warp * NS]);
   auto issue = [&](int it) {
     const int t_base = t_begin + ((warp + kMmaWarps * it) << 4);
     const uint32_t dst_base = my_stages_addr + (it % NS) * L::kStageBytes;
+    if (TMA) {
+      if (lane == 0) {
+        const int blk = tab[(t_base >> p.bs_shift) - b0];
+        const int pos = (blk << p.bs_shift) + (t_base & (p.bs - 1));  // the group's first position in the pool
+        const uint32_t bar = my_bars + 8 * (it % NS);
+        PaMbarExpectTx(bar, L::kStageBytes);
+        TmaLoad3d(dst_base, map_k, 0, kv, pos, bar);
+        TmaLoad3d(dst_base + L::kTileBytes, map_v, 0, kv, pos, bar);
+      }
+      return;
+    }
     size_t group_off = 0;
     if (one_block_per_group) {
       const int blk = tab[(t_base >> p.bs_shift) - b0];
@@ -855,7 +879,7 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
 
   for (int it = 0; it < NS - 1; ++it) {
     if (it < my_n) issue(it);
-    CpAsyncCommit();
+    if (!TMA) CpAsyncCommit();
   }
 
   float o[NT][KS][4];
@@ -874,13 +898,30 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
   const int row_swz = swz(row_a), hi_chunk = lane >> 4;
 
   for (int it = 0; it < my_n; ++it) {
-    if (it + NS - 1 < my_n) issue(it + NS - 1);
-    CpAsyncCommit();
-    CpAsyncWait<NS - 1>();
-    __syncwarp();
     const int t_base = t_begin + ((warp + kMmaWarps * it) << 4);
     const uint32_t k_addr = my_stages_addr + (it % NS) * L::kStageBytes;
     const uint32_t v_addr = k_addr + L::kTileBytes;
+    if (it + NS - 1 < my_n) issue(it + NS - 1);
+    if (TMA) {
+      if (!tc::MbarWait(my_bars + 8 * (it % NS), (it / NS) & 1, &abort_word)) {
+        g_pa_status = 1;
+        break;
+      }
+      if (t_base + 16 > c1) {
+        // positions at or past the live end weigh nothing, but their V rows may hold anything (0 x NaN): zero them
+        const int r0 = c1 - t_base;
+        for (int idx = lane; idx < (16 - r0) * CPR; idx += 32) {
+          *reinterpret_cast<uint4*>(my_stages + (it % NS) * L::kStageBytes + L::kTileBytes + (r0 + idx / CPR) * L::kRowBytes + (idx % CPR) * 16) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // before a later box lands in the same space
+        __syncwarp();
+      }
+    } else {
+      CpAsyncCommit();
+      CpAsyncWait<NS - 1>();
+      __syncwarp();
+    }
 
     // Four accumulation chains per score tile, added at the end: a quarter of the dependent MMAs in a row.
     float sch[4][NT][4];
@@ -981,7 +1022,7 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
     }
     __syncwarp();
   }
-  CpAsyncWait<0>();
+  if (!TMA) CpAsyncWait<0>();
   __syncwarp();
 
   {
@@ -1032,6 +1073,19 @@ __global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
       rec[1] = l;
     }
   }
+}
+
+template <typename QT, int D, int NS, int NT>
+__global__ void __launch_bounds__(kMmaThreads) PaSliceMmaF8(PaParams p)
+{
+  PaSliceMmaF8Body<QT, D, NS, NT, false>(p, nullptr, nullptr);
+}
+
+template <typename QT, int D, int NS, int NT>
+__global__ void __launch_bounds__(kMmaThreads)
+    PaSliceTmaF8(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, PaParams p)
+{
+  PaSliceMmaF8Body<QT, D, NS, NT, true>(p, &map_k, &map_v);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1338,7 +1392,7 @@ bool LaunchTma(const PaParams& p, cudaStream_t stream, cudaError_t* err)
   if (!MmaTmaEnabled() || MmaStages() != 2 || p.bs_shift < 4) return false;
   CUtensorMap map_k, map_v;
   const unsigned long long positions = static_cast<unsigned long long>(p.P) * p.bs;
-  if (!EncodeKvPoolMap(&map_k, p.kc, D, p.Hkv, positions) || !EncodeKvPoolMap(&map_v, p.vc, D, p.Hkv, positions)) return false;
+  if (!EncodeKvPoolMap(&map_k, p.kc, D, p.Hkv, positions, 2) || !EncodeKvPoolMap(&map_v, p.vc, D, p.Hkv, positions, 2)) return false;
   const size_t smem = MmaLayout<D, 2>::Bytes(p.slice / p.bs + 2);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.S, p.Hkv, p.Tb);
@@ -1380,12 +1434,11 @@ int MmaF8Stages()
 template <typename QT, int D, int NS>
 cudaError_t PrepareMmaF8Ns()
 {
-  cudaError_t e = cudaFuncSetAttribute(PaSliceMmaF8<QT, D, NS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(MmaLayoutF8<D, NS>::Bytes(kMaxTabEntries)));
-  if (e == cudaSuccess) {
-    e = cudaFuncSetAttribute(PaSliceMmaF8<QT, D, NS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(MmaLayoutF8<D, NS>::Bytes(kMaxTabEntries)));
-  }
+  const int bytes = static_cast<int>(MmaLayoutF8<D, NS>::Bytes(kMaxTabEntries));
+  cudaError_t e = cudaFuncSetAttribute(PaSliceMmaF8<QT, D, NS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(PaSliceMmaF8<QT, D, NS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(PaSliceTmaF8<QT, D, NS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(PaSliceTmaF8<QT, D, NS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
   return e;
 }
 
@@ -1402,6 +1455,22 @@ cudaError_t LaunchMmaF8Ns(const PaParams& p, cudaStream_t stream)
 {
   const size_t smem = MmaLayoutF8<D, NS>::Bytes(p.slice / p.bs + 2);
   const dim3 grid(p.S, p.Hkv, p.Tb);
+  if (MmaTmaEnabled() && p.bs_shift >= 4) {  // a group of 16 positions lies inside one block: the tiles come as TMA boxes
+    CUtensorMap map_k, map_v;
+    const unsigned long long positions = static_cast<unsigned long long>(p.P) * p.bs;
+    if (EncodeKvPoolMap(&map_k, p.kc, D, p.Hkv, positions, 1) && EncodeKvPoolMap(&map_v, p.vc, D, p.Hkv, positions, 1)) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = grid;
+      cfg.blockDim = dim3(kMmaThreads, 1, 1);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = stream;
+      cudaLaunchAttribute attrs[2];
+      cfg.numAttrs = ChainAttributes(attrs);
+      cfg.attrs = attrs;
+      if (p.NQ <= 8) return cudaLaunchKernelEx(&cfg, PaSliceTmaF8<QT, D, NS, 1>, map_k, map_v, p);
+      return cudaLaunchKernelEx(&cfg, PaSliceTmaF8<QT, D, NS, 2>, map_k, map_v, p);
+    }
+  }
   if (p.NQ <= 8) return LaunchChained(PaSliceMmaF8<QT, D, NS, 1>, grid, kMmaThreads, smem, stream, p);
   return LaunchChained(PaSliceMmaF8<QT, D, NS, 2>, grid, kMmaThreads, smem, stream, p);
 }

@@ -357,7 +357,7 @@ class StepBench:
                     traffic = float(per_pos) * int(lens_now.sum()) * hk
         except Exception:
             pass
-        return {"kernel": ("PaSliceTma" if self.kv == "bf16" else "PaSliceMmaF8") + "+PaCombine", "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+        return {"kernel": ("PaSliceTma" if self.kv == "bf16" else "PaSliceTmaF8") + "+PaCombine", "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / pk["hbm_gbs"], "traffic": traffic, "peak_kind": pk["kind"], "bytes_per_launch": att_bytes,
                 "ms_per_launch": att_ms, "pool": "one block per (sequence, 16 positions): nothing shared",
                 "in_step_pools": {"ms_per_launch": in_step_ms, "logical_gbs": att_bytes / (in_step_ms / 1e3) / 1e9,
@@ -766,7 +766,7 @@ def run_operator(args) -> dict:
         return {"metric": "paged_attention_hbm_gbs", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": max(args.steps, 20),
                 "warmup": 3, "higher_is_better": True, "data": "synthetic", "dtype": "bf16 KV and Q, f32 accumulate",
                 "config": {"workload": "paged-attention decode operator alone", "algorithmic_bytes": out["algorithmic_bytes"], "cases": out},
-                "roofline": {"kernel": ("PaSliceTma" if args.kv == "bf16" else "PaSliceMmaF8") + "+PaCombine", "bound": "hbm", "achieved": head["gbs"], "peak": pk["hbm_gbs"],
+                "roofline": {"kernel": ("PaSliceTma" if args.kv == "bf16" else "PaSliceTmaF8") + "+PaCombine", "bound": "hbm", "achieved": head["gbs"], "peak": pk["hbm_gbs"],
                              "unit": "GB/s", "frac": head["gbs"] / pk["hbm_gbs"], "peak_kind": pk["kind"], "traffic": None}}
     out = operator_int8_projection(torch, dev, pk, only=args.only)
     rows = out["rows"]

@@ -176,3 +176,32 @@ def test_tiny_decoder_with_e4m3_kv_matches_the_oracle(exact):
         assert np.mean(got == kp[l][1:]) >= (1.0 if exact else 0.95)
     print(f"e4m3 KV, exact={exact}: worst logit |d| {worst:.2e}, token differences {swaps} of {48 * B}")
     assert swaps == 0 if exact else swaps <= 6
+
+
+@pytest.mark.parametrize("bs", [16, 32])
+@pytest.mark.parametrize("dim", [64, 128])
+def test_dead_slots_holding_nan_bytes_never_reach_the_output(bs, dim):
+    """Slots at or past a row's length hold the e4m3fn NaN byte (0x7F) in both pools: the output is, bit for bit, that of
+    clean pools.  The TMA-fed kernel copies whole 16-position groups and blanks the V rows past the end itself."""
+    rng = np.random.default_rng(200 + bs + dim)
+    lens = np.asarray([1, 5, 16, 17, 31, 33, 250, 1023, 1025, 700], np.int32)
+    B, width = len(lens), 1040 // bs + 1
+    nb = B * width
+    q = rng.standard_normal((B, 16, dim)).astype(np.float32)
+    k = oracle.snap_e4m3(rng.standard_normal((nb, bs, 2, dim)).astype(np.float32))
+    v = oracle.snap_e4m3(rng.standard_normal((nb, bs, 2, dim)).astype(np.float32))
+    tab = rng.permutation(nb).reshape(B, width).astype(np.int32)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(dim)))
+    want = oracle.paged_attention(q, k, v, tab, lens, scale, threads=8)
+    clean = ops().paged_attention(dev(q), f8_pool(k), f8_pool(v), dev(tab), dev(lens), scale=scale).float().cpu().numpy()
+    assert np.abs(clean - want).max() <= max(1e-4, 1e-5 * float(np.abs(want).max()))
+    live = np.zeros((nb, bs), bool)
+    for r in range(B):
+        for t in range(lens[r]):
+            live[tab[r, t // bs], t % bs] = True
+    kb, vb = oracle.e4m3_bits(k), oracle.e4m3_bits(v)
+    kb[~live], vb[~live] = 0x7F, 0x7F
+    kp, vp = torch.from_numpy(kb).to(DEV).view(F8), torch.from_numpy(vb).to(DEV).view(F8)
+    got = ops().paged_attention(dev(q), kp, vp, dev(tab), dev(lens), scale=scale).float().cpu().numpy()
+    assert np.isfinite(got).all() and np.array_equal(got, clean)
+

@@ -561,6 +561,9 @@ def run_ours(args) -> dict:
     group = None
     parity = None
     if world > 1:
+        # NCCL carries only the handle exchange, barriers and the per-step gather of (best logit, id) pairs; the sums
+        # over ranks are the library's own peer-memory kernels, so NCCL's NVLink multicast buffers are not set up
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         torch.distributed.init_process_group("nccl", device_id=dev)
         group = torch.distributed.group.WORLD
         parity = tp_parity(torch, dev, rank, world, group)
@@ -790,6 +793,7 @@ def run_peer_sum(args) -> dict:
         raise SystemExit("--workload peer_sum needs torch.distributed.run with --gpus N >= 2 ranks")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # NCCL's all-reduce is timed as plain ring/tree; no multicast buffers
     torch.distributed.init_process_group("nccl", device_id=dev)
     group = torch.distributed.group.WORLD
     shapes = [(128, 8192), (8, 8192), (64, 4096)]
